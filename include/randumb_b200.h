@@ -1,0 +1,195 @@
+/*
+ * randumb_b200 -- C ABI of the B200 (sm_100a) pseudorandom-weight linear layer.
+ *
+ * The layer's weight is never stored:  W[o,i] = sum_k S[o,k] * C[k,i]  where
+ *   S[o,k] = squirrel5(uint32(198491317*o + k), seed)  in [-1,1]   (N x R, regenerated on the fly)
+ *   C      = trainable coefficient matrix                          (R x K, row-major)
+ * and   y = x W^T,   dX = dY W,   dC = S^T (dY^T X).
+ *
+ * Conventions for every entry point
+ *   - all pointers are DEVICE pointers owned by the caller (row-major, densely packed unless a
+ *     leading dimension is passed); the library allocates nothing and frees nothing;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream);
+ *     no entry point synchronises the device;
+ *   - return value: 0 = ok, <0 = argument error found on the host before any launch
+ *     (rdb_strerror names it), >0 = a cudaError_t raised by a launch or by tensor-map encoding;
+ *   - `status` (optional, may be NULL) points to 4 device int32 words, zeroed by the caller.  A
+ *     kernel whose bounded internal wait expires writes a non-zero code there and returns early
+ *     instead of hanging; the caller reads it after synchronising when it wants to check;
+ *   - row0 is the global index of the first noise row this call owns: a rank that holds output
+ *     rows [row0, row0+N) of a larger virtual layer passes its own row0 and regenerates exactly
+ *     its rows, so sharding a layer moves no weight bytes;
+ *   - seed is used modulo 2^32 (two's complement for negative Python ints).
+ *
+ * Each declaration cites the reference interface it stands in for (paths inside the reference
+ * project Clyde013/randumb).
+ */
+#ifndef RANDUMB_B200_H
+#define RANDUMB_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RDB_VERSION 100
+
+/* element types */
+#define RDB_F32 0
+#define RDB_BF16 1
+
+/* association of W = S*C with the activation (rdb_linear_*): */
+#define RDB_PATH_AUTO 0     /* pick by FLOP count */
+#define RDB_PATH_FACTORED 1 /* y = (x C^T) S^T ;  g = dY S, dX = g C, dC = g^T X  */
+#define RDB_PATH_WPATH 2    /* materialise W = S C in workspace, then dense products */
+
+/* which kernels may run (rdb_linear_*): */
+#define RDB_IMPL_AUTO 0   /* tcgen05 tensor-core kernels when dtype/shape allow, else SIMT */
+#define RDB_IMPL_SIMT 1   /* CUDA-core kernels only (any shape, any dtype) */
+#define RDB_IMPL_UMMA 2   /* tcgen05 kernels only; error if the shape does not qualify */
+
+/* error codes (negative) */
+#define RDB_OK 0
+#define RDB_ERR_NULL -1
+#define RDB_ERR_SHAPE -2
+#define RDB_ERR_DTYPE -3
+#define RDB_ERR_ALIGN -4
+#define RDB_ERR_WORKSPACE -5
+#define RDB_ERR_UNSUPPORTED -6
+#define RDB_ERR_DRIVER -7
+#define RDB_ERR_TOO_LARGE -8
+
+/* device-side give-up codes written to status[0] */
+#define RDB_STATUS_TIMEOUT_PRODUCER 1
+#define RDB_STATUS_TIMEOUT_MMA 2
+#define RDB_STATUS_TIMEOUT_EPILOGUE 3
+#define RDB_STATUS_TIMEOUT_GENERATOR 4
+
+int rdb_version(void);
+const char *rdb_strerror(int code);
+
+/*
+ * Process-wide tuning switches (not part of the reference surface; defaults are the tuned ones).
+ *   RDB_OPT_NOISE_TILE   0: generated tile 128 noise rows reused by 512 tokens (default)
+ *                        1: generated tile 256 noise rows reused by 256 tokens
+ *   RDB_OPT_BWD_OPERANDS 0: dX / dC read C, g and x in place through MN-major MMA descriptors (default)
+ *                        1: explicit transposed copies in workspace, K-major descriptors only
+ * Returns the previous value, or RDB_ERR_UNSUPPORTED for an unknown key.
+ */
+#define RDB_OPT_NOISE_TILE 1
+#define RDB_OPT_BWD_OPERANDS 2
+int rdb_set_option(int key, int value);
+
+/*
+ * Raw hash words of the noise matrix: out[r*ld + c] = bits(row0 + r, col0 + c, seed), uint32.
+ * The reference never exposes the integers; this is the bit-exactness surface for
+ * squirrel5_gen_2d (src/rten_cpp/RandumbTensor.py:130-164) and sq5_2d (csrc/cuda/rten.cu:28-48).
+ */
+int rdb_noise_bits(uint32_t *out, int64_t rows, int64_t cols, int64_t ld, int64_t row0, int64_t col0,
+                   uint32_t seed, void *stream);
+
+/*
+ * Explicit noise matrix as float32 or bfloat16 (bf16 = round-to-nearest-even of the float32 value).
+ * Stands in for squirrel5_generate_2d (src/rten_cpp/RandumbTensor.py:78-105),
+ * RandumbTensor.get_noise_matrix (:870-873) and rten_cpp::sq5_gen_2d (csrc/cuda/rten.cu:50-71,
+ * without its row-stride defect at :55).
+ */
+int rdb_noise(void *out, int dtype, int64_t rows, int64_t cols, int64_t ld, int64_t row0, int64_t col0,
+              uint32_t seed, void *stream);
+
+/*
+ * 1-D noise out[i] = value(idx0 + i, seed) with no row mixing: squirrel5_gen_1d
+ * (src/rten_cpp/RandumbTensor.py:204-232), the generator of the reference's fused random bias.
+ */
+int rdb_noise_1d(float *out, int64_t n, int64_t idx0, uint32_t seed, void *stream);
+
+/*
+ * Bytes of scratch the linear entry points need for the given problem (op: 0 = forward,
+ * 1 = backward).  The workspace must be 256-byte aligned.
+ */
+size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path,
+                                  int impl);
+
+/*
+ * Forward  y[T,N] = x[T,K] * W^T  with W regenerated from (seed, row0) and coef[R,K].
+ * This is the fused product the reference left as a placeholder: the aten.mm override
+ * (src/rten_cpp/RandumbTensor.py:942-946) -> fakeMM (:771-791), and the abandoned Triton
+ * attempts rt_mm / rt_mm_grouped (:457-769).
+ */
+int rdb_linear_fwd(void *y, const void *x, const void *coef, void *workspace, size_t workspace_bytes,
+                   int64_t T, int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed, int dtype,
+                   int path, int impl, int32_t *status, void *stream);
+
+/*
+ * Backward: dx[T,K] = dy W (skipped when dx == NULL) and dc[R,K] = S^T (dy^T x) (skipped when
+ * dc == NULL).  dc is written in `dtype`.  Replaces fakeMMFunction.backward
+ * (src/rten_cpp/RandumbTensor.py:783-788) followed by RandumbTensorConstructor.backward
+ * (:979-990) / materialize_bwd (:304-359, :383-390): no dense dW is formed on the factored path.
+ */
+int rdb_linear_bwd(void *dx, void *dc, const void *dy, const void *x, const void *coef, void *workspace,
+                   size_t workspace_bytes, int64_t T, int64_t K, int64_t N, int64_t R, int64_t row0,
+                   uint32_t seed, int dtype, int path, int impl, int32_t *status, void *stream);
+
+/*
+ * Batch-1 float32 forward: y[N] = S (C x).  workspace: R floats.  Same reference slot as
+ * rdb_linear_fwd, specialised for a single activation row (matrix-vector; bandwidth bound).
+ */
+int rdb_gemv_fwd(float *y, const float *x, const float *coef, float *workspace, int64_t K, int64_t N,
+                 int64_t R, int64_t row0, uint32_t seed, void *stream);
+
+/*
+ * Batch-1 float32 backward: g = S^T dy (workspace, R floats), dx[K] = g C, dc[R,K] = g x^T.
+ * dx or dc may be NULL.
+ */
+int rdb_gemv_bwd(float *dx, float *dc, const float *dy, const float *x, const float *coef, float *workspace,
+                 int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed, void *stream);
+
+/*
+ * Building block: D[M,N] = A[M,Kc] * G^T where G is generated, never read from memory.
+ *   transposed == 0:  G[n,k] = S[row0+n, col0+k]      (y = z S^T : contraction over noise columns)
+ *   transposed == 1:  G[n,k] = S[row0+k, col0+n]      (g = dY S  : contraction over noise rows)
+ * A is row-major with leading dimension lda; D row-major with ldd.  When d_t != NULL (bf16 tcgen05
+ * kernel only) the transpose D^T[N,M] is written there as well (leading dimension ldd_t).
+ * a_dtype / d_dtype: RDB_F32 or RDB_BF16 (the tcgen05 kernel needs both bf16).
+ * Same reference slot as rt_mm_grouped_kernel (src/rten_cpp/RandumbTensor.py:648-746), whose RT
+ * operand is regenerated tile by tile inside the kernel.
+ */
+int rdb_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda,
+                   int64_t ldd, int64_t ldd_t, int a_dtype, int d_dtype, int transposed, int64_t row0,
+                   int64_t col0, uint32_t seed, int impl, int32_t *status, void *stream);
+
+/*
+ * Building block: dense D[M,N] = op(A) * op(B)^T, float32 accumulation.
+ *   a_kmajor != 0: A is [M,Kc] row-major (lda);  == 0: A is stored [Kc,M] row-major (lda).
+ *   b_kmajor != 0: B is [N,Kc] row-major (ldb);  == 0: B is stored [Kc,N] row-major (ldb).
+ * The plain products of the factored layer (x C^T, g C, g^T x); the reference calls cuBLAS here
+ * (src/rten_cpp/RandumbTensor.py:780, 786-787).
+ */
+int rdb_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda,
+                   int64_t ldb, int64_t ldd, int a_dtype, int b_dtype, int d_dtype, int a_kmajor,
+                   int b_kmajor, int impl, int32_t *status, void *stream);
+
+/*
+ * Reference 1-D-coefficient form (every existing randumb model):
+ *   out[n] = sum_m S[sq(n), m] * coef[m],  sq(n) = (n % Q)*stride_Q + (n / Q)*stride_P,  float32 [P,Q].
+ * Stands in for rten::materialize_fwd (src/rten_cpp/RandumbTensor.py:235-290, 371-381) and
+ * rten_cpp::materialize_fwd (csrc/cuda/rten.cu:74-152); the fused random bias is not included.
+ */
+int rdb_materialize_fwd(float *out, const float *coef, int64_t M, int64_t P, int64_t Q, int64_t stride_P,
+                        int64_t stride_Q, uint32_t seed, void *stream);
+
+/*
+ * dcoef[m] = sum_n S[n,m] * dout[n] over the flattened contiguous dout (float32), deterministic
+ * reduction order.  Stands in for rten::materialize_bwd (src/rten_cpp/RandumbTensor.py:304-359,
+ * 383-390).  workspace: rdb_materialize_bwd_workspace_bytes(Nel, M) bytes.
+ */
+size_t rdb_materialize_bwd_workspace_bytes(int64_t Nel, int64_t M);
+int rdb_materialize_bwd(float *dcoef, const float *dout, float *workspace, int64_t Nel, int64_t M,
+                        uint32_t seed, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RANDUMB_B200_H */

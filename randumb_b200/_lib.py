@@ -1,0 +1,73 @@
+"""ctypes binding of librandumb_b200.so (the C ABI declared in include/randumb_b200.h).
+
+There is no fallback: if the shared library is missing the import of any compute entry raises,
+and every wrapper raises ``RuntimeError`` carrying ``rdb_strerror`` on a non-zero return code.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "librandumb_b200.so")
+
+# constants mirrored from include/randumb_b200.h
+F32, BF16 = 0, 1
+PATH_AUTO, PATH_FACTORED, PATH_WPATH = 0, 1, 2
+IMPL_AUTO, IMPL_SIMT, IMPL_UMMA = 0, 1, 2
+OPT_NOISE_TILE, OPT_BWD_OPERANDS = 1, 2
+STATUS_NAMES = {0: "ok", 1: "producer wait expired", 2: "mma wait expired", 3: "epilogue wait expired",
+                4: "generator wait expired"}
+
+_i64, _u32, _i32, _vp, _sz = ctypes.c_int64, ctypes.c_uint32, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
+
+# name -> (restype, argtypes); one entry per declaration in the header
+PROTOTYPES = {
+    "rdb_version": (_i32, []),
+    "rdb_strerror": (ctypes.c_char_p, [_i32]),
+    "rdb_set_option": (_i32, [_i32, _i32]),
+    "rdb_noise_bits": (_i32, [_vp, _i64, _i64, _i64, _i64, _i64, _u32, _vp]),
+    "rdb_noise": (_i32, [_vp, _i32, _i64, _i64, _i64, _i64, _i64, _u32, _vp]),
+    "rdb_noise_1d": (_i32, [_vp, _i64, _i64, _u32, _vp]),
+    "rdb_linear_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64, _i64, _i32, _i32, _i32]),
+    "rdb_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32, _vp, _vp]),
+    "rdb_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32,
+                              _vp, _vp]),
+    "rdb_gemv_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
+    "rdb_gemv_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
+    "rdb_gemm_noise": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i64, _i64, _u32, _i32,
+                              _vp, _vp]),
+    "rdb_gemm_dense": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp,
+                              _vp]),
+    "rdb_materialize_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _u32, _vp]),
+    "rdb_materialize_bwd_workspace_bytes": (_sz, [_i64, _i64]),
+    "rdb_materialize_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _u32, _vp]),
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the library once; raise loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: build it with `python -m randumb_b200.build` "
+                "(needs nvcc; there is no CPU or PyTorch fallback for the kernels)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def strerror(code: int) -> str:
+    return lib().rdb_strerror(int(code)).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed: [{code}] {strerror(code)}")

@@ -1,0 +1,325 @@
+// C-ABI entry points of the layer: argument checks, association/kernel choice, workspace carving.
+#include "common.cuh"
+
+namespace rdb {
+
+static int g_bwd_operands = 0;  // RDB_OPT_BWD_OPERANDS
+static int g_noise_tile = 0;    // RDB_OPT_NOISE_TILE
+
+// dst[c, r] = src[r, c]  (bf16), 32x32 tiles through shared memory.
+__global__ void transpose_bf16_kernel(__nv_bfloat16 *__restrict__ dst, int64_t ldd, const __nv_bfloat16 *__restrict__ src,
+                                      int64_t lds, int64_t rows, int64_t cols) {
+    __shared__ __nv_bfloat16 tile[32][34];
+    const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+    for (int i = threadIdx.y; i < 32; i += 8) {
+        const int64_t r = r0 + i, c = c0 + threadIdx.x;
+        if (r < rows && c < cols) tile[i][threadIdx.x] = src[r * lds + c];
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += 8) {
+        const int64_t c = c0 + i, r = r0 + threadIdx.x;
+        if (r < rows && c < cols) dst[c * ldd + r] = tile[threadIdx.x][i];
+    }
+}
+
+static int transpose_bf16(void *dst, int64_t ldd, const void *src, int64_t lds, int64_t rows, int64_t cols, cudaStream_t st) {
+    if (rows == 0 || cols == 0) return RDB_OK;
+    const int64_t gx = cdiv64(cols, 32), gy = cdiv64(rows, 32);
+    if (gy > 65535) {
+        // fold the row tiles into x when there are too many for gridDim.y
+        return RDB_ERR_TOO_LARGE;
+    }
+    dim3 grid((unsigned)gx, (unsigned)gy), block(32, 8);
+    transpose_bf16_kernel<<<grid, block, 0, st>>>(reinterpret_cast<__nv_bfloat16 *>(dst), ldd,
+                                                 reinterpret_cast<const __nv_bfloat16 *>(src), lds, rows, cols);
+    return launch_status();
+}
+
+// FLOP-count rule: factored costs 2TR(K+N) per result, the W path 2NRK + 2TNK.
+static int choose_path(int path, int64_t T, int64_t K, int64_t N, int64_t R) {
+    if (path == RDB_PATH_FACTORED || path == RDB_PATH_WPATH) return path;
+    const double fact = 2.0 * (double)T * (double)R * ((double)K + (double)N);
+    const double wp = 2.0 * (double)N * (double)R * (double)K + 2.0 * (double)T * (double)N * (double)K;
+    return fact <= wp ? RDB_PATH_FACTORED : RDB_PATH_WPATH;
+}
+
+static bool umma_eligible(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path) {
+    return dtype == RDB_BF16 && path == RDB_PATH_FACTORED && T >= 1 && (K % 8) == 0 && (N % 8) == 0 && (R % 8) == 0 &&
+           K >= 8 && N >= 8 && R >= 8 && T < (1LL << 31) && K < (1LL << 31) && N < (1LL << 31) && R < (1LL << 31);
+}
+
+// returns RDB_IMPL_SIMT or RDB_IMPL_UMMA, or a negative error
+static int choose_impl(int impl, int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path) {
+    const bool ok = umma_eligible(T, K, N, R, dtype, path);
+    if (impl == RDB_IMPL_UMMA) return ok ? RDB_IMPL_UMMA : RDB_ERR_UNSUPPORTED;
+    if (impl == RDB_IMPL_SIMT) return RDB_IMPL_SIMT;
+    if (impl != RDB_IMPL_AUTO) return RDB_ERR_UNSUPPORTED;
+    return ok ? RDB_IMPL_UMMA : RDB_IMPL_SIMT;
+}
+
+struct WsLayout {
+    size_t off[4];
+    size_t total;
+};
+
+// Workspace segments (each 1024-byte aligned):
+//   UMMA factored  fwd: z bf16[T,R]
+//                  bwd: g bf16[T,R] (+ gT bf16[R,T], xT bf16[K,T], cT bf16[K,R] when explicit transposes are on)
+//   SIMT factored  fwd: z f32[T,R]           bwd: g f32[T,R]
+//   SIMT W path    fwd: W f32[N,K]           bwd: W f32[N,K], dW f32[N,K]
+static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, int path, int impl) {
+    WsLayout w{};
+    size_t seg[4] = {0, 0, 0, 0};
+    if (path == RDB_PATH_FACTORED) {
+        if (impl == RDB_IMPL_UMMA) {
+            seg[0] = (size_t)T * R * 2;
+            if (op == 1 && g_bwd_operands == 1) {
+                seg[1] = (size_t)R * T * 2;
+                seg[2] = (size_t)K * T * 2;
+                seg[3] = (size_t)K * R * 2;
+            }
+        } else {
+            seg[0] = (size_t)T * R * 4;
+        }
+    } else {
+        seg[0] = (size_t)N * K * 4;
+        if (op == 1) seg[1] = (size_t)N * K * 4;
+    }
+    size_t o = 0;
+    for (int i = 0; i < 4; ++i) {
+        w.off[i] = o;
+        o += align_up(seg[i], 1024);
+    }
+    w.total = o;
+    return w;
+}
+
+}  // namespace rdb
+
+using namespace rdb;
+
+extern "C" int rdb_version(void) { return RDB_VERSION; }
+
+extern "C" const char *rdb_strerror(int code) {
+    switch (code) {
+        case RDB_OK: return "ok";
+        case RDB_ERR_NULL: return "null pointer argument";
+        case RDB_ERR_SHAPE: return "invalid shape or leading dimension";
+        case RDB_ERR_DTYPE: return "unsupported element type";
+        case RDB_ERR_ALIGN: return "pointer or leading dimension not aligned as required";
+        case RDB_ERR_WORKSPACE: return "workspace too small or misaligned";
+        case RDB_ERR_UNSUPPORTED: return "combination of options not supported for this problem";
+        case RDB_ERR_DRIVER: return "tensor-map encoding failed (driver entry point unavailable or rejected arguments)";
+        case RDB_ERR_TOO_LARGE: return "problem exceeds a launch limit";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown error";
+}
+
+extern "C" int rdb_set_option(int key, int value) {
+    int prev;
+    switch (key) {
+        case RDB_OPT_NOISE_TILE:
+            prev = g_noise_tile;
+            g_noise_tile = value ? 1 : 0;
+            set_noise_cfg(g_noise_tile);
+            return prev;
+        case RDB_OPT_BWD_OPERANDS:
+            prev = g_bwd_operands;
+            g_bwd_operands = value ? 1 : 0;
+            return prev;
+        default: return RDB_ERR_UNSUPPORTED;
+    }
+}
+
+extern "C" int rdb_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
+                              int64_t ldd_t, int a_dtype, int d_dtype, int transposed, int64_t row0, int64_t col0,
+                              uint32_t seed, int impl, int32_t *status, void *stream) {
+    if (M < 0 || N < 0 || Kc < 0 || lda < Kc || ldd < N) return RDB_ERR_SHAPE;
+    if (M == 0 || N == 0) return RDB_OK;
+    if (!d || (Kc > 0 && !a)) return RDB_ERR_NULL;
+    if ((a_dtype != RDB_F32 && a_dtype != RDB_BF16) || (d_dtype != RDB_F32 && d_dtype != RDB_BF16)) return RDB_ERR_DTYPE;
+    if (d_t && ldd_t < M) return RDB_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const Sq5Lin lin = transposed ? sq5_lin_cols(seed, (uint32_t)row0, (uint32_t)col0)
+                                  : sq5_lin_rows(seed, (uint32_t)row0, (uint32_t)col0);
+    const bool can = a_dtype == RDB_BF16 && d_dtype == RDB_BF16 && umma_shape_ok_noise(M, N, Kc, lda, ldd, a, d) &&
+                     (!d_t || ((ldd_t % 8) == 0));
+    if (impl == RDB_IMPL_UMMA && !can) return RDB_ERR_UNSUPPORTED;
+    if (impl != RDB_IMPL_SIMT && can) return umma_gemm_noise(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+    if (d_t) return RDB_ERR_UNSUPPORTED;
+    return simt_gemm(d, d_dtype, ldd, 1, a, a_dtype, lda, 1, nullptr, RDB_F32, 0, 0, lin, M, N, Kc, st);
+}
+
+extern "C" int rdb_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda,
+                              int64_t ldb, int64_t ldd, int a_dtype, int b_dtype, int d_dtype, int a_kmajor, int b_kmajor,
+                              int impl, int32_t *status, void *stream) {
+    if (M < 0 || N < 0 || Kc < 0 || ldd < N) return RDB_ERR_SHAPE;
+    if (lda < (a_kmajor ? Kc : M) || ldb < (b_kmajor ? Kc : N)) return RDB_ERR_SHAPE;
+    if (M == 0 || N == 0) return RDB_OK;
+    if (!d || (Kc > 0 && (!a || !b))) return RDB_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool can = a_dtype == RDB_BF16 && b_dtype == RDB_BF16 &&
+                     umma_shape_ok_dense(M, N, Kc, lda, ldb, ldd, d_dtype, a_kmajor, b_kmajor, a, b, d);
+    if (impl == RDB_IMPL_UMMA && !can) return RDB_ERR_UNSUPPORTED;
+    if (impl != RDB_IMPL_SIMT && can)
+        return umma_gemm_dense(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, a_kmajor, b_kmajor, status, st);
+    Sq5Lin none{0, 0, 0};
+    // SIMT needs a real B pointer; b == nullptr would select the generated operand.
+    return simt_gemm(d, d_dtype, ldd, 1, a, a_dtype, a_kmajor ? lda : 1, a_kmajor ? 1 : lda, b, b_dtype,
+                     b_kmajor ? ldb : 1, b_kmajor ? 1 : ldb, none, M, N, Kc, st);
+}
+
+extern "C" size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path,
+                                             int impl) {
+    if (T <= 0 || K <= 0 || N <= 0 || R <= 0) return 0;
+    const int p = choose_path(path, T, K, N, R);
+    const int im = choose_impl(impl, T, K, N, R, dtype, p);
+    if (im < 0) return 0;
+    return ws_layout(op, T, K, N, R, p, im).total;
+}
+
+static int check_common(int64_t T, int64_t K, int64_t N, int64_t R, int dtype) {
+    if (T < 0 || K < 0 || N < 0 || R < 0) return RDB_ERR_SHAPE;
+    if (dtype != RDB_F32 && dtype != RDB_BF16) return RDB_ERR_DTYPE;
+    return RDB_OK;
+}
+
+extern "C" int rdb_linear_fwd(void *y, const void *x, const void *coef, void *workspace, size_t workspace_bytes, int64_t T,
+                              int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed, int dtype, int path, int impl,
+                              int32_t *status, void *stream) {
+    int rc = check_common(T, K, N, R, dtype);
+    if (rc) return rc;
+    if (T == 0 || N == 0) return RDB_OK;
+    if (!y) return RDB_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (K == 0 || R == 0) {
+        cudaError_t e = cudaMemsetAsync(y, 0, (size_t)T * N * dtype_size(dtype), st);
+        return e == cudaSuccess ? RDB_OK : (int)e;
+    }
+    if (!x || !coef) return RDB_ERR_NULL;
+    const int p = choose_path(path, T, K, N, R);
+    const int im = choose_impl(impl, T, K, N, R, dtype, p);
+    if (im < 0) return im;
+    const WsLayout w = ws_layout(0, T, K, N, R, p, im);
+    if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return RDB_ERR_WORKSPACE;
+    uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
+    const Sq5Lin rows = sq5_lin_rows(seed, (uint32_t)row0, 0);
+    const Sq5Lin none{0, 0, 0};
+
+    if (p == RDB_PATH_FACTORED) {
+        if (im == RDB_IMPL_UMMA) {
+            void *z = ws + w.off[0];
+            rc = umma_gemm_dense(z, x, coef, T, R, K, K, K, R, RDB_BF16, 1, 1, status, st);
+            if (rc) return rc;
+            return umma_gemm_noise(y, nullptr, z, T, N, R, R, N, 0, rows, status, st);
+        }
+        if (dtype == RDB_F32 && T == 1)
+            return rdb_gemv_fwd((float *)y, (const float *)x, (const float *)coef, (float *)(ws + w.off[0]), K, N, R, row0,
+                                seed, stream);
+        float *z = reinterpret_cast<float *>(ws + w.off[0]);
+        rc = simt_gemm(z, RDB_F32, R, 1, x, dtype, K, 1, coef, dtype, K, 1, none, T, R, K, st);
+        if (rc) return rc;
+        return simt_gemm(y, dtype, N, 1, z, RDB_F32, R, 1, nullptr, RDB_F32, 0, 0, rows, T, N, R, st);
+    }
+    // W path: W[o,i] = sum_r S[row0+o, r] C[r,i], written as D(m=i, n=o) at o*K + i
+    float *W = reinterpret_cast<float *>(ws + w.off[0]);
+    rc = simt_gemm(W, RDB_F32, 1, K, coef, dtype, 1, K, nullptr, RDB_F32, 0, 0, rows, K, N, R, st);
+    if (rc) return rc;
+    return simt_gemm(y, dtype, N, 1, x, dtype, K, 1, W, RDB_F32, K, 1, none, T, N, K, st);
+}
+
+extern "C" int rdb_linear_bwd(void *dx, void *dc, const void *dy, const void *x, const void *coef, void *workspace,
+                              size_t workspace_bytes, int64_t T, int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed,
+                              int dtype, int path, int impl, int32_t *status, void *stream) {
+    int rc = check_common(T, K, N, R, dtype);
+    if (rc) return rc;
+    if (!dx && !dc) return RDB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t es = dtype_size(dtype);
+    if (T == 0 || N == 0 || R == 0 || K == 0) {
+        cudaError_t e = cudaSuccess;
+        if (dx && T > 0 && K > 0) e = cudaMemsetAsync(dx, 0, (size_t)T * K * es, st);
+        if (e == cudaSuccess && dc && R > 0 && K > 0) e = cudaMemsetAsync(dc, 0, (size_t)R * K * es, st);
+        return e == cudaSuccess ? RDB_OK : (int)e;
+    }
+    if (!dy || (dx && !coef) || (dc && !x)) return RDB_ERR_NULL;
+    const int p = choose_path(path, T, K, N, R);
+    const int im = choose_impl(impl, T, K, N, R, dtype, p);
+    if (im < 0) return im;
+    const WsLayout w = ws_layout(1, T, K, N, R, p, im);
+    if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return RDB_ERR_WORKSPACE;
+    uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
+    const Sq5Lin rows = sq5_lin_rows(seed, (uint32_t)row0, 0);
+    const Sq5Lin cols = sq5_lin_cols(seed, (uint32_t)row0, 0);
+    const Sq5Lin none{0, 0, 0};
+
+    if (p == RDB_PATH_FACTORED) {
+        if (im == RDB_IMPL_UMMA) {
+            void *g = ws + w.off[0];
+            if (g_bwd_operands == 0) {
+                // g = dY S ; dX = g C (C read as an MN-major B operand) ; dC = g^T x (both MN-major)
+                rc = umma_gemm_noise(g, nullptr, dy, T, R, N, N, R, 0, cols, status, st);
+                if (rc) return rc;
+                if (dx) {
+                    rc = umma_gemm_dense(dx, g, coef, T, K, R, R, K, K, RDB_BF16, 1, 0, status, st);
+                    if (rc) return rc;
+                }
+                if (dc) {
+                    rc = umma_gemm_dense(dc, g, x, R, K, T, R, K, K, RDB_BF16, 0, 0, status, st);
+                    if (rc) return rc;
+                }
+                return RDB_OK;
+            }
+            void *gT = ws + w.off[1], *xT = ws + w.off[2], *cT = ws + w.off[3];
+            rc = umma_gemm_noise(g, dc ? gT : nullptr, dy, T, R, N, N, R, T, cols, status, st);
+            if (rc) return rc;
+            if (dx) {
+                rc = transpose_bf16(cT, R, coef, K, R, K, st);
+                if (rc) return rc;
+                rc = umma_gemm_dense(dx, g, cT, T, K, R, R, R, K, RDB_BF16, 1, 1, status, st);
+                if (rc) return rc;
+            }
+            if (dc) {
+                rc = transpose_bf16(xT, T, x, K, T, K, st);
+                if (rc) return rc;
+                rc = umma_gemm_dense(dc, gT, xT, R, K, T, T, T, K, RDB_BF16, 1, 1, status, st);
+                if (rc) return rc;
+            }
+            return RDB_OK;
+        }
+        if (dtype == RDB_F32 && T == 1)
+            return rdb_gemv_bwd((float *)dx, (float *)dc, (const float *)dy, (const float *)x, (const float *)coef,
+                                (float *)(ws + w.off[0]), K, N, R, row0, seed, stream);
+        float *g = reinterpret_cast<float *>(ws + w.off[0]);
+        rc = simt_gemm(g, RDB_F32, R, 1, dy, dtype, N, 1, nullptr, RDB_F32, 0, 0, cols, T, R, N, st);
+        if (rc) return rc;
+        if (dx) {
+            rc = simt_gemm(dx, dtype, K, 1, g, RDB_F32, R, 1, coef, dtype, 1, K, none, T, K, R, st);
+            if (rc) return rc;
+        }
+        if (dc) {
+            rc = simt_gemm(dc, dtype, K, 1, g, RDB_F32, 1, R, x, dtype, 1, K, none, R, K, T, st);
+            if (rc) return rc;
+        }
+        return RDB_OK;
+    }
+    // W path
+    float *W = reinterpret_cast<float *>(ws + w.off[0]);
+    float *dW = reinterpret_cast<float *>(ws + w.off[1]);
+    if (dx) {
+        rc = simt_gemm(W, RDB_F32, 1, K, coef, dtype, 1, K, nullptr, RDB_F32, 0, 0, rows, K, N, R, st);
+        if (rc) return rc;
+        rc = simt_gemm(dx, dtype, K, 1, dy, dtype, N, 1, W, RDB_F32, 1, K, none, T, K, N, st);
+        if (rc) return rc;
+    }
+    if (dc) {
+        // dW[o,i] = sum_t dY[t,o] x[t,i] ; dC[r,i] = sum_o S[row0+o, r] dW[o,i], written as D(m=i, n=r) at r*K + i
+        rc = simt_gemm(dW, RDB_F32, K, 1, dy, dtype, 1, N, x, dtype, 1, K, none, N, K, T, st);
+        if (rc) return rc;
+        rc = simt_gemm(dc, dtype, 1, K, dW, RDB_F32, 1, K, nullptr, RDB_F32, 0, 0, cols, K, R, N, st);
+        if (rc) return rc;
+    }
+    return RDB_OK;
+}

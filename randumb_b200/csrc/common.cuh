@@ -1,0 +1,50 @@
+// Shared host/device helpers for the randumb_b200 kernels.
+#pragma once
+#include <cstdint>
+#include <cstddef>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+#include "../../include/randumb_b200.h"
+#include "sq5.cuh"
+
+namespace rdb {
+
+inline int launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? RDB_OK : static_cast<int>(e);
+}
+
+inline int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+inline size_t dtype_size(int dtype) { return dtype == RDB_BF16 ? 2 : 4; }
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- implemented in simt.cu ------------------------------------------------------------------
+// D(m,n) = sum_k A(m,k) * B(n,k); element (i,j) of an operand lives at base[i*rs + j*cs].
+// When b == nullptr the B operand is generated: B(n,k) = value(lin.base + n*lin.sn + k*lin.sk).
+int simt_gemm(void *d, int d_dtype, int64_t d_rs, int64_t d_cs, const void *a, int a_dtype, int64_t a_rs,
+              int64_t a_cs, const void *b, int b_dtype, int64_t b_rs, int64_t b_cs, Sq5Lin lin, int64_t M,
+              int64_t N, int64_t Kc, cudaStream_t stream);
+
+// ---- implemented in umma_gemm.cu -------------------------------------------------------------
+void set_noise_cfg(int v);
+bool umma_shape_ok_noise(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, const void *a, const void *d);
+int umma_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
+                    int64_t ldd_t, Sq5Lin lin, int32_t *status, cudaStream_t stream);
+bool umma_shape_ok_dense(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int d_dtype,
+                         int a_kmajor, int b_kmajor, const void *a, const void *b, const void *d);
+int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda,
+                    int64_t ldb, int64_t ldd, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status,
+                    cudaStream_t stream);
+
+}  // namespace rdb

@@ -1,0 +1,176 @@
+// Batch-1 float32 path:  y = S (C x)  and its backward, as matrix-vector kernels.
+//
+// One activation row makes every product a matrix-vector product, so the cost is reading C
+// (and writing dC) once: 128-bit loads, warp-shuffle reductions, the noise regenerated in
+// registers from (seed, row, k).  Same reference slot as the aten.mm override
+// (src/rten_cpp/RandumbTensor.py:942-946, 771-791) for a single input row.
+#include "common.cuh"
+
+namespace rdb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// z[r] = sum_i C[r,i] * x[i]; one block per coefficient row.
+__global__ void __launch_bounds__(256) gemv_cx_kernel(float *__restrict__ z, const float *__restrict__ C,
+                                                      const float *__restrict__ x, int64_t K) {
+    __shared__ float red[8];
+    const int64_t r = blockIdx.x;
+    const float *row = C + r * K;
+    float acc = 0.0f;
+    const bool vec = ((K & 3) == 0) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    if (vec) {
+        const float4 *row4 = reinterpret_cast<const float4 *>(row);
+        const float4 *x4 = reinterpret_cast<const float4 *>(x);
+        for (int64_t i = threadIdx.x; i < (K >> 2); i += 256) {
+            const float4 c = __ldg(row4 + i);
+            const float4 v = __ldg(x4 + i);
+            acc = fmaf(c.x, v.x, acc);
+            acc = fmaf(c.y, v.y, acc);
+            acc = fmaf(c.z, v.z, acc);
+            acc = fmaf(c.w, v.w, acc);
+        }
+    } else {
+        for (int64_t i = threadIdx.x; i < K; i += 256) acc = fmaf(row[i], x[i], acc);
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += red[w];
+        z[r] = s;
+    }
+}
+
+// y[o] = sum_k S[row0+o, k] * z[k]; one warp per output row, lanes stride over k.
+__global__ void __launch_bounds__(256) gemv_sz_kernel(float *__restrict__ y, const float *__restrict__ z, int64_t N,
+                                                      int64_t R, Sq5Lin lin) {
+    const int64_t o = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (o >= N) return;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rowb = lin.base + (uint32_t)o * lin.sn;
+    float acc = 0.0f;
+    for (int64_t k = lane; k < R; k += 32)
+        acc = fmaf(sq5_to_float(sq5_tail(rowb + (uint32_t)k * lin.sk)), __ldg(z + k), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) y[o] = acc;
+}
+
+// g[k] = sum_o dy[o] * S[row0+o, k]; one block per noise column k.
+__global__ void __launch_bounds__(256) gemv_stdy_kernel(float *__restrict__ g, const float *__restrict__ dy, int64_t N,
+                                                        Sq5Lin lin) {
+    __shared__ float red[8];
+    const uint32_t colb = lin.base + (uint32_t)blockIdx.x * lin.sk;
+    float acc = 0.0f;
+    for (int64_t o = threadIdx.x; o < N; o += 256)
+        acc = fmaf(sq5_to_float(sq5_tail(colb + (uint32_t)o * lin.sn)), __ldg(dy + o), acc);
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += red[w];
+        g[blockIdx.x] = s;
+    }
+}
+
+// dx[i] = sum_r g[r] * C[r,i]  and  dc[r,i] = g[r] * x[i], one pass over C.
+// A block owns 32 columns (8 lanes x float4 = one 128-byte line per row) and walks all rows
+// with 32 row slots; slot partials of dx are summed in a fixed order.
+__global__ void __launch_bounds__(256) gemv_dxdc_kernel(float *__restrict__ dx, float *__restrict__ dc,
+                                                        const float *__restrict__ g, const float *__restrict__ x,
+                                                        const float *__restrict__ C, int64_t K, int64_t R) {
+    __shared__ float part[32][33];
+    const int slot = threadIdx.x >> 3;  // 0..31
+    const int l8 = threadIdx.x & 7;     // 0..7
+    const int64_t c0 = (int64_t)blockIdx.x * 32 + l8 * 4;
+    float ax[4] = {0.f, 0.f, 0.f, 0.f};
+    float xv[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool vec = ((K & 3) == 0) && (c0 + 3 < K) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) &&
+                     (dc == nullptr || (reinterpret_cast<uintptr_t>(dc) & 15) == 0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (dc && c0 + j < K) xv[j] = x[c0 + j];
+    for (int64_t r = slot; r < R; r += 32) {
+        const float gr = __ldg(g + r);
+        if (vec) {
+            if (dx) {
+                const float4 c = __ldg(reinterpret_cast<const float4 *>(C + r * K + c0));
+                ax[0] = fmaf(gr, c.x, ax[0]);
+                ax[1] = fmaf(gr, c.y, ax[1]);
+                ax[2] = fmaf(gr, c.z, ax[2]);
+                ax[3] = fmaf(gr, c.w, ax[3]);
+            }
+            if (dc)
+                *reinterpret_cast<float4 *>(dc + r * K + c0) = make_float4(gr * xv[0], gr * xv[1], gr * xv[2], gr * xv[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (c0 + j < K) {
+                    if (dx) ax[j] = fmaf(gr, C[r * K + c0 + j], ax[j]);
+                    if (dc) dc[r * K + c0 + j] = gr * xv[j];
+                }
+            }
+        }
+    }
+    if (!dx) return;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) part[slot][l8 * 4 + j] = ax[j];
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float s = 0.0f;
+#pragma unroll
+        for (int sidx = 0; sidx < 32; ++sidx) s += part[sidx][threadIdx.x];
+        const int64_t c = (int64_t)blockIdx.x * 32 + threadIdx.x;
+        if (c < K) dx[c] = s;
+    }
+}
+
+}  // namespace rdb
+
+using namespace rdb;
+
+extern "C" int rdb_gemv_fwd(float *y, const float *x, const float *coef, float *workspace, int64_t K, int64_t N,
+                            int64_t R, int64_t row0, uint32_t seed, void *stream) {
+    if (K < 0 || N < 0 || R < 0) return RDB_ERR_SHAPE;
+    if (N == 0) return RDB_OK;
+    if (!y || (R > 0 && (!workspace || (K > 0 && (!x || !coef))))) return RDB_ERR_NULL;
+    if (R > 0x7fffffffLL || cdiv64(N, 8) > 0x7fffffffLL) return RDB_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (R > 0) {
+        gemv_cx_kernel<<<(unsigned)R, 256, 0, st>>>(workspace, coef, x, K);
+        int rc = launch_status();
+        if (rc) return rc;
+    }
+    gemv_sz_kernel<<<(unsigned)cdiv64(N, 8), 256, 0, st>>>(y, workspace, N, R, sq5_lin_rows(seed, (uint32_t)row0, 0));
+    return launch_status();
+}
+
+extern "C" int rdb_gemv_bwd(float *dx, float *dc, const float *dy, const float *x, const float *coef, float *workspace,
+                            int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed, void *stream) {
+    if (K < 0 || N < 0 || R < 0) return RDB_ERR_SHAPE;
+    if (!dx && !dc) return RDB_OK;
+    if (K == 0) return RDB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (R == 0) {
+        if (dx) {
+            cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)K * sizeof(float), st);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return RDB_OK;
+    }
+    if (!workspace || (N > 0 && !dy) || (dx && !coef) || (dc && !x)) return RDB_ERR_NULL;
+    if (R > 0x7fffffffLL || cdiv64(K, 32) > 0x7fffffffLL) return RDB_ERR_TOO_LARGE;
+    gemv_stdy_kernel<<<(unsigned)R, 256, 0, st>>>(workspace, dy, N, sq5_lin_rows(seed, (uint32_t)row0, 0));
+    int rc = launch_status();
+    if (rc) return rc;
+    gemv_dxdc_kernel<<<(unsigned)cdiv64(K, 32), 256, 0, st>>>(dx, dc, workspace, x, coef, K, R);
+    return launch_status();
+}

@@ -1,0 +1,222 @@
+// Explicit noise matrices and the reference's 1-D-coefficient materialise kernels (CUDA cores).
+//
+// Reference behaviour restated here (paths inside the reference project):
+//   explicit noise matrix      src/rten_cpp/RandumbTensor.py:78-105, csrc/cuda/rten.cu:50-71
+//   1-D noise                  src/rten_cpp/RandumbTensor.py:204-232
+//   materialise forward        src/rten_cpp/RandumbTensor.py:235-290, csrc/cuda/rten.cu:74-110
+//   materialise backward       src/rten_cpp/RandumbTensor.py:304-359 (atomics there; a fixed
+//                              two-pass reduction order here so results repeat run to run)
+#include "common.cuh"
+
+namespace rdb {
+
+// mode 0: uint32 words, 1: float32, 2: bf16
+template <int MODE>
+__global__ void noise_kernel(void *__restrict__ out, int64_t rows, int64_t cols, int64_t ld, Sq5Lin lin) {
+    const int64_t cgroups = (cols + 3) >> 2;
+    const int64_t total = rows * cgroups;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / cgroups;
+        const int64_t c0 = (idx - r * cgroups) << 2;
+        const uint32_t b0 = lin.base + (uint32_t)r * lin.sn + (uint32_t)c0 * lin.sk;
+        uint32_t bits[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bits[j] = sq5_tail(b0 + (uint32_t)j * lin.sk);
+        const int64_t off = r * ld + c0;
+        const int nvalid = (int)((cols - c0) < 4 ? (cols - c0) : 4);
+        if (MODE == 0) {
+            uint32_t *o = reinterpret_cast<uint32_t *>(out) + off;
+            if (nvalid == 4 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+                *reinterpret_cast<uint4 *>(o) = make_uint4(bits[0], bits[1], bits[2], bits[3]);
+            } else {
+                for (int j = 0; j < nvalid; ++j) o[j] = bits[j];
+            }
+        } else if (MODE == 1) {
+            float *o = reinterpret_cast<float *>(out) + off;
+            float f[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[j] = sq5_to_float(bits[j]);
+            if (nvalid == 4 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+                *reinterpret_cast<float4 *>(o) = make_float4(f[0], f[1], f[2], f[3]);
+            } else {
+                for (int j = 0; j < nvalid; ++j) o[j] = f[j];
+            }
+        } else {
+            __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(out) + off;
+            __nv_bfloat16 h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __float2bfloat16_rn(sq5_to_float(bits[j]));
+            if (nvalid == 4 && ((reinterpret_cast<uintptr_t>(o) & 7) == 0)) {
+                uint2 v;
+                v.x = (uint32_t)__bfloat16_as_ushort(h[0]) | ((uint32_t)__bfloat16_as_ushort(h[1]) << 16);
+                v.y = (uint32_t)__bfloat16_as_ushort(h[2]) | ((uint32_t)__bfloat16_as_ushort(h[3]) << 16);
+                *reinterpret_cast<uint2 *>(o) = v;
+            } else {
+                for (int j = 0; j < nvalid; ++j) o[j] = h[j];
+            }
+        }
+    }
+}
+
+__global__ void noise_1d_kernel(float *__restrict__ out, int64_t n, uint32_t idx0, uint32_t seed) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = sq5_to_float(sq5_tail((idx0 + (uint32_t)i) * SQ5_N1 + seed));
+}
+
+static int grid_for(int64_t work_items, int block) {
+    int64_t g = cdiv64(work_items, block);
+    const int64_t cap = 148 * 16;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+template <int MODE>
+static int launch_noise(void *out, int64_t rows, int64_t cols, int64_t ld, int64_t row0, int64_t col0, uint32_t seed,
+                        cudaStream_t st) {
+    if (rows == 0 || cols == 0) return RDB_OK;
+    Sq5Lin lin = sq5_lin_rows(seed, (uint32_t)row0, (uint32_t)col0);
+    const int64_t items = rows * ((cols + 3) >> 2);
+    noise_kernel<MODE><<<grid_for(items, 256), 256, 0, st>>>(out, rows, cols, ld, lin);
+    return launch_status();
+}
+
+// ---- materialise forward (1-D coefficient vector) ---------------------------------------------
+constexpr int MAT_CHUNK = 1024;
+
+__global__ void materialize_fwd_kernel(float *__restrict__ out, const float *__restrict__ coef, int64_t M, int64_t Nel,
+                                       int64_t Q, int64_t stride_P, int64_t stride_Q, uint32_t seed) {
+    __shared__ float coef_s[MAT_CHUNK];
+    const int64_t n = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    const bool live = n < Nel;
+    uint32_t rowpos = 0;
+    if (live) {
+        const int64_t sq = (n % Q) * stride_Q + (n / Q) * stride_P;
+        rowpos = ((uint32_t)sq * SQ5_PRIME) * SQ5_N1 + seed;
+    }
+    float acc = 0.0f;
+    for (int64_t m0 = 0; m0 < M; m0 += MAT_CHUNK) {
+        const int len = (int)((M - m0) < MAT_CHUNK ? (M - m0) : MAT_CHUNK);
+        __syncthreads();
+        for (int i = threadIdx.x; i < len; i += blockDim.x) coef_s[i] = coef[m0 + i];
+        __syncthreads();
+        if (live) {
+            uint32_t b0 = rowpos + (uint32_t)m0 * SQ5_N1;
+            for (int m = 0; m < len; ++m) {
+                acc = fmaf(sq5_to_float(sq5_tail(b0)), coef_s[m], acc);
+                b0 += SQ5_N1;
+            }
+        }
+    }
+    if (live) out[n] = acc;
+}
+
+// ---- materialise backward: partial[split][m] then ordered sum over splits ----------------------
+constexpr int BWD_MB = 8;       // coefficient columns per block
+constexpr int BWD_THREADS = 256;
+constexpr int64_t BWD_SPAN = 8192;  // dout elements per split
+
+__global__ void materialize_bwd_partial_kernel(float *__restrict__ partial, const float *__restrict__ dout, int64_t Nel,
+                                               int64_t M, uint32_t seed) {
+    __shared__ float red[BWD_MB][BWD_THREADS];
+    const int64_t m0 = (int64_t)blockIdx.x * BWD_MB;
+    const int64_t split = blockIdx.y;
+    const int64_t n_lo = split * BWD_SPAN;
+    const int64_t n_hi = (n_lo + BWD_SPAN) < Nel ? (n_lo + BWD_SPAN) : Nel;
+    float acc[BWD_MB];
+#pragma unroll
+    for (int j = 0; j < BWD_MB; ++j) acc[j] = 0.0f;
+    for (int64_t n = n_lo + threadIdx.x; n < n_hi; n += BWD_THREADS) {
+        const float d = dout[n];
+        const uint32_t b0 = ((uint32_t)n * SQ5_PRIME + (uint32_t)m0) * SQ5_N1 + seed;
+#pragma unroll
+        for (int j = 0; j < BWD_MB; ++j) acc[j] = fmaf(sq5_to_float(sq5_tail(b0 + (uint32_t)j * SQ5_N1)), d, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < BWD_MB; ++j) red[j][threadIdx.x] = acc[j];
+    __syncthreads();
+    for (int s = BWD_THREADS / 2; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) {
+#pragma unroll
+            for (int j = 0; j < BWD_MB; ++j) red[j][threadIdx.x] += red[j][threadIdx.x + s];
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x < BWD_MB && m0 + threadIdx.x < M) partial[split * M + m0 + threadIdx.x] = red[threadIdx.x][0];
+}
+
+__global__ void materialize_bwd_final_kernel(float *__restrict__ dcoef, const float *__restrict__ partial, int64_t M,
+                                             int64_t nsplit) {
+    const int64_t m = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    float acc = 0.0f;
+    for (int64_t s = 0; s < nsplit; ++s) acc += partial[s * M + m];
+    dcoef[m] = acc;
+}
+
+}  // namespace rdb
+
+using namespace rdb;
+
+extern "C" int rdb_noise_bits(uint32_t *out, int64_t rows, int64_t cols, int64_t ld, int64_t row0, int64_t col0,
+                              uint32_t seed, void *stream) {
+    if (rows < 0 || cols < 0 || ld < cols) return RDB_ERR_SHAPE;
+    if (rows > 0 && cols > 0 && !out) return RDB_ERR_NULL;
+    return launch_noise<0>(out, rows, cols, ld, row0, col0, seed, (cudaStream_t)stream);
+}
+
+extern "C" int rdb_noise(void *out, int dtype, int64_t rows, int64_t cols, int64_t ld, int64_t row0, int64_t col0,
+                         uint32_t seed, void *stream) {
+    if (rows < 0 || cols < 0 || ld < cols) return RDB_ERR_SHAPE;
+    if (rows > 0 && cols > 0 && !out) return RDB_ERR_NULL;
+    if (dtype == RDB_F32) return launch_noise<1>(out, rows, cols, ld, row0, col0, seed, (cudaStream_t)stream);
+    if (dtype == RDB_BF16) return launch_noise<2>(out, rows, cols, ld, row0, col0, seed, (cudaStream_t)stream);
+    return RDB_ERR_DTYPE;
+}
+
+extern "C" int rdb_noise_1d(float *out, int64_t n, int64_t idx0, uint32_t seed, void *stream) {
+    if (n < 0) return RDB_ERR_SHAPE;
+    if (n == 0) return RDB_OK;
+    if (!out) return RDB_ERR_NULL;
+    noise_1d_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(out, n, (uint32_t)idx0, seed);
+    return launch_status();
+}
+
+extern "C" int rdb_materialize_fwd(float *out, const float *coef, int64_t M, int64_t P, int64_t Q, int64_t stride_P,
+                                   int64_t stride_Q, uint32_t seed, void *stream) {
+    if (M < 0 || P < 0 || Q < 0) return RDB_ERR_SHAPE;
+    const int64_t Nel = P * Q;
+    if (Nel == 0) return RDB_OK;
+    if (!out || (M > 0 && !coef)) return RDB_ERR_NULL;
+    if (cdiv64(Nel, 128) > 0x7fffffffLL) return RDB_ERR_TOO_LARGE;
+    materialize_fwd_kernel<<<(unsigned)cdiv64(Nel, 128), 128, 0, (cudaStream_t)stream>>>(out, coef, M, Nel, Q, stride_P,
+                                                                                       stride_Q, seed);
+    return launch_status();
+}
+
+extern "C" size_t rdb_materialize_bwd_workspace_bytes(int64_t Nel, int64_t M) {
+    if (Nel <= 0 || M <= 0) return 0;
+    return (size_t)cdiv64(Nel, BWD_SPAN) * (size_t)M * sizeof(float);
+}
+
+extern "C" int rdb_materialize_bwd(float *dcoef, const float *dout, float *workspace, int64_t Nel, int64_t M,
+                                   uint32_t seed, void *stream) {
+    if (Nel < 0 || M < 0) return RDB_ERR_SHAPE;
+    if (M == 0) return RDB_OK;
+    if (!dcoef) return RDB_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (Nel == 0) {
+        cudaError_t e = cudaMemsetAsync(dcoef, 0, (size_t)M * sizeof(float), st);
+        return e == cudaSuccess ? RDB_OK : (int)e;
+    }
+    if (!dout || !workspace) return RDB_ERR_NULL;
+    const int64_t nsplit = cdiv64(Nel, BWD_SPAN);
+    if (nsplit > 65535) return RDB_ERR_TOO_LARGE;
+    dim3 grid((unsigned)cdiv64(M, BWD_MB), (unsigned)nsplit);
+    materialize_bwd_partial_kernel<<<grid, BWD_THREADS, 0, st>>>(workspace, dout, Nel, M, seed);
+    int rc = launch_status();
+    if (rc) return rc;
+    materialize_bwd_final_kernel<<<(unsigned)cdiv64(M, 128), 128, 0, st>>>(dcoef, workspace, M, nsplit);
+    return launch_status();
+}

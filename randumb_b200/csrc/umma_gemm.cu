@@ -1,0 +1,601 @@
+// bf16 tensor-core (tcgen05 / TMEM / TMA) kernels of the pseudorandom-weight layer.
+//
+// Two persistent, warp-specialised kernels, one CTA per SM:
+//
+//  noise_gemm_kernel   D[M,N] = A[M,Kc] * G^T  where the B operand G is never read from memory:
+//                      generator warps hash (seed, row, k) with 32-bit integer ALU ops in
+//                      registers, convert to bf16 and write the tile straight into shared
+//                      memory in the 128-byte-swizzled K-major layout the MMA descriptor
+//                      expects, while a TMA warp stages the A tiles beside it.  One generated
+//                      [BN x 64] stage is consumed by MT token sub-tiles (MT*128 rows of A), so
+//                      every hash is amortised over MT*128 tokens.
+//                      Serves y = z S^T (forward) and g = dY S (backward, transposed walk).
+//
+//  dense_gemm_kernel   D[M,N] = op(A) op(B)^T with both operands staged by TMA (K-major or
+//                      MN-major), double-buffered TMEM accumulators so the epilogue of one tile
+//                      overlaps the main loop of the next.  Serves z = x C^T, dX = g C, dC = g^T x.
+//
+// The reference has no tensor-core path for any of this: its fused attempt runs tl.dot in IEEE
+// float32 (src/rten_cpp/RandumbTensor.py:539, 725) and the production path materialises W and
+// calls cuBLAS (:780, :786-787).
+//
+// Every barrier wait is bounded (ptx::mbar_wait); a role that gives up raises the CTA's abort
+// flag, writes a code to status[0] and all roles fall through to the common teardown, which
+// releases TMEM.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace rdb {
+
+using namespace ptx;
+
+constexpr int BM = 128;            // rows of one MMA (TMEM lanes)
+constexpr int BK = 64;             // bf16 elements per 128-byte swizzle row
+constexpr int UMMA_K = 16;         // K extent of one tcgen05.mma for 16-bit inputs
+constexpr int SUB_BYTES = BM * BK * 2;  // one [128 x 64] bf16 sub-tile
+constexpr int TMEM_COLS = 512;
+
+// ------------------------------------------------------------------------------------------------
+// epilogue helpers: one thread owns one accumulator row, 32 consecutive columns in registers
+// ------------------------------------------------------------------------------------------------
+template <typename OutT>
+__device__ __forceinline__ void store_row32(OutT *dst, const uint32_t (&r)[32], int ncols);
+
+template <>
+__device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16 *dst, const uint32_t (&r)[32], int ncols) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        if (v * 8 < ncols) {
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                p[j] = *reinterpret_cast<uint32_t *>(&h);
+            }
+            *reinterpret_cast<uint4 *>(dst + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+        }
+    }
+}
+
+template <>
+__device__ __forceinline__ void store_row32<float>(float *dst, const uint32_t (&r)[32], int ncols) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+        if (v * 4 < ncols)
+            *reinterpret_cast<uint4 *>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+    }
+}
+
+struct PipeState {
+    uint32_t idx = 0, phase = 0;
+    template <int STAGES> __device__ __forceinline__ void advance() {
+        if (++idx == STAGES) { idx = 0; phase ^= 1; }
+    }
+};
+
+__device__ __forceinline__ void raise_abort(volatile int *abort_flag, int32_t *status, int code) {
+    *abort_flag = 1;
+    if (status) atomicCAS(status, 0, code);
+}
+
+// ================================================================================================
+// noise_gemm_kernel
+// ================================================================================================
+template <int MT, int BN, int SA, int SB>
+struct NoiseCfg {
+    static constexpr int A_STAGE = MT * SUB_BYTES;
+    static constexpr int B_STAGE = BN * BK * 2;
+    static constexpr int GEN_WARPS = 8;
+    static constexpr int GEN_THREADS = GEN_WARPS * 32;
+    static constexpr int THREADS = (2 + 4 + GEN_WARPS) * 32;
+    static constexpr int FIRST_EPI_WARP = 2;
+    static constexpr int FIRST_GEN_WARP = 6;
+    static constexpr int SMEM_DYN = SA * A_STAGE + SB * B_STAGE + 1024;
+    static_assert(MT * BN <= TMEM_COLS, "accumulators exceed TMEM");
+    static_assert(BN % 32 == 0 && BN <= 256, "BN");
+    static_assert((BN * 8) % GEN_THREADS == 0, "generator chunking");
+};
+
+template <int MT, int BN, int SA, int SB>
+__global__ void __launch_bounds__(NoiseCfg<MT, BN, SA, SB>::THREADS, 1)
+noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__restrict__ d, int64_t ldd,
+                  __nv_bfloat16 *__restrict__ d_t, int64_t ldd_t, int64_t M, int64_t N, int64_t Kc, Sq5Lin lin,
+                  int32_t *status) {
+    using Cfg = NoiseCfg<MT, BN, SA, SB>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full_a[SA], bar_empty_a[SA], bar_full_b[SB], bar_empty_b[SB], bar_tmem_full, bar_tmem_empty;
+    __shared__ uint32_t tmem_holder;
+    __shared__ int abort_flag;
+
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+    uint8_t *smem = smem_raw + pad;
+    const uint32_t smem_a = raw_addr + pad;
+    const uint32_t smem_b = smem_a + SA * Cfg::A_STAGE;
+    uint8_t *smem_b_gen = smem + SA * Cfg::A_STAGE;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SA; ++s) { mbar_init(smem_u32(&bar_full_a[s]), 1); mbar_init(smem_u32(&bar_empty_a[s]), 1); }
+        for (int s = 0; s < SB; ++s) { mbar_init(smem_u32(&bar_full_b[s]), Cfg::GEN_THREADS); mbar_init(smem_u32(&bar_empty_b[s]), 1); }
+        mbar_init(smem_u32(&bar_tmem_full), 1);
+        mbar_init(smem_u32(&bar_tmem_empty), 128);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_holder), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+    volatile int *abortp = &abort_flag;
+
+    const int64_t tiles_n = (N + BN - 1) / BN;
+    const int64_t tiles_m = (M + (int64_t)MT * BM - 1) / ((int64_t)MT * BM);
+    const int64_t total_tiles = tiles_m * tiles_n;
+    const int num_kb = (int)((Kc + BK - 1) / BK);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (A tiles)
+        if (lane == 0) {
+            prefetch_tmap(&tmap_a);
+            PipeState st;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int64_t m0 = (tile / tiles_n) * (int64_t)MT * BM;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_empty_a[st.idx]), st.phase ^ 1, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = smem_u32(&bar_full_a[st.idx]);
+                    mbar_arrive_expect_tx(fb, Cfg::A_STAGE);
+#pragma unroll
+                    for (int s = 0; s < MT; ++s)
+                        tma_load_2d(smem_a + st.idx * Cfg::A_STAGE + s * SUB_BYTES, &tmap_a, fb, kb * BK,
+                                    (int32_t)(m0 + s * BM));
+                    st.advance<SA>();
+                }
+            }
+            // Loads still in flight complete on their own barriers; wait for them (bounded) so the
+            // CTA does not retire with copies targeting its shared memory.
+            if (!ok) {
+                for (int s = 0; s < SA; ++s) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&bar_full_a[s]), 0) && !mbar_try_wait(smem_u32(&bar_full_a[s]), 1)) {
+                        if (clock64() - t0 > 20000000LL) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(BM, BN, 0, 0);
+            PipeState sa, sb;
+            uint32_t tphase = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(smem_u32(&bar_tmem_empty), tphase ^ 1, abortp)) {
+                    raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
+                    break;
+                }
+                tc_fence_after_sync();
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_full_a[sa.idx]), sa.phase, abortp) ||
+                        !mbar_wait(smem_u32(&bar_full_b[sb.idx]), sb.phase, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_stage = smem_a + sa.idx * Cfg::A_STAGE;
+                    const uint32_t b_stage = smem_b + sb.idx * Cfg::B_STAGE;
+#pragma unroll
+                    for (int s = 0; s < MT; ++s) {
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t adesc = smem_desc_sw128(a_stage + s * SUB_BYTES + k * UMMA_K * 2, 0, 1024);
+                            const uint64_t bdesc = smem_desc_sw128(b_stage + k * UMMA_K * 2, 0, 1024);
+                            umma_bf16(tmem_base + s * BN, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(smem_u32(&bar_empty_a[sa.idx]));
+                    umma_commit(smem_u32(&bar_empty_b[sb.idx]));
+                    sa.advance<SA>();
+                    sb.advance<SB>();
+                }
+                if (ok) umma_commit(smem_u32(&bar_tmem_full));
+                tphase ^= 1;
+            }
+        }
+    } else if (warp < Cfg::FIRST_GEN_WARP) {
+        // ------------------------------------------------------------------ epilogue (4 warps)
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint32_t tphase = 0;
+        for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int64_t m0 = (tile / tiles_n) * (int64_t)MT * BM;
+            const int64_t n0 = (tile % tiles_n) * BN;
+            if (!mbar_wait(smem_u32(&bar_tmem_full), tphase, abortp)) {
+                raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
+                break;
+            }
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int s = 0; s < MT; ++s) {
+                const int64_t row = m0 + s * BM + q * 32 + lane;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * BN + c0), r);
+                    tmem_ld_wait();
+                    const int64_t col = n0 + c0;
+                    const int ncols = (int)((N - col) < 32 ? (N - col) : 32);
+                    if (row < M && ncols > 0) {
+                        store_row32<__nv_bfloat16>(d + row * ldd + col, r, ncols);
+                        if (d_t) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < ncols) d_t[(col + j) * ldd_t + row] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bar_tmem_empty));
+            tphase ^= 1;
+        }
+    } else {
+        // ------------------------------------------------------------------ generators (8 warps)
+        const int tg = threadIdx.x - Cfg::FIRST_GEN_WARP * 32;
+        constexpr int CHUNKS = (BN * 8) / Cfg::GEN_THREADS;  // 16-byte chunks per thread per stage
+        PipeState sb;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int64_t n0 = (tile % tiles_n) * BN;
+            // b0 of this thread's chunks at k-block 0
+            uint32_t bstart[CHUNKS];
+            uint32_t soff[CHUNKS];
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+                const int id = tg + c * Cfg::GEN_THREADS;
+                const int rowi = id >> 3, ch = id & 7;
+                bstart[c] = lin.base + (uint32_t)(n0 + rowi) * lin.sn + (uint32_t)(ch * 8) * lin.sk;
+                soff[c] = (uint32_t)(rowi * 128 + ((ch ^ (rowi & 7)) << 4));
+            }
+            const uint32_t kb_step = (uint32_t)BK * lin.sk;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait(smem_u32(&bar_empty_b[sb.idx]), sb.phase ^ 1, abortp)) {
+                    raise_abort(abortp, status, RDB_STATUS_TIMEOUT_GENERATOR);
+                    ok = false;
+                    break;
+                }
+                uint8_t *stage = smem_b_gen + sb.idx * Cfg::B_STAGE;
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c) {
+                    uint32_t p[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float f0 = sq5_to_float(sq5_tail(bstart[c] + (uint32_t)(2 * j) * lin.sk));
+                        const float f1 = sq5_to_float(sq5_tail(bstart[c] + (uint32_t)(2 * j + 1) * lin.sk));
+                        __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                        p[j] = *reinterpret_cast<uint32_t *>(&h);
+                    }
+                    *reinterpret_cast<uint4 *>(stage + soff[c]) = make_uint4(p[0], p[1], p[2], p[3]);
+                    bstart[c] += kb_step;
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&bar_full_b[sb.idx]));
+                sb.advance<SB>();
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ================================================================================================
+// dense_gemm_kernel
+// ================================================================================================
+template <int BN, int STAGES>
+struct DenseCfg {
+    static constexpr int A_STAGE = SUB_BYTES;
+    static constexpr int B_STAGE = BN * BK * 2;
+    static constexpr int STAGE = A_STAGE + B_STAGE;
+    static constexpr int THREADS = 6 * 32;
+    static constexpr int SMEM_DYN = STAGES * STAGE + 1024;
+    static_assert(2 * BN <= TMEM_COLS, "two accumulator stages must fit TMEM");
+    static_assert(BN % 64 == 0 && BN <= 256, "BN");
+};
+
+template <int BN, int STAGES, int A_MN, int B_MN, typename OutT>
+__global__ void __launch_bounds__(DenseCfg<BN, STAGES>::THREADS, 1)
+dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  OutT *__restrict__ d, int64_t ldd, int64_t M, int64_t N, int64_t Kc, int32_t *status) {
+    using Cfg = DenseCfg<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tmem_full[2], bar_tmem_empty[2];
+    __shared__ uint32_t tmem_holder;
+    __shared__ int abort_flag;
+
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tmem_full[s]), 1); mbar_init(smem_u32(&bar_tmem_empty[s]), 128); }
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_holder), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+    volatile int *abortp = &abort_flag;
+
+    const int64_t tiles_n = (N + BN - 1) / BN;
+    const int64_t tiles_m = (M + BM - 1) / BM;
+    const int64_t total_tiles = tiles_m * tiles_n;
+    const int num_kb = (int)((Kc + BK - 1) / BK);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            prefetch_tmap(&tmap_a);
+            prefetch_tmap(&tmap_b);
+            PipeState st;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int32_t m0 = (int32_t)((tile / tiles_n) * BM);
+                const int32_t n0 = (int32_t)((tile % tiles_n) * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_empty[st.idx]), st.phase ^ 1, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = smem_u32(&bar_full[st.idx]);
+                    mbar_arrive_expect_tx(fb, Cfg::STAGE);
+                    const uint32_t sa = smem_base + st.idx * Cfg::STAGE;
+                    const uint32_t sbm = sa + Cfg::A_STAGE;
+                    if (A_MN) {
+                        // operand stored [Kc, M]: two boxes of 64 (M, contiguous) x 64 (K rows)
+#pragma unroll
+                        for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (64 * BK * 2), &tmap_a, fb, m0 + i * 64, kb * BK);
+                    } else {
+                        tma_load_2d(sa, &tmap_a, fb, kb * BK, m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int i = 0; i < BN / 64; ++i) tma_load_2d(sbm + i * (64 * BK * 2), &tmap_b, fb, n0 + i * 64, kb * BK);
+                    } else {
+                        tma_load_2d(sbm, &tmap_b, fb, kb * BK, n0);
+                    }
+                    st.advance<STAGES>();
+                }
+            }
+            if (!ok) {
+                for (int s = 0; s < STAGES; ++s) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&bar_full[s]), 0) && !mbar_try_wait(smem_u32(&bar_full[s]), 1)) {
+                        if (clock64() - t0 > 20000000LL) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(BM, BN, A_MN, B_MN);
+            // K-major: 8-row groups 1024 B apart, k-step = 32 B inside the swizzle row.
+            // MN-major: 64-element column blocks 8192 B apart (LBO), 8-k groups 1024 B apart (SBO),
+            //           k-step of 16 = two groups = 2048 B.
+            constexpr uint32_t A_LBO = A_MN ? 64 * BK * 2 : 0, A_KSTEP = A_MN ? 2048 : UMMA_K * 2;
+            constexpr uint32_t B_LBO = B_MN ? 64 * BK * 2 : 0, B_KSTEP = B_MN ? 2048 : UMMA_K * 2;
+            PipeState st;
+            uint32_t acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1, abortp)) {
+                    raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t tacc = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_full[st.idx]), st.phase, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_base + st.idx * Cfg::STAGE;
+                    const uint32_t sbm = sa + Cfg::A_STAGE;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t adesc = smem_desc_sw128(sa + k * A_KSTEP, A_LBO, 1024);
+                        const uint64_t bdesc = smem_desc_sw128(sbm + k * B_KSTEP, B_LBO, 1024);
+                        umma_bf16(tacc, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&bar_empty[st.idx]));
+                    st.advance<STAGES>();
+                }
+                if (ok) umma_commit(smem_u32(&bar_tmem_full[acc]));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        uint32_t acc = 0, acc_phase = 0;
+        for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int64_t m0 = (tile / tiles_n) * BM;
+            const int64_t n0 = (tile % tiles_n) * BN;
+            if (!mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, abortp)) {
+                raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
+                break;
+            }
+            tc_fence_after_sync();
+            const int64_t row = m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                tmem_ld_wait();
+                const int64_t col = n0 + c0;
+                const int ncols = (int)((N - col) < 32 ? (N - col) : 32);
+                if (row < M && ncols > 0) store_row32<OutT>(d + row * ldd + col, r, ncols);
+            }
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ================================================================================================
+// host side
+// ================================================================================================
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return (EncodeTiledFn) nullptr;
+        if (q != cudaDriverEntryPointSuccess) return (EncodeTiledFn) nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// bf16 matrix with `inner` contiguous elements per row, `outer` rows, row pitch ld elements.
+static int make_tmap(CUtensorMap *m, const void *base, int64_t inner, int64_t outer, int64_t ld, uint32_t box_inner,
+                     uint32_t box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return RDB_ERR_DRIVER;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? RDB_OK : RDB_ERR_DRIVER;
+}
+
+static int sm_count() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    return n;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool umma_shape_ok_noise(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, const void *a, const void *d) {
+    return M >= 1 && N >= 8 && Kc >= 8 && (N % 8) == 0 && (Kc % 8) == 0 && (lda % 8) == 0 && (ldd % 8) == 0 &&
+           aligned16(a) && aligned16(d) && M < (1LL << 31) && N < (1LL << 31) && Kc < (1LL << 31);
+}
+
+template <int MT, int BN, int SA, int SB>
+static int launch_noise_gemm(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
+                             int64_t ldd_t, Sq5Lin lin, int32_t *status, cudaStream_t st) {
+    using Cfg = NoiseCfg<MT, BN, SA, SB>;
+    CUtensorMap ta;
+    int rc = make_tmap(&ta, a, Kc, M, lda, BK, BM);
+    if (rc) return rc;
+    auto kern = noise_gemm_kernel<MT, BN, SA, SB>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
+    if (e != cudaSuccess) return (int)e;
+    const int64_t tiles = cdiv64(M, (int64_t)MT * BM) * cdiv64(N, BN);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, reinterpret_cast<__nv_bfloat16 *>(d), ldd,
+                                                    reinterpret_cast<__nv_bfloat16 *>(d_t), ldd_t, M, N, Kc, lin, status);
+    return launch_status();
+}
+
+static int g_noise_cfg = 0;  // 0 = 4 sub-tiles x 128 columns, 1 = 2 sub-tiles x 256 columns
+void set_noise_cfg(int v) { g_noise_cfg = v; }
+
+int umma_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
+                    int64_t ldd_t, Sq5Lin lin, int32_t *status, cudaStream_t st) {
+    if (M == 0 || N == 0) return RDB_OK;
+    if (g_noise_cfg == 1) return launch_noise_gemm<2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+    return launch_noise_gemm<4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+}
+
+bool umma_shape_ok_dense(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int d_dtype,
+                         int a_kmajor, int b_kmajor, const void *a, const void *b, const void *d) {
+    (void)d_dtype;
+    // An MN-major operand has its M (or N) extent as the contiguous TMA dimension.
+    if (!a_kmajor && (M % 8) != 0) return false;
+    if (!b_kmajor && (N % 8) != 0) return false;
+    return M >= 1 && N >= 8 && Kc >= 8 && (N % 8) == 0 && (Kc % 8) == 0 && (lda % 8) == 0 &&
+           (ldb % 8) == 0 && (ldd % 8) == 0 && aligned16(a) && aligned16(b) && aligned16(d) && M < (1LL << 31) &&
+           N < (1LL << 31) && Kc < (1LL << 31);
+}
+
+template <int BN, int STAGES, int A_MN, int B_MN, typename OutT>
+static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
+                        int64_t ldd, int32_t *status, cudaStream_t st) {
+    using Cfg = DenseCfg<BN, STAGES>;
+    CUtensorMap ta, tb;
+    int rc = A_MN ? make_tmap(&ta, a, M, Kc, lda, 64, BK) : make_tmap(&ta, a, Kc, M, lda, BK, BM);
+    if (rc) return rc;
+    rc = B_MN ? make_tmap(&tb, b, N, Kc, ldb, 64, BK) : make_tmap(&tb, b, Kc, N, ldb, BK, BN);
+    if (rc) return rc;
+    auto kern = dense_gemm_kernel<BN, STAGES, A_MN, B_MN, OutT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
+    if (e != cudaSuccess) return (int)e;
+    const int64_t tiles = cdiv64(M, BM) * cdiv64(N, BN);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, tb, reinterpret_cast<OutT *>(d), ldd, M, N, Kc, status);
+    return launch_status();
+}
+
+template <int A_MN, int B_MN>
+static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
+                        int64_t ldd, int d_dtype, int32_t *status, cudaStream_t st) {
+    if (d_dtype == RDB_BF16)
+        return launch_dense<256, 4, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
+    if (d_dtype == RDB_F32) return launch_dense<256, 4, A_MN, B_MN, float>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
+    return RDB_ERR_DTYPE;
+}
+
+int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
+                    int64_t ldd, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status, cudaStream_t st) {
+    if (M == 0 || N == 0) return RDB_OK;
+    if (a_kmajor && b_kmajor) return dense_by_out<0, 0>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st);
+    if (a_kmajor && !b_kmajor) return dense_by_out<0, 1>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st);
+    if (!a_kmajor && b_kmajor) return dense_by_out<1, 0>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st);
+    return dense_by_out<1, 1>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st);
+}
+
+}  // namespace rdb

@@ -1,0 +1,263 @@
+"""Tensor-level wrappers over the C ABI: torch supplies device memory and the current stream,
+every number is produced by the library's own CUDA kernels.
+
+All functions require CUDA tensors and raise ``RuntimeError`` otherwise -- there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import (BF16, F32, IMPL_AUTO, IMPL_SIMT, IMPL_UMMA, PATH_AUTO, PATH_FACTORED, PATH_WPATH)  # noqa: F401
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+_status_bufs: dict[int, torch.Tensor] = {}
+
+
+def _dt(t: torch.dtype) -> int:
+    try:
+        return _DT[t]
+    except KeyError:
+        raise RuntimeError(f"randumb_b200 supports float32 and bfloat16, got {t}") from None
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("randumb_b200 kernels run on CUDA tensors only (no CPU implementation)")
+        if dev is not None and t.device != dev:
+            raise RuntimeError("all tensors must live on the same device")
+        dev = t.device
+    return dev
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _seed(seed: int) -> int:
+    return int(seed) & 0xFFFFFFFF
+
+
+def status_buffer(dev: torch.device) -> torch.Tensor:
+    """Per-device int32[4] word the kernels write to when a bounded wait expires."""
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    buf = _status_bufs.get(idx)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_bufs[idx] = buf
+    return buf
+
+
+def check_status(dev: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel launched so far gave up on a barrier wait."""
+    devs = [dev.index if dev is not None and dev.index is not None else torch.cuda.current_device()] if dev is not None \
+        else list(_status_bufs.keys())
+    for idx in devs:
+        buf = _status_bufs.get(idx)
+        if buf is None:
+            continue
+        code = int(buf[0].item())
+        if code != 0:
+            buf.zero_()
+            raise RuntimeError(f"randumb_b200 kernel gave up: {_lib.STATUS_NAMES.get(code, code)}")
+
+
+def set_option(key: int, value: int) -> int:
+    return _lib.lib().rdb_set_option(key, value)
+
+
+# ------------------------------------------------------------------------------------------ noise
+def noise_bits(rows: int, cols: int, seed: int, row0: int = 0, col0: int = 0, device="cuda") -> torch.Tensor:
+    """uint32 hash words of S[row0:row0+rows, col0:col0+cols], returned as an int32 tensor (same bits)."""
+    dev = torch.device(device)
+    out = torch.empty((rows, cols), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_noise_bits(_ptr(out), rows, cols, cols, row0, col0, _seed(seed), _stream(out.device))
+    _lib.check(rc, "rdb_noise_bits")
+    return out
+
+
+def noise(rows: int, cols: int, seed: int, row0: int = 0, col0: int = 0, dtype=torch.float32, device="cuda") -> torch.Tensor:
+    dev = torch.device(device)
+    out = torch.empty((rows, cols), dtype=dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_noise(_ptr(out), _dt(dtype), rows, cols, cols, row0, col0, _seed(seed), _stream(out.device))
+    _lib.check(rc, "rdb_noise")
+    return out
+
+
+def noise_1d(n: int, seed: int, idx0: int = 0, device="cuda") -> torch.Tensor:
+    dev = torch.device(device)
+    out = torch.empty((n,), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_noise_1d(_ptr(out), n, idx0, _seed(seed), _stream(out.device))
+    _lib.check(rc, "rdb_noise_1d")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ layer
+def _workspace(nbytes: int, dev: torch.device) -> torch.Tensor:
+    return torch.empty((max(int(nbytes), 256),), dtype=torch.uint8, device=dev)
+
+
+def linear_fwd(x: torch.Tensor, coef: torch.Tensor, seed: int, out_features: int, row0: int = 0,
+               path: int = PATH_AUTO, impl: int = IMPL_AUTO) -> torch.Tensor:
+    """y[T, N] = x[T, K] @ (S[row0:row0+N] @ coef[R, K]).T  -- x, coef contiguous, same dtype."""
+    dev = _need_cuda(x, coef)
+    if x.dim() != 2 or coef.dim() != 2 or x.shape[1] != coef.shape[1]:
+        raise RuntimeError(f"linear_fwd: x {tuple(x.shape)} and coef {tuple(coef.shape)} do not match [T,K] / [R,K]")
+    if x.dtype != coef.dtype:
+        raise RuntimeError("linear_fwd: x and coef must have the same dtype")
+    assert x.is_contiguous() and coef.is_contiguous(), "linear_fwd expects contiguous x and coef"
+    T, K = x.shape
+    R = coef.shape[0]
+    N = int(out_features)
+    dt = _dt(x.dtype)
+    L = _lib.lib()
+    y = torch.empty((T, N), dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        nbytes = L.rdb_linear_workspace_bytes(0, T, K, N, R, dt, path, impl)
+        ws = _workspace(nbytes, dev)
+        rc = L.rdb_linear_fwd(_ptr(y), _ptr(x), _ptr(coef), _ptr(ws), ws.numel(), T, K, N, R, row0, _seed(seed), dt, path,
+                              impl, _ptr(status_buffer(dev)), _stream(dev))
+    _lib.check(rc, "rdb_linear_fwd")
+    return y
+
+
+def linear_bwd(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, row0: int = 0, need_dx: bool = True,
+               need_dc: bool = True, path: int = PATH_AUTO, impl: int = IMPL_AUTO
+               ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """(dx[T,K], dc[R,K]) for dy[T,N]; either may be skipped."""
+    dev = _need_cuda(dy, x, coef)
+    if dy.dim() != 2 or x.dim() != 2 or coef.dim() != 2 or dy.shape[0] != x.shape[0] or x.shape[1] != coef.shape[1]:
+        raise RuntimeError("linear_bwd: shapes must be dy[T,N], x[T,K], coef[R,K]")
+    if not (dy.dtype == x.dtype == coef.dtype):
+        raise RuntimeError("linear_bwd: dy, x and coef must have the same dtype")
+    assert dy.is_contiguous() and x.is_contiguous() and coef.is_contiguous(), "linear_bwd expects contiguous inputs"
+    T, N = dy.shape
+    K = x.shape[1]
+    R = coef.shape[0]
+    dt = _dt(x.dtype)
+    L = _lib.lib()
+    dx = torch.empty((T, K), dtype=x.dtype, device=dev) if need_dx else None
+    dc = torch.empty((R, K), dtype=x.dtype, device=dev) if need_dc else None
+    with torch.cuda.device(dev):
+        nbytes = L.rdb_linear_workspace_bytes(1, T, K, N, R, dt, path, impl)
+        ws = _workspace(nbytes, dev)
+        rc = L.rdb_linear_bwd(_ptr(dx), _ptr(dc), _ptr(dy), _ptr(x), _ptr(coef), _ptr(ws), ws.numel(), T, K, N, R, row0,
+                              _seed(seed), dt, path, impl, _ptr(status_buffer(dev)), _stream(dev))
+    _lib.check(rc, "rdb_linear_bwd")
+    return dx, dc
+
+
+def gemv_fwd(x: torch.Tensor, coef: torch.Tensor, seed: int, out_features: int, row0: int = 0) -> torch.Tensor:
+    dev = _need_cuda(x, coef)
+    assert x.dtype == torch.float32 and coef.dtype == torch.float32 and x.is_contiguous() and coef.is_contiguous()
+    R, K = coef.shape
+    assert x.numel() == K
+    y = torch.empty((int(out_features),), dtype=torch.float32, device=dev)
+    ws = torch.empty((max(R, 1),), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_gemv_fwd(_ptr(y), _ptr(x), _ptr(coef), _ptr(ws), K, int(out_features), R, row0, _seed(seed),
+                                     _stream(dev))
+    _lib.check(rc, "rdb_gemv_fwd")
+    return y
+
+
+def gemv_bwd(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, row0: int = 0, need_dx: bool = True,
+             need_dc: bool = True):
+    dev = _need_cuda(dy, x, coef)
+    assert dy.dtype == torch.float32 and x.dtype == torch.float32 and coef.dtype == torch.float32
+    assert dy.is_contiguous() and x.is_contiguous() and coef.is_contiguous()
+    R, K = coef.shape
+    N = dy.numel()
+    dx = torch.empty((K,), dtype=torch.float32, device=dev) if need_dx else None
+    dc = torch.empty((R, K), dtype=torch.float32, device=dev) if need_dc else None
+    ws = torch.empty((max(R, 1),), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_gemv_bwd(_ptr(dx), _ptr(dc), _ptr(dy), _ptr(x), _ptr(coef), _ptr(ws), K, N, R, row0,
+                                     _seed(seed), _stream(dev))
+    _lib.check(rc, "rdb_gemv_bwd")
+    return dx, dc
+
+
+# ------------------------------------------------------------------------------------------ building blocks
+def gemm_noise(a: torch.Tensor, n: int, seed: int, transposed: bool = False, row0: int = 0, col0: int = 0,
+               impl: int = IMPL_AUTO, out_dtype: Optional[torch.dtype] = None, want_transpose: bool = False):
+    """D[M, n] = a[M, Kc] @ G.T with G generated (see rdb_gemm_noise)."""
+    dev = _need_cuda(a)
+    assert a.dim() == 2 and a.is_contiguous()
+    M, Kc = a.shape
+    out_dtype = out_dtype or a.dtype
+    d = torch.empty((M, n), dtype=out_dtype, device=dev)
+    d_t = torch.empty((n, M), dtype=out_dtype, device=dev) if want_transpose else None
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_gemm_noise(_ptr(d), _ptr(d_t), _ptr(a), M, n, Kc, Kc, n, M, _dt(a.dtype), _dt(out_dtype),
+                                       1 if transposed else 0, row0, col0, _seed(seed), impl, _ptr(status_buffer(dev)),
+                                       _stream(dev))
+    _lib.check(rc, "rdb_gemm_noise")
+    return (d, d_t) if want_transpose else d
+
+
+def gemm_dense(a: torch.Tensor, b: torch.Tensor, a_kmajor: bool = True, b_kmajor: bool = True,
+               out_dtype: Optional[torch.dtype] = None, impl: int = IMPL_AUTO) -> torch.Tensor:
+    """D[M, N] = op(a) @ op(b).T; a is [M,Kc] (a_kmajor) or [Kc,M]; b is [N,Kc] (b_kmajor) or [Kc,N]."""
+    dev = _need_cuda(a, b)
+    assert a.dim() == 2 and b.dim() == 2 and a.is_contiguous() and b.is_contiguous()
+    M, Kc = (a.shape[0], a.shape[1]) if a_kmajor else (a.shape[1], a.shape[0])
+    N, Kb = (b.shape[0], b.shape[1]) if b_kmajor else (b.shape[1], b.shape[0])
+    if Kc != Kb:
+        raise RuntimeError("gemm_dense: contraction extents differ")
+    out_dtype = out_dtype or a.dtype
+    d = torch.empty((M, N), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_gemm_dense(_ptr(d), _ptr(a), _ptr(b), M, N, Kc, a.shape[1], b.shape[1], N, _dt(a.dtype),
+                                       _dt(b.dtype), _dt(out_dtype), 1 if a_kmajor else 0, 1 if b_kmajor else 0, impl,
+                                       _ptr(status_buffer(dev)), _stream(dev))
+    _lib.check(rc, "rdb_gemm_dense")
+    return d
+
+
+# ------------------------------------------------------------------------------------------ 1-D coefficient form
+def materialize_fwd(coef: torch.Tensor, size, strides, seed: int) -> torch.Tensor:
+    dev = _need_cuda(coef)
+    assert coef.dim() == 1 and coef.dtype == torch.float32 and coef.is_contiguous()
+    size = list(size)
+    strides = list(strides)
+    if len(size) == 1:
+        P, Q, sP, sQ = 1, size[0], 0, strides[0]
+    elif len(size) == 2:
+        P, Q, sP, sQ = size[0], size[1], strides[0], strides[1]
+    else:
+        raise RuntimeError("materialize_fwd handles 1-D and 2-D outputs")
+    out = torch.empty(size, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_materialize_fwd(_ptr(out), _ptr(coef), coef.numel(), P, Q, sP, sQ, _seed(seed), _stream(dev))
+    _lib.check(rc, "rdb_materialize_fwd")
+    return out
+
+
+def materialize_bwd(dout: torch.Tensor, dcoefs_size: int, seed: int) -> torch.Tensor:
+    dev = _need_cuda(dout)
+    assert dout.is_contiguous(), "dout is not contiguous, backwards pass might give incorrect results."
+    dout = dout.reshape(-1).to(torch.float32)
+    L = _lib.lib()
+    dcoef = torch.empty((int(dcoefs_size),), dtype=torch.float32, device=dev)
+    nbytes = L.rdb_materialize_bwd_workspace_bytes(dout.numel(), int(dcoefs_size))
+    ws = torch.empty((max(nbytes // 4, 1),), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = L.rdb_materialize_bwd(_ptr(dcoef), _ptr(dout), _ptr(ws), dout.numel(), int(dcoefs_size), _seed(seed),
+                                   _stream(dev))
+    _lib.check(rc, "rdb_materialize_bwd")
+    return dcoef
