@@ -1,0 +1,179 @@
+"""torch.library operator boundary.
+
+Keeps the reference's operator names and schemas so existing call sites bind unchanged:
+
+  rten::materialize_fwd / rten::materialize_bwd     src/rten_cpp/RandumbTensor.py:371-390
+  rten_cpp::sq5_gen_2d / rten_cpp::materialize_fwd  src/rten_cpp/csrc/rten.cpp:36-39, ops.py:8-13
+
+and adds the operators of the matrix-coefficient layer ``W = S @ C`` that fill the slot the
+reference left to ``fakeMM`` (RandumbTensor.py:771-791, 942-946):
+
+  rten::rlinear_fwd(x, coef, seed, out_features, row0=0) -> y
+  rten::rlinear_bwd(dy, x, coef, seed, row0, need_dx, need_dc) -> (dx, dc)
+  rten::noise(rows, cols, seed, row0, dtype, device) -> S
+
+Every operator is functional (fresh outputs, current stream), has a fake (meta) kernel so
+FakeTensor / torch.compile tracing works, and -- like the reference (RandumbTensor.py:438-448) --
+a CPU registration that raises ``NotImplementedError``: there is no CPU implementation.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+from torch.library import custom_op
+
+from . import kernels as K
+
+
+def _cpu_raises(name):
+    def _impl(*args, **kwargs):
+        raise NotImplementedError(f"Unsupported CPU implementation of {name} called.")
+    return _impl
+
+
+# ------------------------------------------------------------------------------------------------
+# matrix-coefficient layer
+# ------------------------------------------------------------------------------------------------
+@custom_op("rten::rlinear_fwd", mutates_args=(), device_types="cuda")
+def rlinear_fwd(x: torch.Tensor, coef: torch.Tensor, seed: int, out_features: int, row0: int = 0) -> torch.Tensor:
+    assert x.dim() == 2, "rlinear_fwd expects x flattened to [T, K]"
+    return K.linear_fwd(x.contiguous(), coef.contiguous(), seed, out_features, row0)
+
+
+@rlinear_fwd.register_fake
+def _(x, coef, seed, out_features, row0=0):
+    return x.new_empty((x.shape[0], out_features))
+
+
+rlinear_fwd.register_kernel("cpu")(_cpu_raises("rlinear_fwd"))
+
+
+@custom_op("rten::rlinear_bwd", mutates_args=(), device_types="cuda")
+def rlinear_bwd(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, row0: int, need_dx: bool,
+                need_dc: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    dx, dc = K.linear_bwd(dy.contiguous(), x.contiguous(), coef.contiguous(), seed, row0, need_dx, need_dc)
+    # custom ops cannot return None: an empty tensor stands for "not requested"
+    if dx is None:
+        dx = x.new_empty((0,))
+    if dc is None:
+        dc = coef.new_empty((0,))
+    return dx, dc
+
+
+@rlinear_bwd.register_fake
+def _(dy, x, coef, seed, row0, need_dx, need_dc):
+    return (x.new_empty(x.shape) if need_dx else x.new_empty((0,)),
+            coef.new_empty(coef.shape) if need_dc else coef.new_empty((0,)))
+
+
+rlinear_bwd.register_kernel("cpu")(_cpu_raises("rlinear_bwd"))
+
+
+def _rlinear_setup(ctx, inputs, output):
+    x, coef, seed, out_features, row0 = inputs
+    ctx.save_for_backward(x, coef)
+    ctx.seed = seed
+    ctx.row0 = row0
+
+
+def _rlinear_backward(ctx, dy):
+    x, coef = ctx.saved_tensors
+    need_dx, need_dc = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+    dx, dc = rlinear_bwd(dy, x, coef, ctx.seed, ctx.row0, need_dx, need_dc)
+    return (dx if need_dx else None), (dc if need_dc else None), None, None, None
+
+
+rlinear_fwd.register_autograd(_rlinear_backward, setup_context=_rlinear_setup)
+
+
+def rlinear(x: torch.Tensor, coef: torch.Tensor, seed: int, out_features: int, row0: int = 0,
+            bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ (S @ coef).T (+ bias) for x of shape [..., K]; differentiable in x and coef."""
+    lead = x.shape[:-1]
+    y = rlinear_fwd(x.reshape(-1, x.shape[-1]), coef, seed, out_features, row0)
+    y = y.reshape(*lead, out_features)
+    if bias is not None:
+        y = y + bias
+    return y
+
+
+@custom_op("rten::noise", mutates_args=(), device_types="cuda")
+def noise(rows: int, cols: int, seed: int, row0: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+    return K.noise(rows, cols, seed, row0, 0, dtype, device)
+
+
+@noise.register_fake
+def _(rows, cols, seed, row0, dtype, device):
+    return torch.empty((rows, cols), dtype=dtype, device=device)
+
+
+# ------------------------------------------------------------------------------------------------
+# reference operators (1-D coefficient vector)
+# ------------------------------------------------------------------------------------------------
+@custom_op("rten::materialize_fwd", mutates_args=(), device_types="cuda")
+def materialize_fwd(coefs: torch.Tensor, size: List[int], strides: List[int], seed: int,
+                    scale_bias: Optional[torch.Tensor], fused_bias: bool) -> torch.Tensor:
+    assert not (fused_bias and scale_bias is None), "scale_bias not initialized but fused_bias is True"
+    if fused_bias:
+        raise NotImplementedError("the fused random bias of materialize_fwd is not part of this build")
+    return K.materialize_fwd(coefs.float().contiguous(), size, strides, seed)
+
+
+@materialize_fwd.register_fake
+def _(coefs, size, strides, seed, scale_bias, fused_bias):
+    return coefs.new_empty(size, dtype=torch.float32)
+
+
+materialize_fwd.register_kernel("cpu")(_cpu_raises("materialize_fwd"))
+
+
+@custom_op("rten::materialize_bwd", mutates_args=(), device_types="cuda")
+def materialize_bwd(dout: torch.Tensor, dcoefs_size: int, seed: int) -> torch.Tensor:
+    assert dout.is_contiguous(), "dout is not contiguous, backwards pass might give incorrect results."
+    return K.materialize_bwd(dout, dcoefs_size, seed)
+
+
+@materialize_bwd.register_fake
+def _(dout, dcoefs_size, seed):
+    return dout.new_empty((dcoefs_size,), dtype=torch.float32)
+
+
+materialize_bwd.register_kernel("cpu")(_cpu_raises("materialize_bwd"))
+
+
+def _mat_setup(ctx, inputs, output):
+    coefs, size, strides, seed, scale_bias, fused_bias = inputs
+    ctx.dcoefs_size = coefs.numel()
+    ctx.seed = seed
+    ctx.coef_dtype = coefs.dtype
+
+
+def _mat_backward(ctx, grad):
+    dcoefs = materialize_bwd(grad.contiguous(), ctx.dcoefs_size, ctx.seed).to(ctx.coef_dtype)
+    return dcoefs, None, None, None, None, None
+
+
+materialize_fwd.register_autograd(_mat_backward, setup_context=_mat_setup)
+
+
+# C++-namespace twins of the reference (rten.cpp:36-39); registered from Python onto the same C ABI.
+@custom_op("rten_cpp::sq5_gen_2d", mutates_args=())
+def sq5_gen_2d(M: int, N: int, seed: int) -> torch.Tensor:
+    return K.noise(M, N, seed, 0, 0, torch.float32, torch.device("cuda", torch.cuda.current_device()))
+
+
+@sq5_gen_2d.register_fake
+def _(M, N, seed):
+    return torch.empty((M, N), dtype=torch.float32, device="cuda")
+
+
+@custom_op("rten_cpp::materialize_fwd", mutates_args=(), device_types="cuda")
+def materialize_fwd_cpp(coef: torch.Tensor, seed: int, P: int, Q: int, stride_P: int, stride_Q: int) -> torch.Tensor:
+    assert coef.dim() == 1 and coef.is_contiguous()
+    return K.materialize_fwd(coef.float(), [P, Q], [stride_P, stride_Q], seed)
+
+
+@materialize_fwd_cpp.register_fake
+def _(coef, seed, P, Q, stride_P, stride_Q):
+    return coef.new_empty((P, Q), dtype=torch.float32)
