@@ -1,0 +1,455 @@
+#!/usr/bin/env python
+"""Benchmark of the fused pseudorandom-weight matmul (forward + dX + dC) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemm|sharded|gemv]
+
+One step = one forward + backward pass of the layer over one batch of seeded synthetic input.
+Default workload ("gemm"): x bf16 [8192 x 4096], virtual W [16384 x 4096], d_c = 1024, seed 42, float32
+accumulation -- the single-GPU configuration the headline metric is quoted on.  With N > 1 (launched by
+torchrun, one rank per GPU) every rank runs that step on its own tokens and the coefficient gradients
+are summed with one NCCL all-reduce per step (data parallel, weak scaling).
+
+`--workload sharded` runs the 65536 x 16384 virtual layer (d_c = 2048, seed 7) with its output rows split
+over the ranks (strong scaling); `--workload gemv` the batch-1 float32 4096 x 4096 layer.
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the reference's CPU PyTorch path (explicit noise
+matrix, W = S @ C, F.linear, autograd) on the host cores instead; it never touches the GPU kernels.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: T, K, N, R, seed, dtype
+    "gemm": dict(T=8192, K=4096, N=16384, R=1024, seed=42, dtype="bf16", coef_std=(3 * 0.02 ** 2 / 1024) ** 0.5),
+    "sharded": dict(T=4096, K=16384, N=65536, R=2048, seed=7, dtype="bf16", coef_std=(3 * 0.02 ** 2 / 2048) ** 0.5),
+    "gemv": dict(T=1, K=4096, N=4096, R=256, seed=42, dtype="f32", coef_std=(3.0 / (256 * 4096)) ** 0.5),
+}
+
+
+def algorithmic_flops(T, K, N, R):
+    """Minimum-association count for fwd + dX + dC: factored 2TR(3K+2N) or the W path 6TNK + 6NRK."""
+    fact = 2.0 * T * R * (3 * K + 2 * N)
+    wpath = 6.0 * T * N * K + 6.0 * N * R * K
+    return min(fact, wpath)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm=d["hbm_gbs"], tensor=d["bf16_tflops"], tensor_sustained=d["bf16_tflops_sustained"], src="measured")
+    return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.lines, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        for ts, line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clk, mx = float(parts[1]), float(parts[2])
+            except ValueError:
+                continue
+            smax = mx
+            if t0 - 0.05 <= ts <= t1 + 0.1:
+                sm.append(clk)
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        if not sm:  # region shorter than the sampling period: use everything seen
+            for ts, line in self.lines:
+                parts = [p.strip() for p in line.split(",")]
+                try:
+                    sm.append(float(parts[1]))
+                except (ValueError, IndexError):
+                    pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: explicit S, W = S @ C, F.linear, autograd -- float32 on the host cores
+# --------------------------------------------------------------------------------------------------
+def cpu_reference_step(cfg, T_sample, state=None):
+    """One forward+backward of the reference's PyTorch path on the CPU; returns (seconds, state)."""
+    from oracle import oracle as O  # the CPU baseline leg is one of the places allowed to run the oracle
+    K, N, R, seed = cfg["K"], cfg["N"], cfg["R"], cfg["seed"]
+    if state is None:
+        g = torch.Generator().manual_seed(1003)
+        x = torch.randn(T_sample, K, generator=g)
+        C = (torch.randn(R, K, generator=g) * cfg["coef_std"])
+        dy = torch.randn(T_sample, N, generator=g)
+        if cfg["dtype"] == "bf16":
+            x, C, dy = x.bfloat16().float(), C.bfloat16().float(), dy.bfloat16().float()
+        state = (x, C, dy)
+    x, C, dy = state
+    t0 = time.perf_counter()
+    S = torch.from_numpy(O.c_noise_f32(N, R, seed))        # generation is part of the path and is timed
+    xr = x.clone().requires_grad_(True)
+    Cr = C.clone().requires_grad_(True)
+    W = S @ Cr
+    y = torch.nn.functional.linear(xr, W)
+    y.backward(dy)
+    dt = time.perf_counter() - t0
+    return dt, state
+
+
+def pick_cpu_sample(cfg, budget_s):
+    """Largest token count (<= the workload's) whose estimated step time fits the budget."""
+    T = cfg["T"]
+    probe = min(T, 256)
+    cpu_reference_step(cfg, probe)                          # warm the thread pool / page in
+    t_probe, _ = cpu_reference_step(cfg, probe)
+    fixed = t_probe                                         # mostly the token-independent S, W = S@C, dC part
+    t2, _ = cpu_reference_step(cfg, min(T, 2 * probe))
+    per_tok = max((t2 - t_probe) / max(min(T, 2 * probe) - probe, 1), 1e-7)
+    fixed = max(t_probe - per_tok * probe, 0.0)
+    T_fit = int((budget_s - fixed) / per_tok) if budget_s > fixed else probe
+    T_s = max(probe, min(T, T_fit))
+    if T_s < T:
+        T_s = max(probe, (T_s // 256) * 256)
+    return T_s
+
+
+def run_reference(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    T_s = pick_cpu_sample(cfg, budget_s=max(120.0 / max(args.steps + args.warmup, 1), 1.0))
+    state = None
+    for _ in range(args.warmup):
+        _, state = cpu_reference_step(cfg, T_s, state)
+    times = []
+    for _ in range(args.steps):
+        dt, state = cpu_reference_step(cfg, T_s, state)
+        times.append(dt)
+    total = sum(times)
+    flops = algorithmic_flops(T_s, cfg["K"], cfg["N"], cfg["R"]) * args.steps
+    value = flops / total / 1e12
+    sample = f"{T_s} of {cfg['T']} tokens per step, full K/N/d_c; algorithmic FLOPs of the sample / wall time"
+    line = {
+        "impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.workload, cfg, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(workload):
+    return "fused PRNG-matmul fwd+bwd GB/s" if workload == "gemv" else "fused PRNG-matmul fwd+bwd TFLOP/s"
+
+
+def workload_config(name, cfg, gpus):
+    par = {"gemm": f"dp{gpus} (tokens per rank fixed, dC all-reduce)" if gpus > 1 else "single GPU",
+           "sharded": f"output rows split over {gpus} ranks, dC and dX all-reduce" if gpus > 1 else "single GPU",
+           "gemv": "replicas only"}[name]
+    return {"workload": f"{name}: x[{cfg['T']}x{cfg['K']}] {cfg['dtype']}, virtual W[{cfg['N']}x{cfg['K']}], d_c={cfg['R']}, "
+                        f"seed={cfg['seed']}, fwd + dX + dC",
+            "parallelism": par, "l2": "inputs and outputs exceed the 126 MB L2 (no explicit flush)" if name != "gemv"
+            else "L2 flushed between iterations"}
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def run_ours(args, cfg):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py measures the CUDA kernels; no GPU is visible (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from randumb_b200 import kernels as K
+    import randumb_b200 as rb
+
+    dt = torch.bfloat16 if cfg["dtype"] == "bf16" else torch.float32
+    T, Kin, N, R, seed = cfg["T"], cfg["K"], cfg["N"], cfg["R"], cfg["seed"]
+    row0, n_local = 0, N
+    if args.workload == "sharded" and world > 1:
+        lo, hi = rb.parallel.shard_range(N, world, rank)
+        row0, n_local = lo, hi - lo
+    g = torch.Generator().manual_seed(1003 + (rank if args.workload == "gemm" else 0))
+    x_host = torch.randn(T, Kin, generator=g).to(dt).pin_memory()
+    C = (torch.randn(R, Kin, generator=torch.Generator().manual_seed(7)) * cfg["coef_std"]).to(dt).to(dev)
+    x = x_host.to(dev)
+    dy = torch.randn(T, n_local, generator=g).to(dt).to(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.workload == "gemv" else None
+
+    def step():
+        y = K.linear_fwd(x, C, seed, n_local, row0)
+        dx, dc = K.linear_bwd(dy, x, C, seed, row0)
+        if world > 1:
+            dist.all_reduce(dc)
+            if args.workload == "sharded":
+                dist.all_reduce(dx)
+        return y, dx, dc
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+        if flush is not None:
+            flush.zero_()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
+    if flush is None:
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        barrier()
+        elapsed_ms = ev0.elapsed_time(ev1)
+    else:
+        elapsed_ms = 0.0
+        for _ in range(args.steps):
+            flush.zero_()
+            ev0.record()
+            step()
+            ev1.record()
+            torch.cuda.synchronize()
+            elapsed_ms += ev0.elapsed_time(ev1)
+        barrier()
+    t_wall1 = time.time()
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    K.check_status()
+    tmax = torch.tensor([elapsed_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(tmax.item())
+
+    # ---- dominant kernel, timed live with CUDA events on the launching stream -------------------
+    roofline, peaks = None, measured_peaks()
+    if args.workload != "gemv":
+        z = torch.randn(T, R, device=dev).to(dt)
+        reps = max(args.steps, 5)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(2 * reps)]
+        for _ in range(2):
+            K.gemm_noise(z, n_local, seed, False, row0, impl=K.IMPL_UMMA)
+            K.gemm_noise(dy, R, seed, True, row0, impl=K.IMPL_UMMA)
+        torch.cuda.synchronize()
+        for i in range(reps):
+            evs[2 * i][0].record(); K.gemm_noise(z, n_local, seed, False, row0, impl=K.IMPL_UMMA); evs[2 * i][1].record()
+            evs[2 * i + 1][0].record(); K.gemm_noise(dy, R, seed, True, row0, impl=K.IMPL_UMMA); evs[2 * i + 1][1].record()
+        torch.cuda.synchronize()
+        avg_ms = sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+        flops_launch = 2.0 * T * n_local * R
+        achieved = flops_launch / (avg_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "noise_gemm_kernel (y = z S^T and g = dY S launches)", "achieved": achieved,
+                    "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
+                    "peak_source": f"{peaks['src']} burst bf16", "avg_launch_ms": avg_ms, "traffic": NOISE_GEMM_DRAM_BYTES.get(args.workload)}
+    else:
+        # matrix-vector: bytes of C read twice and dC written once (+ the small vectors)
+        bytes_step = 3 * R * Kin * 4 + 4 * (3 * Kin + 2 * N + 2 * R)
+        achieved = bytes_step / (elapsed_ms / args.steps * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "gemv_cx / gemv_sz / gemv_stdy / gemv_dxdc (whole step)", "achieved": achieved,
+                    "peak": peaks["hbm"], "unit": "GB/s", "frac": achieved / peaks["hbm"], "peak_source": f"{peaks['src']} copy",
+                    "traffic": None}
+
+    # ---- end to end through the public module API, host buffers, copies inside the timed region ----
+    e2e = run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier)
+
+    if args.workload == "gemv":
+        bytes_step = 3 * R * Kin * 4 + 4 * (3 * Kin + 2 * N + 2 * R)
+        value = world * bytes_step * args.steps / (elapsed_ms * 1e-3) / 1e9
+        unit = "GB/s"
+    else:
+        # every rank's algorithmic work; for the sharded layer the rows (and so the work) are split
+        per_rank = algorithmic_flops(T, Kin, n_local, R) if args.workload == "sharded" else algorithmic_flops(T, Kin, N, R)
+        total = per_rank * world if args.workload == "gemm" else _sum_over_ranks(per_rank, world, dev)
+        value = total * args.steps / (elapsed_ms * 1e-3) / 1e12
+        unit = "TFLOP/s"
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        T_s = pick_cpu_sample(cfg, budget_s=20.0)
+        dt_cpu, _ = cpu_reference_step(cfg, T_s)
+        if args.workload == "gemv":
+            v = (3 * R * Kin * 4 + 4 * (3 * Kin + 2 * N + 2 * R)) / dt_cpu / 1e9
+        else:
+            v = algorithmic_flops(T_s, Kin, N, R) / dt_cpu / 1e12
+        cpu_baseline = {"value": v, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
+                        "sample": f"one step at {T_s} of {T} tokens (full K/N/d_c) in {dt_cpu:.2f} s: explicit S from the C oracle, "
+                                  "W = S @ C, F.linear, autograd; float32"}
+
+    if rank == 0:
+        line = {
+            "metric": metric_name(args.workload), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if args.workload == "sharded" else "weak", "vs_baseline": None,
+            "dtype": cfg["dtype"], "data": "synthetic", "config": workload_config(args.workload, cfg, world),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(args.workload, T) * args.steps,
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _sum_over_ranks(v, world, dev):
+    import torch.distributed as dist
+    t = torch.tensor([v], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t)
+    return float(t.item())
+
+
+def launches_per_step(workload, T):
+    # forward: dense z + generated-operand y; backward: generated-operand g + dense dX + dense dC
+    return 4 if workload == "gemv" else 5
+
+
+# DRAM bytes per launch of noise_gemm_kernel from the ncu capture summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum, scaled to the full launch); None until captured.
+NOISE_GEMM_DRAM_BYTES = {"gemm": None, "sharded": None}
+
+
+def run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier):
+    """Same step through RandumbLinear-style public API: x comes from pinned host memory every step
+    (prefetched on a copy stream so the transfer overlaps the previous step's kernels), the loss value is
+    read back to the host every step."""
+    import torch.distributed as dist
+    T, Kin, N, R, seed = cfg["T"], cfg["K"], cfg["N"], cfg["R"], cfg["seed"]
+    coef = torch.nn.Parameter(C.clone())
+    copy_stream = torch.cuda.Stream(device=dev)
+    hosts = [x_host, x_host.clone().pin_memory()]
+    bufs = [torch.empty_like(x_host, device=dev) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def prefetch(i):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[i % 2])
+            bufs[i % 2].copy_(hosts[i % 2], non_blocking=True)
+            ready[i % 2].record(copy_stream)
+
+    def one(i, nsteps):
+        torch.cuda.current_stream(dev).wait_event(ready[i % 2])
+        if i + 1 < nsteps:
+            prefetch(i + 1)
+        xin = bufs[i % 2].requires_grad_(True)
+        y = rb.rlinear(xin, coef, seed, n_local, row0)
+        loss = y.float().square().mean()
+        loss.backward()
+        consumed[i % 2].record(torch.cuda.current_stream(dev))
+        if world > 1:
+            dist.all_reduce(coef.grad)
+        val = float(loss.item())                       # device -> host read of the step's result
+        coef.grad = None
+        bufs[i % 2].requires_grad_(False)
+        bufs[i % 2].grad = None
+        return val
+
+    n_e2e = max(3, min(args.steps, 10))
+    for c in consumed:
+        c.record(torch.cuda.current_stream(dev))
+    prefetch(0)
+    for i in range(3):
+        one(i, 3)
+    barrier()
+    for c in consumed:
+        c.record(torch.cuda.current_stream(dev))
+    prefetch(0)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(n_e2e):
+        one(i, n_e2e)
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    tmax = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    ms = float(tmax.item())
+    if args.workload == "gemv":
+        work = world * (3 * R * Kin * 4 + 4 * (3 * Kin + 2 * N + 2 * R)) / 1e9
+        unit = "GB/s"
+    else:
+        per_rank = algorithmic_flops(T, Kin, n_local, R)
+        work = (per_rank * world if args.workload == "gemm" else _sum_over_ranks(per_rank, world, dev)) / 1e12
+        unit = "TFLOP/s"
+    return {"value": work * n_e2e / (ms * 1e-3), "unit": unit, "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
+            "d2h_bytes_per_step": 4, "steps": n_e2e, "ms_per_step": ms / n_e2e,
+            "what": "pinned-host x -> device (copy stream, overlapped), rlinear forward, mean-square loss, autograd backward "
+                    "(dX and dC), loss.item() back to the host"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gemm", choices=list(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

@@ -133,6 +133,14 @@ int rdb_linear_bwd(void *dx, void *dc, const void *dy, const void *x, const void
                    uint32_t seed, int dtype, int path, int impl, int32_t *status, void *stream);
 
 /*
+ * Dense weight w[N,K] = S[row0:row0+N, 0:R] * coef[R,K] written out in `dtype` (debugging and ops
+ * that have no fused kernel).  Stands in for RandumbTensor.materialize / get_materialized
+ * (src/rten_cpp/RandumbTensor.py:862-868, 887-892) for a matrix-shaped coefficient.
+ */
+int rdb_linear_weight(void *w, const void *coef, int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed,
+                      int dtype, void *stream);
+
+/*
  * Batch-1 float32 forward: y[N] = S (C x).  workspace: R floats.  Same reference slot as
  * rdb_linear_fwd, specialised for a single activation row (matrix-vector; bandwidth bound).
  */

@@ -180,6 +180,17 @@ extern "C" size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64
     return ws_layout(op, T, K, N, R, p, im).total;
 }
 
+extern "C" int rdb_linear_weight(void *w, const void *coef, int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed,
+                                 int dtype, void *stream) {
+    if (K < 0 || N < 0 || R < 0) return RDB_ERR_SHAPE;
+    if (dtype != RDB_F32 && dtype != RDB_BF16) return RDB_ERR_DTYPE;
+    if (K == 0 || N == 0) return RDB_OK;
+    if (!w || (R > 0 && !coef)) return RDB_ERR_NULL;
+    // W[o,i] = sum_r C[r,i] S[row0+o, r], written as D(m=i, n=o) at o*K + i
+    return simt_gemm(w, dtype, 1, K, coef, dtype, 1, K, nullptr, RDB_F32, 0, 0, sq5_lin_rows(seed, (uint32_t)row0, 0), K, N,
+                     R, (cudaStream_t)stream);
+}
+
 static int check_common(int64_t T, int64_t K, int64_t N, int64_t R, int dtype) {
     if (T < 0 || K < 0 || N < 0 || R < 0) return RDB_ERR_SHAPE;
     if (dtype != RDB_F32 && dtype != RDB_BF16) return RDB_ERR_DTYPE;

@@ -161,6 +161,19 @@ def linear_bwd(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int,
     return dx, dc
 
 
+def linear_weight(coef: torch.Tensor, seed: int, out_features: int, row0: int = 0) -> torch.Tensor:
+    """Dense W[N, K] = S[row0:row0+N] @ coef (debugging / ops without a fused kernel)."""
+    dev = _need_cuda(coef)
+    assert coef.dim() == 2 and coef.is_contiguous()
+    R, K = coef.shape
+    w = torch.empty((int(out_features), K), dtype=coef.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_linear_weight(_ptr(w), _ptr(coef), K, int(out_features), R, row0, _seed(seed), _dt(coef.dtype),
+                                          _stream(dev))
+    _lib.check(rc, "rdb_linear_weight")
+    return w
+
+
 def gemv_fwd(x: torch.Tensor, coef: torch.Tensor, seed: int, out_features: int, row0: int = 0) -> torch.Tensor:
     dev = _need_cuda(x, coef)
     assert x.dtype == torch.float32 and coef.dtype == torch.float32 and x.is_contiguous() and coef.is_contiguous()

@@ -1,0 +1,167 @@
+"""Modules whose weights are RandumbTensors.
+
+``RandumbLinear`` is the matrix-coefficient layer (coef ``[d_c, in_features]``); ``SillyLinear`` keeps
+the reference constructor conventions (src/rten_cpp/SillyLayers.py:142-227): ``int_dim`` and ``seed``
+are lists of two values or generators, parameters are ``weight_coef`` / ``bias_coef``, the virtual
+tensors are registered as buffers ``weight`` / ``bias``.  ``stepgen`` / ``listgen`` are the reference's
+seed and int_dim sequences (SillyLayers.py:25-34).
+"""
+from __future__ import annotations
+
+import math
+from types import GeneratorType
+from typing import Generator, Optional, Union
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+from .tensor import CreateRandumbTensor, RandumbTensor
+
+
+def stepgen(offset, step):
+    """offset, offset+step, offset+2*step, ... -- a whole model's seeds are then two integers."""
+    i = 0
+    while True:
+        yield offset + step * i
+        i += 1
+
+
+def listgen(lst):
+    for i in lst:
+        yield i
+
+
+def kaiming_out_std(fan_in: int, a: float = math.sqrt(5)) -> float:
+    """Standard deviation nn.Linear's default init gives its weight: gain / sqrt(fan_in)."""
+    gain = math.sqrt(2.0 / (1 + a * a))
+    return gain / math.sqrt(fan_in)
+
+
+def coef_std_for(out_std: float, int_dim: int) -> float:
+    """var(W) = int_dim * var(S) * var(coef) with var(S) = 1/3  =>  std(coef) = sqrt(3/int_dim) * std(W)
+    (reference: SillyLayers.py:62-71, README.md:20-29)."""
+    return math.sqrt(3.0 / int_dim) * out_std
+
+
+class RandumbModuleMixin(nn.Module):
+    """``.to()/.cuda()/.float()`` rebuild the RandumbTensor buffers around the moved parameters, because a
+    wrapper subclass cannot change device or dtype in place (reference: SillyLayers.py:89-113)."""
+
+    def _apply(self, fn, *args, **kwargs):
+        super()._apply(fn, *args, **kwargs)
+        self._rebuild_virtual_buffers()
+        return self
+
+    def _rebuild_virtual_buffers(self):
+        for name, buf in list(self._buffers.items()):
+            if isinstance(buf, RandumbTensor):
+                coef = getattr(self, f"{name}_coef")
+                self._buffers[name] = CreateRandumbTensor(coef, buf.seed, buf.shape, buf.scale_bias, buf.fused_bias, buf.row0)
+
+
+class RandumbLinear(RandumbModuleMixin, nn.Module):
+    """``y = x @ (S @ C).T (+ b)`` with ``S = noise(out_features, d_c; seed)`` regenerated inside the kernels.
+
+    Args:
+        in_features, out_features: as nn.Linear.
+        d_c: coefficient (intrinsic) dimension; the trainable state is ``coef[d_c, in_features]``.
+        seed: noise seed of this layer.
+        bias: ordinary dense bias vector (not pseudorandom).
+        row0: global index of this module's first output row -- a rank that owns rows
+            ``[row0, row0 + out_features)`` of a larger virtual layer regenerates exactly those rows.
+        init_std: target std of the virtual weight; default is nn.Linear's Kaiming-uniform equivalent.
+            ``coef ~ N(0, 3 * init_std**2 / d_c)``.
+    """
+
+    def __init__(self, in_features: int, out_features: int, d_c: int, seed: int, bias: bool = False, device=None,
+                 dtype=None, row0: int = 0, init_std: Optional[float] = None):
+        super().__init__()
+        self.in_features, self.out_features, self.d_c, self.seed, self.row0 = in_features, out_features, d_c, int(seed), int(row0)
+        self.init_std = init_std if init_std is not None else kaiming_out_std(in_features)
+        self.weight_coef = nn.Parameter(torch.empty((d_c, in_features), device=device, dtype=dtype))
+        self.register_buffer("weight", CreateRandumbTensor(self.weight_coef, self.seed, (out_features, in_features), row0=self.row0),
+                             persistent=False)
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed & 0x7FFFFFFFFFFFFFFF)
+        with torch.no_grad():
+            self.weight_coef.normal_(0.0, coef_std_for(self.init_std, self.d_c), generator=gen)
+            if self.bias is not None:
+                self.bias.zero_()
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        coef = self.weight_coef if self.weight_coef.dtype == input.dtype else self.weight_coef.to(input.dtype)
+        return ops.rlinear(input, coef, self.seed, self.out_features, self.row0, self.bias)
+
+    def get_extra_state(self):
+        return {"seed": self.seed, "d_c": self.d_c, "out_features": self.out_features, "row0": self.row0}
+
+    def set_extra_state(self, state):
+        if state["d_c"] != self.d_c or state["out_features"] != self.out_features:
+            raise RuntimeError(f"checkpoint describes a different layer: {state}")
+        self.seed, self.row0 = int(state["seed"]), int(state["row0"])
+        self._rebuild_virtual_buffers_with_seed()
+
+    def _rebuild_virtual_buffers_with_seed(self):
+        self._buffers["weight"] = CreateRandumbTensor(self.weight_coef, self.seed, (self.out_features, self.in_features),
+                                                      row0=self.row0)
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, d_c={self.d_c}, seed={self.seed}, "
+                f"row0={self.row0}, bias={self.bias is not None}")
+
+
+class SillyLinear(RandumbModuleMixin, nn.Module):
+    """Reference-convention linear layer: weight and bias are both RandumbTensors.
+
+    ``int_dim`` / ``seed``: list of two values or a generator (first for the weight, second for the
+    bias).  The weight uses the matrix-coefficient form (``weight_coef`` is ``[int_dim[0], in_features]``);
+    the bias keeps the reference's 1-D coefficient form (``bias_coef`` is ``[int_dim[1]]``) and is
+    materialised by ``rten::materialize_fwd``.  The reference's fused random bias (``rt_bias``) is not
+    part of this build.
+    """
+    num_seeds = 2
+
+    def __init__(self, in_features: int, out_features: int, int_dim: Union[list, Generator], seed: Union[list, Generator],
+                 bias: bool = True, rt_bias: bool = False, device=None, dtype=None) -> None:
+        super().__init__()
+        if rt_bias:
+            raise NotImplementedError("rt_bias (fused random bias) is not part of this build")
+        self.in_features, self.out_features, self.rt_bias = in_features, out_features, rt_bias
+        self.int_dim = [next(int_dim) for _ in range(self.num_seeds)] if isinstance(int_dim, GeneratorType) else list(int_dim)
+        self.seed = [next(seed) for _ in range(self.num_seeds)] if isinstance(seed, GeneratorType) else list(seed)
+        self.weight_coef = nn.Parameter(torch.empty((self.int_dim[0], in_features), dtype=dtype, device=device))
+        self.register_buffer("weight", CreateRandumbTensor(self.weight_coef, self.seed[0], (out_features, in_features)),
+                             persistent=False)
+        if bias:
+            self.bias_coef = nn.Parameter(torch.empty(self.int_dim[1], dtype=dtype, device=device))
+            self.register_buffer("bias", CreateRandumbTensor(self.bias_coef, self.seed[1], (out_features,)), persistent=False)
+        else:
+            self.bias = None
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        """Uniform coefficients with the variance that gives the virtual weight nn.Linear's default std
+        (reference ``init_kaiming_uniform``: SillyLayers.py:37-79)."""
+        out_std = kaiming_out_std(self.in_features)
+        gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed[0] & 0x7FFFFFFFFFFFFFFF)
+        with torch.no_grad():
+            bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[0])
+            self.weight_coef.uniform_(-bound, bound, generator=gen)
+            if self.bias is not None:
+                bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[1])
+                self.bias_coef.uniform_(-bound, bound, generator=gen)
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        return F.linear(input, self.weight, self.bias)
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, int_dim={self.int_dim}, "
+                f"seeds={self.seed}, bias={self.bias is not None}")

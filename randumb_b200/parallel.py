@@ -1,0 +1,172 @@
+"""Multi-GPU use of the layer: one process per GPU, torch.distributed (NCCL over NVLink) for the two
+exchanges the path has.
+
+* Row sharding of one large virtual layer: rank r owns output rows ``[r*N/G, (r+1)*N/G)`` and
+  regenerates exactly those noise rows from ``(seed, row0)`` -- no weight bytes ever move.  The only
+  traffic is activations: optionally the output ``y`` (all-gathered along features) in forward, and the
+  sums over ranks of the input gradient and of ``dC`` in backward.
+* Data parallel training: every rank holds all of ``C``; the coefficient gradients are summed with one
+  flat all-reduce per step.  (The reference's only parallelism is DDP in its GPT app:
+  modded-nanogpt/train_gpt2.py:261, 346, 441.)
+
+The collectives are plain NCCL calls on separate buffers; none of the compute kernels reads a peer's
+memory.  ``local_*`` callables are injectable so the partitioning and collective plumbing can be
+exercised with CPU (gloo) ranks.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+# ------------------------------------------------------------------------------------------------
+# partition arithmetic
+# ------------------------------------------------------------------------------------------------
+def shard_range(total: int, world: int, rank: int, multiple: int = 8) -> Tuple[int, int]:
+    """[lo, hi) of the ``rank``-th of ``world`` contiguous shards of ``total`` items.
+
+    Shard sizes are multiples of ``multiple`` (the tensor-core kernels want rows in groups of 8) except
+    possibly the last, and differ by at most one group.
+    """
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    groups = (total + multiple - 1) // multiple
+    base, extra = divmod(groups, world)
+    lo_g = rank * base + min(rank, extra)
+    hi_g = lo_g + base + (1 if rank < extra else 0)
+    return min(lo_g * multiple, total), min(hi_g * multiple, total)
+
+
+def all_shard_ranges(total: int, world: int, multiple: int = 8) -> List[Tuple[int, int]]:
+    return [shard_range(total, world, r, multiple) for r in range(world)]
+
+
+# ------------------------------------------------------------------------------------------------
+# autograd-aware collectives
+# ------------------------------------------------------------------------------------------------
+def _gather_blocks(x: torch.Tensor, sizes: Sequence[int], dim: int, group) -> List[torch.Tensor]:
+    """all_gather of blocks whose extent along ``dim`` differs per rank (padded to the largest)."""
+    big = max(sizes)
+    if x.shape[dim] != big:
+        pad_shape = list(x.shape)
+        pad_shape[dim] = big - x.shape[dim]
+        x = torch.cat([x, x.new_zeros(pad_shape)], dim=dim)
+    parts = [torch.empty_like(x) for _ in sizes]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return [p.narrow(dim, 0, n) for p, n in zip(parts, sizes)]
+
+
+class _AllGatherCols(torch.autograd.Function):
+    """Concatenate per-rank column blocks [T, n_r] into [T, sum n_r]; backward keeps this rank's block."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, sizes: Sequence[int], group):
+        ctx.group, ctx.sizes = group, list(sizes)
+        ctx.rank = dist.get_rank(group)
+        return torch.cat(_gather_blocks(x, sizes, 1, group), dim=1)
+
+    @staticmethod
+    def backward(ctx, grad):
+        lo = sum(ctx.sizes[:ctx.rank])
+        return grad[:, lo:lo + ctx.sizes[ctx.rank]].contiguous(), None, None
+
+
+class _AllGatherRows(torch.autograd.Function):
+    """Concatenate per-rank row blocks [t_r, R] into [sum t_r, R]; backward sums the gradient over ranks
+    (every rank consumed the full gathered tensor) and keeps this rank's rows."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, sizes: Sequence[int], group):
+        ctx.group, ctx.sizes = group, list(sizes)
+        ctx.rank = dist.get_rank(group)
+        return torch.cat(_gather_blocks(x, sizes, 0, group), dim=0)
+
+    @staticmethod
+    def backward(ctx, grad):
+        grad = grad.contiguous()
+        dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=ctx.group)
+        lo = sum(ctx.sizes[:ctx.rank])
+        return grad[lo:lo + ctx.sizes[ctx.rank]].contiguous(), None, None
+
+
+def all_gather_cols(x: torch.Tensor, sizes: Sequence[int], group=None) -> torch.Tensor:
+    return _AllGatherCols.apply(x, sizes, group)
+
+
+def all_gather_rows(x: torch.Tensor, sizes: Sequence[int], group=None) -> torch.Tensor:
+    return _AllGatherRows.apply(x, sizes, group)
+
+
+# ------------------------------------------------------------------------------------------------
+# row-sharded virtual layer
+# ------------------------------------------------------------------------------------------------
+def _default_local_linear(x, coef, seed, n_local, row0):
+    from . import ops
+    return ops.rlinear(x, coef, seed, n_local, row0)
+
+
+class RowShardedRandumbLinear(torch.nn.Module):
+    """Rank-local part of a virtual layer with ``out_features`` rows split over the process group.
+
+    forward(x) with x replicated on every rank returns this rank's columns ``y[:, lo:hi]`` (the
+    column-parallel convention) or, with ``gather_output=True``, the full ``y`` after an all-gather of
+    the activations.  ``coef`` is replicated; its gradient is the sum over ranks of the local
+    contributions (``allreduce_coef_grads``), as is the gradient of the replicated input.
+    """
+
+    def __init__(self, in_features: int, out_features: int, d_c: int, seed: int, group=None, gather_output: bool = False,
+                 device=None, dtype=None, init_std: Optional[float] = None,
+                 local_linear: Callable = _default_local_linear):
+        super().__init__()
+        from .layers import coef_std_for, kaiming_out_std
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.in_features, self.out_features, self.d_c, self.seed = in_features, out_features, d_c, int(seed)
+        self.ranges = all_shard_ranges(out_features, self.world)
+        self.row_lo, self.row_hi = self.ranges[self.rank]
+        self.gather_output = gather_output
+        self.local_linear = local_linear
+        self.weight_coef = torch.nn.Parameter(torch.empty((d_c, in_features), device=device, dtype=dtype))
+        std = coef_std_for(init_std if init_std is not None else kaiming_out_std(in_features), d_c)
+        gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed & 0x7FFFFFFFFFFFFFFF)
+        with torch.no_grad():
+            self.weight_coef.normal_(0.0, std, generator=gen)  # same seed on every rank => identical replicas
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.local_linear(x, self.weight_coef, self.seed, self.row_hi - self.row_lo, self.row_lo)
+        if self.gather_output and self.world > 1:
+            lead = y.shape[:-1]
+            y2 = all_gather_cols(y.reshape(-1, y.shape[-1]), [hi - lo for lo, hi in self.ranges], self.group)
+            y = y2.reshape(*lead, self.out_features)
+        return y
+
+
+# ------------------------------------------------------------------------------------------------
+# gradient exchange
+# ------------------------------------------------------------------------------------------------
+def allreduce_coef_grads(params: Sequence[torch.nn.Parameter], group=None, average: bool = True,
+                         comm_dtype: Optional[torch.dtype] = None) -> int:
+    """One flat all-reduce over the gradients of ``params``; returns the bytes sent per rank.
+
+    The coefficient matrices are small (d_c x in_features each), so all of them are packed into a
+    single bucket: one launch, one NVLink/NVSwitch reduction.
+    """
+    grads = [p.grad for p in params if p.grad is not None]
+    if not grads:
+        return 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    dt = comm_dtype or grads[0].dtype
+    flat = torch.cat([g.reshape(-1).to(dt) for g in grads])
+    if world > 1:
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        if average:
+            flat /= world
+    off = 0
+    for g in grads:
+        n = g.numel()
+        g.copy_(flat[off:off + n].view_as(g))
+        off += n
+    return flat.numel() * flat.element_size()

@@ -1,0 +1,231 @@
+"""Parity of the layer's CUDA kernels (through the C ABI) with the CPU oracle.
+
+Tolerances: float32 -- rel-Frobenius <= 1e-5 and allclose(rtol=1e-5, atol=1e-5*rms) against a float64
+oracle on the same float32 inputs; bf16 -- the same two tests with 2e-2 against a float32 oracle on the
+bf16-rounded inputs and the unrounded float32 noise.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+BF16_TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def K():
+    from randumb_b200 import kernels
+    assert torch.cuda.is_available()
+    return kernels
+
+
+def _inputs(T, Kin, N, R, dtype, seed=0, coef_scale=None):
+    g = torch.Generator().manual_seed(1000 + seed)
+    x = torch.randn(T, Kin, generator=g)
+    scale = coef_scale if coef_scale is not None else (3.0 / (R * Kin)) ** 0.5
+    C = torch.randn(R, Kin, generator=g) * scale
+    dy = torch.randn(T, N, generator=g)
+    return x.to(dtype), C.to(dtype), dy.to(dtype)
+
+
+def _check(K, T, Kin, N, R, dtype, seed, row0, path, impl, tol):
+    x, C, dy = _inputs(T, Kin, N, R, dtype, seed)
+    odt = torch.float64 if dtype == torch.float32 else torch.float32
+    y, dx, dc = O.linear_reference(x, C, seed, N, row0, dy, dtype=odt)
+    yg = K.linear_fwd(x.cuda(), C.cuda(), seed, N, row0, path=path, impl=impl)
+    dxg, dcg = K.linear_bwd(dy.cuda(), x.cuda(), C.cuda(), seed, row0, path=path, impl=impl)
+    torch.cuda.synchronize()
+    K.check_status()
+    assert yg.dtype == dtype and dxg.dtype == dtype and dcg.dtype == dtype
+    assert O.close(yg, y, tol), f"y rel {O.rel_fro(yg, y):.3e}"
+    assert O.close(dxg, dx, tol), f"dx rel {O.rel_fro(dxg, dx):.3e}"
+    assert O.close(dcg, dc, tol), f"dc rel {O.rel_fro(dcg, dc):.3e}"
+
+
+# ---- float32 (CUDA cores) -------------------------------------------------------------------------
+@pytest.mark.parametrize("T,Kin,N,R,seed,row0,path", [
+    (64, 784, 256, 64, 0, 0, 0),      # MNIST-shaped layer 1 (factored)
+    (64, 256, 10, 64, 1, 0, 0),       # MNIST-shaped head: the W path is cheaper and is chosen
+    (64, 256, 10, 64, 1, 0, 1),       # same, forced factored
+    (33, 70, 45, 9, 5, 7, 2), (33, 70, 45, 9, 5, 7, 1),   # ragged everything, both associations
+    (5, 8, 300, 16, 3, 0, 0), (1, 1, 1, 1, 2, 0, 0), (2, 3, 5, 1, 2, 4, 2)])
+def test_f32_layer(K, T, Kin, N, R, seed, row0, path):
+    _check(K, T, Kin, N, R, torch.float32, seed, row0, path, K.IMPL_AUTO, F32_TOL)
+
+
+@pytest.mark.parametrize("Kin,N,R,seed", [(4096, 4096, 256, 42), (100, 37, 5, 1), (4098, 513, 33, 9)])
+def test_f32_gemv(K, Kin, N, R, seed):
+    """Batch-1: the matrix-vector kernels (also what rdb_linear_* dispatches to for T == 1)."""
+    x, C, dy = _inputs(1, Kin, N, R, torch.float32, seed)
+    y, dx, dc = O.linear_reference(x, C, seed, N, 0, dy)
+    yg = K.gemv_fwd(x.cuda().view(-1), C.cuda(), seed, N)
+    dxg, dcg = K.gemv_bwd(dy.cuda().view(-1), x.cuda().view(-1), C.cuda(), seed)
+    assert O.close(yg.view(1, -1), y, F32_TOL) and O.close(dxg.view(1, -1), dx, F32_TOL) and O.close(dcg, dc, F32_TOL)
+    y2 = K.linear_fwd(x.cuda(), C.cuda(), seed, N)
+    dx2, dc2 = K.linear_bwd(dy.cuda(), x.cuda(), C.cuda(), seed)
+    assert torch.equal(y2.view(-1), yg) and torch.equal(dx2.view(-1), dxg) and torch.equal(dc2, dcg)
+    dx3, none = K.gemv_bwd(dy.cuda().view(-1), x.cuda().view(-1), C.cuda(), seed, need_dc=False)
+    assert none is None and torch.equal(dx3, dxg)
+
+
+# ---- bf16 on tensor cores --------------------------------------------------------------------------
+@pytest.mark.parametrize("T,Kin,N,R,seed,row0", [
+    (512, 256, 384, 128, 42, 0),
+    (1000, 264, 520, 72, 7, 1000),     # nothing a multiple of the tile
+    (8, 8, 8, 8, 3, 0),                # smallest shape the tensor-core path takes
+    (130, 4096, 136, 1024, 5, 65530),  # long contractions, noise rows around 2^16
+    (1024, 768, 3072, 128, 13, 0),     # GPT-2-small MLP up-projection shape (tokens reduced)
+])
+def test_bf16_layer_tensor_cores(K, T, Kin, N, R, seed, row0):
+    _check(K, T, Kin, N, R, torch.bfloat16, seed, row0, K.PATH_FACTORED, K.IMPL_UMMA, BF16_TOL)
+
+
+@pytest.mark.parametrize("opt", [(1, 1), (2, 1)])
+def test_bf16_layer_alternative_kernel_settings(K, opt):
+    key, val = opt
+    prev = K.set_option(key, val)
+    try:
+        _check(K, 700, 264, 520, 72, torch.bfloat16, 7, 10, K.PATH_FACTORED, K.IMPL_UMMA, BF16_TOL)
+    finally:
+        K.set_option(key, prev)
+
+
+@pytest.mark.parametrize("T,Kin,N,R,seed,row0,path", [(64, 80, 96, 16, 0, 0, 0), (33, 70, 45, 9, 5, 7, 2), (33, 70, 45, 9, 5, 7, 1)])
+def test_bf16_layer_any_shape_path(K, T, Kin, N, R, seed, row0, path):
+    """Shapes the tensor-core kernels refuse (odd extents) run on the CUDA-core kernels."""
+    _check(K, T, Kin, N, R, torch.bfloat16, seed, row0, path, K.IMPL_AUTO, BF16_TOL)
+
+
+def test_umma_refuses_unaligned_shapes(K):
+    x, C, _ = _inputs(33, 70, 45, 9, torch.bfloat16)
+    with pytest.raises(RuntimeError, match="not supported"):
+        K.linear_fwd(x.cuda(), C.cuda(), 0, 45, impl=K.IMPL_UMMA)
+
+
+# ---- building blocks ----------------------------------------------------------------------------------
+def test_generated_operand_is_the_noise_matrix(K):
+    """With A = I the product returns the generated tile itself: element-exact layout check."""
+    A = torch.eye(128, 64).bfloat16().cuda()
+    d = K.gemm_noise(A, 256, 11, False, 5, impl=K.IMPL_UMMA).cpu()
+    G = O.noise_bf16(256, 64, 11, row0=5)
+    assert torch.equal(d[:64], G.t().contiguous()) and float(d[64:].abs().max()) == 0.0
+    dt = K.gemm_noise(A, 256, 11, True, 5, impl=K.IMPL_UMMA).cpu()        # G[n, k] = S[row0 + k, n]
+    Gt = O.noise_bf16(64, 256, 11, row0=5)
+    assert torch.equal(dt[:64], Gt)
+
+
+@pytest.mark.parametrize("akm,bkm", [(True, True), (True, False), (False, True), (False, False)])
+@pytest.mark.parametrize("out", [torch.bfloat16, torch.float32])
+def test_dense_products_all_operand_layouts(K, akm, bkm, out):
+    g = torch.Generator().manual_seed(4)
+    M, N, Kc = 1000, 520, 328
+    A = torch.randn(M, Kc, generator=g).bfloat16()
+    B = torch.randn(N, Kc, generator=g).bfloat16()
+    ref = A.float() @ B.float().t()
+    a = (A if akm else A.t().contiguous()).cuda()
+    b = (B if bkm else B.t().contiguous()).cuda()
+    d = K.gemm_dense(a, b, akm, bkm, out_dtype=out, impl=K.IMPL_UMMA)
+    K.check_status()
+    assert O.close(d, ref, 1e-2 if out == torch.bfloat16 else 1e-5)
+    d2 = K.gemm_dense(a, b, akm, bkm, out_dtype=out, impl=K.IMPL_SIMT)
+    assert O.close(d2, ref, 1e-2 if out == torch.bfloat16 else 1e-5)
+
+
+def test_transposed_output_of_generated_product(K):
+    g = torch.Generator().manual_seed(5)
+    A = torch.randn(600, 1000, generator=g).bfloat16().cuda()
+    d, dt = K.gemm_noise(A, 136, 11, True, 0, impl=K.IMPL_UMMA, want_transpose=True)
+    assert torch.equal(d.t().contiguous(), dt)
+
+
+# ---- edge cases ----------------------------------------------------------------------------------------
+def test_empty_and_degenerate(K):
+    dev = "cuda"
+    C = torch.randn(4, 8, device=dev)
+    assert K.linear_fwd(torch.empty(0, 8, device=dev), C, 0, 16).shape == (0, 16)
+    assert K.linear_fwd(torch.randn(3, 8, device=dev), C, 0, 0).shape == (3, 0)
+    y = K.linear_fwd(torch.randn(3, 8, device=dev), torch.empty(0, 8, device=dev), 0, 5)   # d_c == 0 -> W == 0
+    assert float(y.abs().max()) == 0.0
+    dx, dc = K.linear_bwd(torch.empty(0, 16, device=dev), torch.empty(0, 8, device=dev), C, 0)
+    assert dx.shape == (0, 8) and dc.shape == (4, 8) and float(dc.abs().max()) == 0.0
+    with pytest.raises(RuntimeError):
+        K.linear_fwd(torch.randn(3, 7, device=dev), C, 0, 16)                                  # K mismatch
+    with pytest.raises(RuntimeError):
+        K.linear_fwd(torch.randn(3, 8, device=dev).double(), C.double(), 0, 16)                # dtype
+
+
+def test_row_sharded_outputs_equal_the_unsharded_layer(K):
+    """A rank that owns rows [row0, row0+n) computes exactly the same numbers as the full layer."""
+    x, C, dy = _inputs(256, 128, 512, 64, torch.bfloat16, 3)
+    xg, Cg, dyg = x.cuda(), C.cuda(), dy.cuda()
+    y = K.linear_fwd(xg, Cg, 7, 512)
+    parts = [K.linear_fwd(xg, Cg, 7, 128, row0=128 * r) for r in range(4)]
+    assert torch.equal(torch.cat(parts, dim=1), y)
+    dx, dc = K.linear_bwd(dyg, xg, Cg, 7)
+    dxs = [K.linear_bwd(dyg[:, 128 * r:128 * (r + 1)].contiguous(), xg, Cg, 7, row0=128 * r) for r in range(4)]
+    assert O.close(sum(p[0].float() for p in dxs), dx.float(), BF16_TOL)
+    assert O.close(sum(p[1].float() for p in dxs), dc.float(), BF16_TOL)
+
+
+def test_run_to_run_reproducible(K):
+    x, C, dy = _inputs(700, 264, 520, 72, torch.bfloat16, 9)
+    a = K.linear_fwd(x.cuda(), C.cuda(), 1, 520)
+    b = K.linear_fwd(x.cuda(), C.cuda(), 1, 520)
+    assert torch.equal(a, b)
+    d1 = K.linear_bwd(dy.cuda(), x.cuda(), C.cuda(), 1)
+    d2 = K.linear_bwd(dy.cuda(), x.cuda(), C.cuda(), 1)
+    assert torch.equal(d1[0], d2[0]) and torch.equal(d1[1], d2[1])
+
+
+# ---- full benchmark size: properties that do not need the oracle at that size ---------------------------
+def test_full_size_properties(K):
+    """8192 x 4096 -> 16384, d_c = 1024 (the headline configuration)."""
+    T, Kin, N, R, seed = 8192, 4096, 16384, 1024, 42
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(T, Kin, device="cuda", generator=g).bfloat16()
+    C = (torch.randn(R, Kin, device="cuda", generator=g) * (3 * 0.02 ** 2 / R) ** 0.5).bfloat16()
+    dy = torch.randn(T, N, device="cuda", generator=g).bfloat16()
+    y = K.linear_fwd(x, C, seed, N)
+    dx, dc = K.linear_bwd(dy, x, C, seed)
+    torch.cuda.synchronize()
+    K.check_status()
+    # (1) a slab of output rows equals the same slab computed as its own (small) problem, against the oracle
+    rows = slice(4096, 4096 + 24)
+    y_ref, _, _ = O.linear_reference(x[:64].cpu(), C.cpu(), seed, 24, row0=4096, dtype=torch.float32)
+    assert O.close(y[:64, rows], y_ref, BF16_TOL)
+    # (2) <dy, y> == <dx, x> == <dc, C>  (adjoint identity of a linear map, up to bf16 rounding)
+    ip_y = float((dy.float() * y.float()).sum())
+    ip_x = float((dx.float() * x.float()).sum())
+    ip_c = float((dc.float() * C.float()).sum())
+    scale = float(dy.float().norm() * y.float().norm())
+    assert abs(ip_y - ip_x) / scale < 2e-3 and abs(ip_y - ip_c) / scale < 2e-3
+    # (3) token shards reproduce the full result exactly (tiles do not interact across tokens)
+    y_half = K.linear_fwd(x[:4096].contiguous(), C, seed, N)
+    assert torch.equal(y_half, y[:4096])
+
+
+# ---- the reference's 1-D coefficient form -------------------------------------------------------------------
+def test_materialize_against_reference_kernel_outputs(K, golden):
+    coef = torch.from_numpy(golden["matfwd_coef"]).cuda()
+    got = K.materialize_fwd(coef, [18, 18], [18, 1], 1337).cpu().numpy()
+    np.testing.assert_allclose(got, golden["matfwd_18x18_contig_seed1337"], atol=3e-6)
+    got = K.materialize_fwd(coef, [18, 10], [1, 18], 5).cpu().numpy()
+    np.testing.assert_allclose(got, golden["matfwd_18x10_transposed_seed5"], atol=3e-6)
+    got = K.materialize_fwd(coef, [70], [1], 42).cpu().numpy()
+    np.testing.assert_allclose(got, golden["matfwd_70x1_seed42"].ravel(), atol=3e-6)
+    dout = torch.from_numpy(golden["matbwd_dout"]).cuda()
+    got = K.materialize_bwd(dout, 24, 1337).cpu().numpy()
+    np.testing.assert_allclose(got, golden["matbwd_333_M24_seed1337"], atol=2e-5)
+    # larger, against the oracle
+    coef2 = torch.randn(300, generator=torch.Generator().manual_seed(1))
+    want = O.materialize_fwd(coef2.numpy(), 40, 50, 50, 1, 3)
+    got = K.materialize_fwd(coef2.cuda(), [40, 50], [50, 1], 3).cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+    dout2 = torch.randn(20000, generator=torch.Generator().manual_seed(2))
+    want = O.materialize_bwd(dout2.numpy(), 37, 8)
+    got = K.materialize_bwd(dout2.cuda(), 37, 8).cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-3)

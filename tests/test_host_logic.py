@@ -1,0 +1,113 @@
+"""Host-side mirror of the reference interface: operator schemas, the tensor subclass's metadata
+handling, module conventions, sharding arithmetic.  CPU only -- no kernel runs here."""
+import math
+
+import pytest
+import torch
+
+import randumb_b200 as rb
+from randumb_b200 import parallel
+from randumb_b200.tensor import RandumbTensor
+
+
+def test_operator_schemas_match_reference_names():
+    s = str(torch.ops.rten.materialize_fwd.default._schema)
+    assert s == ("rten::materialize_fwd(Tensor coefs, SymInt[] size, SymInt[] strides, SymInt seed, "
+                 "Tensor? scale_bias, bool fused_bias) -> Tensor")
+    assert str(torch.ops.rten.materialize_bwd.default._schema) == \
+        "rten::materialize_bwd(Tensor dout, SymInt dcoefs_size, SymInt seed) -> Tensor"
+    assert "rten::rlinear_fwd(Tensor x, Tensor coef, SymInt seed, SymInt out_features, SymInt row0=0) -> Tensor" == \
+        str(torch.ops.rten.rlinear_fwd.default._schema)
+    assert str(torch.ops.rten_cpp.sq5_gen_2d.default._schema) == "rten_cpp::sq5_gen_2d(SymInt M, SymInt N, SymInt seed) -> Tensor"
+    assert str(torch.ops.rten_cpp.materialize_fwd.default._schema).startswith("rten_cpp::materialize_fwd(Tensor coef, SymInt seed, SymInt P")
+
+
+def test_cpu_calls_raise_like_the_reference():
+    with pytest.raises(NotImplementedError, match="Unsupported CPU implementation"):
+        rb.ops.rlinear_fwd(torch.ones(2, 3), torch.ones(4, 3), 0, 5)
+    with pytest.raises(NotImplementedError, match="Unsupported CPU implementation"):
+        rb.ops.materialize_bwd(torch.ones(6), 3, 0)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        rb.kernels.linear_fwd(torch.ones(2, 3), torch.ones(4, 3), 0, 5)
+
+
+def test_fake_tensor_tracing_gives_shapes():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        x = torch.empty(6, 5, 3, device="cuda")
+        c = torch.empty(4, 3, device="cuda")
+        assert rb.rlinear(x, c, 0, 7).shape == (6, 5, 7)
+        dx, dc = rb.ops.rlinear_bwd(torch.empty(30, 7, device="cuda"), x.reshape(30, 3), c, 0, 0, True, False)
+        assert dx.shape == (30, 3) and dc.numel() == 0
+
+
+def test_randumb_tensor_metadata_and_views():
+    coef = torch.zeros(8, 16)
+    rt = rb.CreateRandumbTensor(coef, 5, (24, 16))
+    assert isinstance(rt, RandumbTensor) and rt.is_matrix_form
+    assert rt.noise_matrix_shape == (24, 8) and rt.int_dim == 8
+    t = rt.t()
+    assert isinstance(t, RandumbTensor) and t.shape == (16, 24) and t.stride() == (1, 16)
+    assert t._is_transposed() and t.noise_matrix_shape == (24, 8)
+    h = rt.to(torch.bfloat16)
+    assert isinstance(h, RandumbTensor) and h.dtype == torch.bfloat16 and h._coef.dtype == torch.bfloat16
+    with pytest.raises(AssertionError):
+        rb.CreateRandumbTensor(torch.zeros(8, 15), 5, (24, 16))        # coef columns != in_features
+    # reference form: 1-D coefficient, any shape, views keep working
+    r1 = rb.CreateRandumbTensor(torch.zeros(6), 3, (4, 10))
+    assert not r1.is_matrix_form and r1.noise_matrix_shape == (40, 6)
+    v = r1.view(8, 5).transpose(0, 1)
+    assert isinstance(v, RandumbTensor) and v.shape == (5, 8) and v.stride() == (1, 5)
+    with pytest.raises(Exception):
+        v.view(40)                                                       # incompatible view is refused
+
+
+def test_constructor_edge_tracks_coef():
+    coef = torch.nn.Parameter(torch.zeros(8, 16))
+    rt = rb.CreateRandumbTensor(coef, 5, (24, 16))
+    assert rt.requires_grad and rt.grad_fn is not None
+
+
+def test_seed_generators():
+    g = rb.stepgen(13, 7)
+    assert [next(g) for _ in range(4)] == [13, 20, 27, 34]
+    assert list(rb.listgen([3, 1, 2])) == [3, 1, 2]
+
+
+def test_randumb_linear_init_and_state():
+    m = rb.RandumbLinear(784, 256, 64, seed=0)
+    assert m.weight_coef.shape == (64, 784)
+    # coef ~ N(0, 3 std^2 / d_c) with std^2 = 1/(3 fan_in)
+    want = math.sqrt(3.0 / 64) * math.sqrt(1.0 / (3 * 784))
+    assert abs(float(m.weight_coef.detach().std()) - want) / want < 0.05
+    m2 = rb.RandumbLinear(784, 256, 64, seed=0)
+    assert torch.equal(m.weight_coef, m2.weight_coef)                    # init is a function of the seed
+    sd = m.state_dict()
+    assert set(sd.keys()) == {"weight_coef", "_extra_state"} and sd["_extra_state"]["seed"] == 0
+    m3 = rb.RandumbLinear(784, 256, 64, seed=9)
+    m3.load_state_dict(sd)
+    assert m3.seed == 0 and torch.equal(m3.weight_coef, m.weight_coef) and m3.weight.seed == 0
+    m3.to(torch.bfloat16)
+    assert m3.weight.dtype == torch.bfloat16 and m3.weight._coef is m3.weight_coef
+
+
+def test_silly_linear_conventions():
+    s = rb.SillyLinear(16, 24, rb.stepgen(8, 0), rb.stepgen(13, 7))
+    assert s.int_dim == [8, 8] and s.seed == [13, 20]
+    assert s.weight_coef.shape == (8, 16) and s.bias_coef.shape == (8,)
+    assert s.weight.seed == 13 and s.bias.seed == 20 and not s.bias.is_matrix_form
+    assert {n for n, _ in s.named_parameters()} == {"weight_coef", "bias_coef"}
+    s2 = rb.SillyLinear(16, 24, [4, 2], [1, 2], bias=False)
+    assert s2.bias is None
+
+
+@pytest.mark.parametrize("total,world", [(65536, 8), (16384, 4), (1000, 3), (8, 8), (10, 4), (0, 2)])
+def test_shard_ranges_partition(total, world):
+    rs = parallel.all_shard_ranges(total, world)
+    assert rs[0][0] == 0 and rs[-1][1] == total
+    for (a, b), (c, d) in zip(rs, rs[1:]):
+        assert b == c and a <= b
+    for lo, hi in rs[:-1]:
+        assert (lo % 8 == 0 or lo == total) and (hi % 8 == 0 or hi == total)
+    sizes = [hi - lo for lo, hi in rs]
+    assert max(sizes) - min(sizes) <= 8
