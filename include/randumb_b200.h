@@ -60,6 +60,8 @@ extern "C" {
 #define RDB_ERR_UNSUPPORTED -6
 #define RDB_ERR_DRIVER -7
 #define RDB_ERR_TOO_LARGE -8
+/* tensor-map encoding rejected by the driver: the code is RDB_ERR_DRIVER_BASE - CUresult */
+#define RDB_ERR_DRIVER_BASE -1000
 
 /* device-side give-up codes written to status[0] */
 #define RDB_STATUS_TIMEOUT_PRODUCER 1
@@ -72,14 +74,15 @@ const char *rdb_strerror(int code);
 
 /*
  * Process-wide tuning switches (not part of the reference surface; defaults are the tuned ones).
- *   RDB_OPT_NOISE_TILE   0: generated tile 128 noise rows reused by 512 tokens (default)
- *                        1: generated tile 256 noise rows reused by 256 tokens
- *   RDB_OPT_BWD_OPERANDS 0: dX / dC read C, g and x in place through MN-major MMA descriptors (default)
- *                        1: explicit transposed copies in workspace, K-major descriptors only
+ *   RDB_OPT_NOISE_TILE   work unit of the generated-operand kernel; every hash is reused by
+ *                        (cluster size) x (token sub-tiles) x 128 tokens:
+ *                        0: 1 CTA,  4 sub-tiles, 128 generated rows      1: 1 CTA,  2 sub-tiles, 256 rows
+ *                        2: 2 CTAs, 4 sub-tiles, 128 rows                3: 4 CTAs, 4 sub-tiles, 128 rows
+ *                        4: 4 CTAs, 2 sub-tiles, 256 rows                5: 8 CTAs, 2 sub-tiles, 256 rows
+ *                        (CTAs of a cluster share each generated stage through distributed shared memory)
  * Returns the previous value, or RDB_ERR_UNSUPPORTED for an unknown key.
  */
 #define RDB_OPT_NOISE_TILE 1
-#define RDB_OPT_BWD_OPERANDS 2
 int rdb_set_option(int key, int value);
 
 /*

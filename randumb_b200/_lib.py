@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "librandumb_b200.so")
 F32, BF16 = 0, 1
 PATH_AUTO, PATH_FACTORED, PATH_WPATH = 0, 1, 2
 IMPL_AUTO, IMPL_SIMT, IMPL_UMMA = 0, 1, 2
-OPT_NOISE_TILE, OPT_BWD_OPERANDS = 1, 2
+OPT_NOISE_TILE = 1
 STATUS_NAMES = {0: "ok", 1: "producer wait expired", 2: "mma wait expired", 3: "epilogue wait expired",
                 4: "generator wait expired"}
 

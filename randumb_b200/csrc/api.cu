@@ -1,39 +1,11 @@
 // C-ABI entry points of the layer: argument checks, association/kernel choice, workspace carving.
+#include <cstdio>
+
 #include "common.cuh"
 
 namespace rdb {
 
-static int g_bwd_operands = 0;  // RDB_OPT_BWD_OPERANDS
 static int g_noise_tile = 0;    // RDB_OPT_NOISE_TILE
-
-// dst[c, r] = src[r, c]  (bf16), 32x32 tiles through shared memory.
-__global__ void transpose_bf16_kernel(__nv_bfloat16 *__restrict__ dst, int64_t ldd, const __nv_bfloat16 *__restrict__ src,
-                                      int64_t lds, int64_t rows, int64_t cols) {
-    __shared__ __nv_bfloat16 tile[32][34];
-    const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
-    for (int i = threadIdx.y; i < 32; i += 8) {
-        const int64_t r = r0 + i, c = c0 + threadIdx.x;
-        if (r < rows && c < cols) tile[i][threadIdx.x] = src[r * lds + c];
-    }
-    __syncthreads();
-    for (int i = threadIdx.y; i < 32; i += 8) {
-        const int64_t c = c0 + i, r = r0 + threadIdx.x;
-        if (r < rows && c < cols) dst[c * ldd + r] = tile[threadIdx.x][i];
-    }
-}
-
-static int transpose_bf16(void *dst, int64_t ldd, const void *src, int64_t lds, int64_t rows, int64_t cols, cudaStream_t st) {
-    if (rows == 0 || cols == 0) return RDB_OK;
-    const int64_t gx = cdiv64(cols, 32), gy = cdiv64(rows, 32);
-    if (gy > 65535) {
-        // fold the row tiles into x when there are too many for gridDim.y
-        return RDB_ERR_TOO_LARGE;
-    }
-    dim3 grid((unsigned)gx, (unsigned)gy), block(32, 8);
-    transpose_bf16_kernel<<<grid, block, 0, st>>>(reinterpret_cast<__nv_bfloat16 *>(dst), ldd,
-                                                 reinterpret_cast<const __nv_bfloat16 *>(src), lds, rows, cols);
-    return launch_status();
-}
 
 // FLOP-count rule: factored costs 2TR(K+N) per result, the W path 2NRK + 2TNK.
 static int choose_path(int path, int64_t T, int64_t K, int64_t N, int64_t R) {
@@ -64,7 +36,7 @@ struct WsLayout {
 
 // Workspace segments (each 1024-byte aligned):
 //   UMMA factored  fwd: z bf16[T,R]
-//                  bwd: g bf16[T,R] (+ gT bf16[R,T], xT bf16[K,T], cT bf16[K,R] when explicit transposes are on)
+//                  bwd: g bf16[T,R]
 //   SIMT factored  fwd: z f32[T,R]           bwd: g f32[T,R]
 //   SIMT W path    fwd: W f32[N,K]           bwd: W f32[N,K], dW f32[N,K]
 static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, int path, int impl) {
@@ -73,11 +45,6 @@ static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, in
     if (path == RDB_PATH_FACTORED) {
         if (impl == RDB_IMPL_UMMA) {
             seg[0] = (size_t)T * R * 2;
-            if (op == 1 && g_bwd_operands == 1) {
-                seg[1] = (size_t)R * T * 2;
-                seg[2] = (size_t)K * T * 2;
-                seg[3] = (size_t)K * R * 2;
-            }
         } else {
             seg[0] = (size_t)T * R * 4;
         }
@@ -114,6 +81,11 @@ extern "C" const char *rdb_strerror(int code) {
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    if (code <= RDB_ERR_DRIVER_BASE && code > RDB_ERR_DRIVER_BASE - 1000) {
+        static thread_local char buf[96];
+        snprintf(buf, sizeof(buf), "tensor-map encoding rejected by the driver (CUresult %d)", RDB_ERR_DRIVER_BASE - code);
+        return buf;
+    }
     return "unknown error";
 }
 
@@ -122,12 +94,8 @@ extern "C" int rdb_set_option(int key, int value) {
     switch (key) {
         case RDB_OPT_NOISE_TILE:
             prev = g_noise_tile;
-            g_noise_tile = value ? 1 : 0;
+            g_noise_tile = (value >= 0 && value <= 5) ? value : 0;
             set_noise_cfg(g_noise_tile);
-            return prev;
-        case RDB_OPT_BWD_OPERANDS:
-            prev = g_bwd_operands;
-            g_bwd_operands = value ? 1 : 0;
             return prev;
         default: return RDB_ERR_UNSUPPORTED;
     }
@@ -269,33 +237,15 @@ extern "C" int rdb_linear_bwd(void *dx, void *dc, const void *dy, const void *x,
     if (p == RDB_PATH_FACTORED) {
         if (im == RDB_IMPL_UMMA) {
             void *g = ws + w.off[0];
-            if (g_bwd_operands == 0) {
-                // g = dY S ; dX = g C (C read as an MN-major B operand) ; dC = g^T x (both MN-major)
-                rc = umma_gemm_noise(g, nullptr, dy, T, R, N, N, R, 0, cols, status, st);
-                if (rc) return rc;
-                if (dx) {
-                    rc = umma_gemm_dense(dx, g, coef, T, K, R, R, K, K, RDB_BF16, 1, 0, status, st);
-                    if (rc) return rc;
-                }
-                if (dc) {
-                    rc = umma_gemm_dense(dc, g, x, R, K, T, R, K, K, RDB_BF16, 0, 0, status, st);
-                    if (rc) return rc;
-                }
-                return RDB_OK;
-            }
-            void *gT = ws + w.off[1], *xT = ws + w.off[2], *cT = ws + w.off[3];
-            rc = umma_gemm_noise(g, dc ? gT : nullptr, dy, T, R, N, N, R, T, cols, status, st);
+            // g = dY S ; dX = g C (C read in place as an MN-major B operand) ; dC = g^T x (both operands MN-major)
+            rc = umma_gemm_noise(g, nullptr, dy, T, R, N, N, R, 0, cols, status, st);
             if (rc) return rc;
             if (dx) {
-                rc = transpose_bf16(cT, R, coef, K, R, K, st);
-                if (rc) return rc;
-                rc = umma_gemm_dense(dx, g, cT, T, K, R, R, R, K, RDB_BF16, 1, 1, status, st);
+                rc = umma_gemm_dense(dx, g, coef, T, K, R, R, K, K, RDB_BF16, 1, 0, status, st);
                 if (rc) return rc;
             }
             if (dc) {
-                rc = transpose_bf16(xT, T, x, K, T, K, st);
-                if (rc) return rc;
-                rc = umma_gemm_dense(dc, gT, xT, R, K, T, T, T, K, RDB_BF16, 1, 1, status, st);
+                rc = umma_gemm_dense(dc, g, x, R, K, T, R, K, K, RDB_BF16, 0, 0, status, st);
                 if (rc) return rc;
             }
             return RDB_OK;

@@ -23,6 +23,8 @@
 // flag, writes a code to status[0] and all roles fall through to the common teardown, which
 // releases TMEM.
 #include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "umma.cuh"
@@ -83,7 +85,7 @@ __device__ __forceinline__ void raise_abort(volatile int *abort_flag, int32_t *s
 // ================================================================================================
 // noise_gemm_kernel
 // ================================================================================================
-template <int MT, int BN, int SA, int SB>
+template <int CS, int MT, int BN, int SA, int SB>
 struct NoiseCfg {
     static constexpr int A_STAGE = MT * SUB_BYTES;
     static constexpr int B_STAGE = BN * BK * 2;
@@ -93,17 +95,23 @@ struct NoiseCfg {
     static constexpr int FIRST_EPI_WARP = 2;
     static constexpr int FIRST_GEN_WARP = 6;
     static constexpr int SMEM_DYN = SA * A_STAGE + SB * B_STAGE + 1024;
+    static constexpr int ROWS_PER_CTA = BN / CS;                       // noise rows of a stage this CTA generates
+    static constexpr int CHUNKS = (ROWS_PER_CTA * 8) / GEN_THREADS;    // 16-byte chunks per generator thread per stage
     static_assert(MT * BN <= TMEM_COLS, "accumulators exceed TMEM");
     static_assert(BN % 32 == 0 && BN <= 256, "BN");
-    static_assert((BN * 8) % GEN_THREADS == 0, "generator chunking");
+    static_assert(CS == 1 || CS == 2 || CS == 4 || CS == 8, "cluster size");
+    static_assert(BN % CS == 0 && (ROWS_PER_CTA * 8) % GEN_THREADS == 0 && CHUNKS >= 1, "generator chunking");
 };
 
-template <int MT, int BN, int SA, int SB>
-__global__ void __launch_bounds__(NoiseCfg<MT, BN, SA, SB>::THREADS, 1)
+// CS CTAs of a thread-block cluster work on CS token tiles against the SAME generated operand: each CTA
+// hashes 1/CS of every [BN x 64] stage and stores its part into the shared memory of all CS CTAs
+// (distributed shared memory), so one hash is amortised over CS * MT * 128 tokens.
+template <int CS, int MT, int BN, int SA, int SB>
+__global__ void __launch_bounds__(NoiseCfg<CS, MT, BN, SA, SB>::THREADS, 1)
 noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__restrict__ d, int64_t ldd,
                   __nv_bfloat16 *__restrict__ d_t, int64_t ldd_t, int64_t M, int64_t N, int64_t Kc, Sq5Lin lin,
                   int32_t *status) {
-    using Cfg = NoiseCfg<MT, BN, SA, SB>;
+    using Cfg = NoiseCfg<CS, MT, BN, SA, SB>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full_a[SA], bar_empty_a[SA], bar_full_b[SB], bar_empty_b[SB], bar_tmem_full, bar_tmem_empty;
     __shared__ uint32_t tmem_holder;
@@ -111,17 +119,19 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
 
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
-    uint8_t *smem = smem_raw + pad;
     const uint32_t smem_a = raw_addr + pad;
     const uint32_t smem_b = smem_a + SA * Cfg::A_STAGE;
-    uint8_t *smem_b_gen = smem + SA * Cfg::A_STAGE;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CS > 1) ? cluster_ctarank() : 0u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; ++s) { mbar_init(smem_u32(&bar_full_a[s]), 1); mbar_init(smem_u32(&bar_empty_a[s]), 1); }
-        for (int s = 0; s < SB; ++s) { mbar_init(smem_u32(&bar_full_b[s]), Cfg::GEN_THREADS); mbar_init(smem_u32(&bar_empty_b[s]), 1); }
+        for (int s = 0; s < SB; ++s) {
+            mbar_init(smem_u32(&bar_full_b[s]), CS * Cfg::GEN_WARPS);   // one arrival per generator warp of every CTA
+            mbar_init(smem_u32(&bar_empty_b[s]), CS);                   // one MMA commit from every CTA
+        }
         mbar_init(smem_u32(&bar_tmem_full), 1);
         mbar_init(smem_u32(&bar_tmem_empty), 128);
         abort_flag = 0;
@@ -133,14 +143,20 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (CS > 1) cluster_sync_all();   // peers must see initialised barriers before any remote arrive
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_holder;
     volatile int *abortp = &abort_flag;
 
     const int64_t tiles_n = (N + BN - 1) / BN;
     const int64_t tiles_m = (M + (int64_t)MT * BM - 1) / ((int64_t)MT * BM);
-    const int64_t total_tiles = tiles_m * tiles_n;
+    const int64_t ctiles_m = (tiles_m + CS - 1) / CS;          // cluster tiles along tokens
+    const int64_t total_ctiles = ctiles_m * tiles_n;
+    const int64_t cluster_id = blockIdx.x / CS;
+    const int64_t num_clusters = gridDim.x / CS;
     const int num_kb = (int)((Kc + BK - 1) / BK);
+    // token tile of this CTA inside cluster tile `ct` (may lie past the end: loads zero-fill, stores are masked)
+    auto m_base = [&](int64_t ct) { return ((ct / tiles_n) * CS + cta_rank) * (int64_t)MT * BM; };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (A tiles)
@@ -148,8 +164,8 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             prefetch_tmap(&tmap_a);
             PipeState st;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int64_t m0 = (tile / tiles_n) * (int64_t)MT * BM;
+            for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
+                const int64_t m0 = m_base(ct);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&bar_empty_a[st.idx]), st.phase ^ 1, abortp)) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
@@ -183,19 +199,22 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             PipeState sa, sb;
             uint32_t tphase = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
                 if (!mbar_wait(smem_u32(&bar_tmem_empty), tphase ^ 1, abortp)) {
                     raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
                     break;
                 }
                 tc_fence_after_sync();
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(smem_u32(&bar_full_a[sa.idx]), sa.phase, abortp) ||
-                        !mbar_wait(smem_u32(&bar_full_b[sb.idx]), sb.phase, abortp)) {
+                    const bool got_a = mbar_wait(smem_u32(&bar_full_a[sa.idx]), sa.phase, abortp);
+                    const bool got_b = got_a && (CS > 1 ? mbar_wait_cluster(smem_u32(&bar_full_b[sb.idx]), sb.phase, abortp)
+                                                        : mbar_wait(smem_u32(&bar_full_b[sb.idx]), sb.phase, abortp));
+                    if (!got_b) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
                         ok = false;
                         break;
                     }
+                    if (CS > 1) fence_proxy_async_all();   // peers wrote the stage through the generic proxy
                     tc_fence_after_sync();
                     const uint32_t a_stage = smem_a + sa.idx * Cfg::A_STAGE;
                     const uint32_t b_stage = smem_b + sb.idx * Cfg::B_STAGE;
@@ -209,7 +228,13 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                         }
                     }
                     umma_commit(smem_u32(&bar_empty_a[sa.idx]));
-                    umma_commit(smem_u32(&bar_empty_b[sb.idx]));
+                    // the stage is rewritten by every CTA's generators: tell all of them it is free here
+                    if (CS > 1) {
+#pragma unroll
+                        for (int c = 0; c < CS; ++c) umma_commit(mapa(smem_u32(&bar_empty_b[sb.idx]), (uint32_t)c));
+                    } else {
+                        umma_commit(smem_u32(&bar_empty_b[sb.idx]));
+                    }
                     sa.advance<SA>();
                     sb.advance<SB>();
                 }
@@ -221,9 +246,9 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
         // ------------------------------------------------------------------ epilogue (4 warps)
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         uint32_t tphase = 0;
-        for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            const int64_t m0 = (tile / tiles_n) * (int64_t)MT * BM;
-            const int64_t n0 = (tile % tiles_n) * BN;
+        for (int64_t ct = cluster_id; ct < total_ctiles; ct += num_clusters) {
+            const int64_t m0 = m_base(ct);
+            const int64_t n0 = (ct % tiles_n) * BN;
             if (!mbar_wait(smem_u32(&bar_tmem_full), tphase, abortp)) {
                 raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
                 break;
@@ -256,29 +281,30 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
     } else {
         // ------------------------------------------------------------------ generators (8 warps)
         const int tg = threadIdx.x - Cfg::FIRST_GEN_WARP * 32;
-        constexpr int CHUNKS = (BN * 8) / Cfg::GEN_THREADS;  // 16-byte chunks per thread per stage
+        constexpr int CHUNKS = Cfg::CHUNKS;
         PipeState sb;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int64_t n0 = (tile % tiles_n) * BN;
-            // b0 of this thread's chunks at k-block 0
+        for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
+            const int64_t n0 = (ct % tiles_n) * BN;
+            // hash front end b0 of this thread's chunks at k-block 0, and their swizzled offsets in a stage
             uint32_t bstart[CHUNKS];
             uint32_t soff[CHUNKS];
 #pragma unroll
             for (int c = 0; c < CHUNKS; ++c) {
                 const int id = tg + c * Cfg::GEN_THREADS;
-                const int rowi = id >> 3, ch = id & 7;
+                const int rowi = (int)cta_rank * Cfg::ROWS_PER_CTA + (id >> 3), ch = id & 7;
                 bstart[c] = lin.base + (uint32_t)(n0 + rowi) * lin.sn + (uint32_t)(ch * 8) * lin.sk;
                 soff[c] = (uint32_t)(rowi * 128 + ((ch ^ (rowi & 7)) << 4));
             }
             const uint32_t kb_step = (uint32_t)BK * lin.sk;
             for (int kb = 0; kb < num_kb; ++kb) {
-                if (!mbar_wait(smem_u32(&bar_empty_b[sb.idx]), sb.phase ^ 1, abortp)) {
+                const uint32_t eb = smem_u32(&bar_empty_b[sb.idx]);
+                if (!(CS > 1 ? mbar_wait_cluster(eb, sb.phase ^ 1, abortp) : mbar_wait(eb, sb.phase ^ 1, abortp))) {
                     raise_abort(abortp, status, RDB_STATUS_TIMEOUT_GENERATOR);
                     ok = false;
                     break;
                 }
-                uint8_t *stage = smem_b_gen + sb.idx * Cfg::B_STAGE;
+                const uint32_t stage = smem_b + sb.idx * Cfg::B_STAGE;
 #pragma unroll
                 for (int c = 0; c < CHUNKS; ++c) {
                     uint32_t p[4];
@@ -289,11 +315,27 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                         __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
                         p[j] = *reinterpret_cast<uint32_t *>(&h);
                     }
-                    *reinterpret_cast<uint4 *>(stage + soff[c]) = make_uint4(p[0], p[1], p[2], p[3]);
+                    if (CS > 1) {
+#pragma unroll
+                        for (int dst = 0; dst < CS; ++dst) st_cluster_v4(mapa(stage + soff[c], (uint32_t)dst), p[0], p[1], p[2], p[3]);
+                    } else {
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + soff[c]), "r"(p[0]), "r"(p[1]),
+                                     "r"(p[2]), "r"(p[3]) : "memory");
+                    }
                     bstart[c] += kb_step;
                 }
-                fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&bar_full_b[sb.idx]));
+                // every writer fences its own stores towards the async proxy, then one lane per warp signals
+                if (CS > 1) fence_proxy_async_all(); else fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    const uint32_t fb = smem_u32(&bar_full_b[sb.idx]);
+                    if (CS > 1) {
+#pragma unroll
+                        for (int dst = 0; dst < CS; ++dst) mbar_arrive_cluster(mapa(fb, (uint32_t)dst));
+                    } else {
+                        mbar_arrive(fb);
+                    }
+                }
                 sb.advance<SB>();
             }
         }
@@ -302,6 +344,7 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
+    if (CS > 1) cluster_sync_all();   // no CTA retires while a peer may still write into it
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
@@ -507,7 +550,13 @@ static int make_tmap(CUtensorMap *m, const void *base, int64_t inner, int64_t ou
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? RDB_OK : RDB_ERR_DRIVER;
+    if (r != CUDA_SUCCESS) {
+        if (getenv("RDB_DEBUG"))
+            fprintf(stderr, "randumb_b200: cuTensorMapEncodeTiled -> %d (base %p inner %lld outer %lld ld %lld box %u x %u)\n",
+                    (int)r, base, (long long)inner, (long long)outer, (long long)ld, box_inner, box_outer);
+        return RDB_ERR_DRIVER_BASE - (int)r;   // keeps the CUresult visible to the caller
+    }
+    return RDB_OK;
 }
 
 static int sm_count() {
@@ -524,31 +573,59 @@ bool umma_shape_ok_noise(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t 
            aligned16(a) && aligned16(d) && M < (1LL << 31) && N < (1LL << 31) && Kc < (1LL << 31);
 }
 
-template <int MT, int BN, int SA, int SB>
+template <int CS, int MT, int BN, int SA, int SB>
 static int launch_noise_gemm(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
                              int64_t ldd_t, Sq5Lin lin, int32_t *status, cudaStream_t st) {
-    using Cfg = NoiseCfg<MT, BN, SA, SB>;
+    using Cfg = NoiseCfg<CS, MT, BN, SA, SB>;
     CUtensorMap ta;
     int rc = make_tmap(&ta, a, Kc, M, lda, BK, BM);
     if (rc) return rc;
-    auto kern = noise_gemm_kernel<MT, BN, SA, SB>;
+    auto kern = noise_gemm_kernel<CS, MT, BN, SA, SB>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
     if (e != cudaSuccess) return (int)e;
-    const int64_t tiles = cdiv64(M, (int64_t)MT * BM) * cdiv64(N, BN);
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, reinterpret_cast<__nv_bfloat16 *>(d), ldd,
-                                                    reinterpret_cast<__nv_bfloat16 *>(d_t), ldd_t, M, N, Kc, lin, status);
+    const int64_t ctiles = cdiv64(cdiv64(M, (int64_t)MT * BM), CS) * cdiv64(N, BN);
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(Cfg::THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_DYN;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int max_clusters = sm_count() / CS;
+    if (CS > 1) {
+        cfg.gridDim = dim3(CS);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) max_clusters = n;
+        else (void)cudaGetLastError();
+    }
+    const int64_t nclusters = ctiles < max_clusters ? ctiles : max_clusters;
+    cfg.gridDim = dim3((unsigned)(nclusters * CS));
+    __nv_bfloat16 *dp = reinterpret_cast<__nv_bfloat16 *>(d), *dtp = reinterpret_cast<__nv_bfloat16 *>(d_t);
+    e = cudaLaunchKernelEx(&cfg, kern, ta, dp, ldd, dtp, ldd_t, M, N, Kc, lin, status);
+    if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
 
-static int g_noise_cfg = 0;  // 0 = 4 sub-tiles x 128 columns, 1 = 2 sub-tiles x 256 columns
+// RDB_OPT_NOISE_TILE: (cluster size, token sub-tiles, generated rows) per work unit
+static int g_noise_cfg = 0;
 void set_noise_cfg(int v) { g_noise_cfg = v; }
 
 int umma_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
                     int64_t ldd_t, Sq5Lin lin, int32_t *status, cudaStream_t st) {
     if (M == 0 || N == 0) return RDB_OK;
-    if (g_noise_cfg == 1) return launch_noise_gemm<2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-    return launch_noise_gemm<4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+    switch (g_noise_cfg) {
+        case 1: return launch_noise_gemm<1, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        case 2: return launch_noise_gemm<2, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        case 3: return launch_noise_gemm<4, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        case 4: return launch_noise_gemm<4, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        case 5: return launch_noise_gemm<8, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        default: return launch_noise_gemm<1, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+    }
 }
 
 bool umma_shape_ok_dense(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int d_dtype,

@@ -84,14 +84,16 @@ def test_bf16_layer_tensor_cores(K, T, Kin, N, R, seed, row0):
     _check(K, T, Kin, N, R, torch.bfloat16, seed, row0, K.PATH_FACTORED, K.IMPL_UMMA, BF16_TOL)
 
 
-@pytest.mark.parametrize("opt", [(1, 1), (2, 1)])
-def test_bf16_layer_alternative_kernel_settings(K, opt):
-    key, val = opt
-    prev = K.set_option(key, val)
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5])
+def test_bf16_layer_every_work_unit_shape(K, tile):
+    """Every (cluster size, sub-tiles, generated rows) variant of the generated-operand kernel, on a shape
+    with ragged tiles and an odd number of token tiles per cluster."""
+    prev = K.set_option(1, tile)
     try:
-        _check(K, 700, 264, 520, 72, torch.bfloat16, 7, 10, K.PATH_FACTORED, K.IMPL_UMMA, BF16_TOL)
+        _check(K, 1500, 264, 520, 72, torch.bfloat16, 7, 10, K.PATH_FACTORED, K.IMPL_UMMA, BF16_TOL)
+        _check(K, 100, 64, 136, 200, torch.bfloat16, 8, 0, K.PATH_FACTORED, K.IMPL_UMMA, BF16_TOL)
     finally:
-        K.set_option(key, prev)
+        K.set_option(1, prev)
 
 
 @pytest.mark.parametrize("T,Kin,N,R,seed,row0,path", [(64, 80, 96, 16, 0, 0, 0), (33, 70, 45, 9, 5, 7, 2), (33, 70, 45, 9, 5, 7, 1)])
