@@ -86,6 +86,16 @@ const char *rdb_strerror(int code);
 int rdb_set_option(int key, int value);
 
 /*
+ * Tuning aid.  While a device buffer of at least 64 bytes per CTA (148 * 64 covers any launch) is
+ * registered, every launch of the generated-operand tensor-core kernel writes eight int64 SM-cycle
+ * counters per CTA into it: [0] MMA thread waiting for the streamed operand, [1] waiting for the generated
+ * operand, [2] waiting for the epilogue to drain TMEM, [3] MMA thread total, [4] TMA thread waiting for a
+ * free stage, [5] generator waiting for a free stage, [6] generator hashing and storing, [7] epilogue busy.
+ * Pass NULL to switch it off (the default; the counters then cost nothing).
+ */
+int rdb_set_profile_buffer(void *device_buffer, size_t bytes);
+
+/*
  * Raw hash words of the noise matrix: out[r*ld + c] = bits(row0 + r, col0 + c, seed), uint32.
  * The reference never exposes the integers; this is the bit-exactness surface for
  * squirrel5_gen_2d (src/rten_cpp/RandumbTensor.py:130-164) and sq5_2d (csrc/cuda/rten.cu:28-48).

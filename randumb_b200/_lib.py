@@ -26,6 +26,7 @@ PROTOTYPES = {
     "rdb_version": (_i32, []),
     "rdb_strerror": (ctypes.c_char_p, [_i32]),
     "rdb_set_option": (_i32, [_i32, _i32]),
+    "rdb_set_profile_buffer": (_i32, [_vp, _sz]),
     "rdb_noise_bits": (_i32, [_vp, _i64, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_noise": (_i32, [_vp, _i32, _i64, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_noise_1d": (_i32, [_vp, _i64, _i64, _u32, _vp]),

@@ -101,6 +101,11 @@ extern "C" int rdb_set_option(int key, int value) {
     }
 }
 
+extern "C" int rdb_set_profile_buffer(void *device_buffer, size_t bytes) {
+    set_profile_buffer(device_buffer, bytes);
+    return RDB_OK;
+}
+
 extern "C" int rdb_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
                               int64_t ldd_t, int a_dtype, int d_dtype, int transposed, int64_t row0, int64_t col0,
                               uint32_t seed, int impl, int32_t *status, void *stream) {

@@ -117,6 +117,13 @@ __device__ __forceinline__ uint32_t mapa(uint32_t saddr, uint32_t cta) {
 __device__ __forceinline__ void st_cluster_v4(uint32_t caddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(caddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+// Asynchronous 16-byte store into the shared memory of a CTA of the cluster; when the data has landed,
+// 16 transaction bytes are completed on `cbar`, an mbarrier in that same CTA.  Non-blocking: the issuing
+// thread needs no fence and no separate arrive.
+__device__ __forceinline__ void st_async_v4(uint32_t caddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t cbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(caddr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(cbar) : "memory");
+}
 // Arrive on a barrier that may live in another CTA of the cluster (release at cluster scope).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t caddr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(caddr) : "memory");

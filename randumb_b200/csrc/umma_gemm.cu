@@ -110,8 +110,10 @@ template <int CS, int MT, int BN, int SA, int SB>
 __global__ void __launch_bounds__(NoiseCfg<CS, MT, BN, SA, SB>::THREADS, 1)
 noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__restrict__ d, int64_t ldd,
                   __nv_bfloat16 *__restrict__ d_t, int64_t ldd_t, int64_t M, int64_t N, int64_t Kc, Sq5Lin lin,
-                  int32_t *status) {
+                  int32_t *status, long long *prof) {
     using Cfg = NoiseCfg<CS, MT, BN, SA, SB>;
+    // prof (optional): 8 cycle counters per CTA -- where each role waits; see rdb_set_profile_buffer
+    long long pc0 = 0, pc1 = 0, pc2 = 0;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full_a[SA], bar_empty_a[SA], bar_full_b[SB], bar_empty_b[SB], bar_tmem_full, bar_tmem_empty;
     __shared__ uint32_t tmem_holder;
@@ -121,6 +123,7 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
     const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
     const uint32_t smem_a = raw_addr + pad;
     const uint32_t smem_b = smem_a + SA * Cfg::A_STAGE;
+    uint8_t *smem_gen = smem_raw + pad;   // generic pointer to the same place as smem_a
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -129,7 +132,9 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; ++s) { mbar_init(smem_u32(&bar_full_a[s]), 1); mbar_init(smem_u32(&bar_empty_a[s]), 1); }
         for (int s = 0; s < SB; ++s) {
-            mbar_init(smem_u32(&bar_full_b[s]), CS * Cfg::GEN_WARPS);   // one arrival per generator warp of every CTA
+            // single CTA: every generator thread arrives.  cluster: one local arrive.expect_tx per phase and the
+            // stage's bytes land as asynchronous stores from all CTAs, each completing its transaction bytes.
+            mbar_init(smem_u32(&bar_full_b[s]), CS > 1 ? 1 : Cfg::GEN_THREADS);
             mbar_init(smem_u32(&bar_empty_b[s]), CS);                   // one MMA commit from every CTA
         }
         mbar_init(smem_u32(&bar_tmem_full), 1);
@@ -167,11 +172,13 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
                 const int64_t m0 = m_base(ct);
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    const long long tw = prof ? clock64() : 0;
                     if (!mbar_wait(smem_u32(&bar_empty_a[st.idx]), st.phase ^ 1, abortp)) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
                         ok = false;
                         break;
                     }
+                    if (prof) pc0 += clock64() - tw;
                     const uint32_t fb = smem_u32(&bar_full_a[st.idx]);
                     mbar_arrive_expect_tx(fb, Cfg::A_STAGE);
 #pragma unroll
@@ -181,6 +188,7 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                     st.advance<SA>();
                 }
             }
+            if (prof) prof[blockIdx.x * 8 + 4] = pc0;
             // Loads still in flight complete on their own barriers; wait for them (bounded) so the
             // CTA does not retire with copies targeting its shared memory.
             if (!ok) {
@@ -199,22 +207,28 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             PipeState sa, sb;
             uint32_t tphase = 0;
             bool ok = true;
+            const long long t_start = prof ? clock64() : 0;
             for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
+                long long tw = prof ? clock64() : 0;
                 if (!mbar_wait(smem_u32(&bar_tmem_empty), tphase ^ 1, abortp)) {
                     raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
                     break;
                 }
+                if (prof) pc2 += clock64() - tw;
                 tc_fence_after_sync();
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    tw = prof ? clock64() : 0;
                     const bool got_a = mbar_wait(smem_u32(&bar_full_a[sa.idx]), sa.phase, abortp);
+                    const long long tw2 = prof ? clock64() : 0;
                     const bool got_b = got_a && (CS > 1 ? mbar_wait_cluster(smem_u32(&bar_full_b[sb.idx]), sb.phase, abortp)
                                                         : mbar_wait(smem_u32(&bar_full_b[sb.idx]), sb.phase, abortp));
+                    if (prof) { pc0 += tw2 - tw; pc1 += clock64() - tw2; }
                     if (!got_b) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
                         ok = false;
                         break;
                     }
-                    if (CS > 1) fence_proxy_async_all();   // peers wrote the stage through the generic proxy
+                    if (CS > 1) fence_proxy_async_smem();  // the stage arrived as stores from other threads/CTAs
                     tc_fence_after_sync();
                     const uint32_t a_stage = smem_a + sa.idx * Cfg::A_STAGE;
                     const uint32_t b_stage = smem_b + sb.idx * Cfg::B_STAGE;
@@ -241,6 +255,12 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                 if (ok) umma_commit(smem_u32(&bar_tmem_full));
                 tphase ^= 1;
             }
+            if (prof) {
+                prof[blockIdx.x * 8 + 0] = pc0;
+                prof[blockIdx.x * 8 + 1] = pc1;
+                prof[blockIdx.x * 8 + 2] = pc2;
+                prof[blockIdx.x * 8 + 3] = clock64() - t_start;
+            }
         }
     } else if (warp < Cfg::FIRST_GEN_WARP) {
         // ------------------------------------------------------------------ epilogue (4 warps)
@@ -253,6 +273,7 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                 raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
                 break;
             }
+            const long long te = prof ? clock64() : 0;
             tc_fence_after_sync();
 #pragma unroll 1
             for (int s = 0; s < MT; ++s) {
@@ -277,7 +298,9 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bar_tmem_empty));
             tphase ^= 1;
+            if (prof) pc0 += clock64() - te;
         }
+        if (prof && warp == Cfg::FIRST_EPI_WARP && lane == 0) prof[blockIdx.x * 8 + 7] = pc0;
     } else {
         // ------------------------------------------------------------------ generators (8 warps)
         const int tg = threadIdx.x - Cfg::FIRST_GEN_WARP * 32;
@@ -299,12 +322,16 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             const uint32_t kb_step = (uint32_t)BK * lin.sk;
             for (int kb = 0; kb < num_kb; ++kb) {
                 const uint32_t eb = smem_u32(&bar_empty_b[sb.idx]);
+                const long long tw = prof ? clock64() : 0;
                 if (!(CS > 1 ? mbar_wait_cluster(eb, sb.phase ^ 1, abortp) : mbar_wait(eb, sb.phase ^ 1, abortp))) {
                     raise_abort(abortp, status, RDB_STATUS_TIMEOUT_GENERATOR);
                     ok = false;
                     break;
                 }
+                const long long tc = prof ? clock64() : 0;
                 const uint32_t stage = smem_b + sb.idx * Cfg::B_STAGE;
+                const uint32_t fb = smem_u32(&bar_full_b[sb.idx]);
+                if (CS > 1 && tg == 0) mbar_arrive_expect_tx(fb, Cfg::B_STAGE);   // this phase's local arrival + byte count
 #pragma unroll
                 for (int c = 0; c < CHUNKS; ++c) {
                     uint32_t p[4];
@@ -317,27 +344,24 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                     }
                     if (CS > 1) {
 #pragma unroll
-                        for (int dst = 0; dst < CS; ++dst) st_cluster_v4(mapa(stage + soff[c], (uint32_t)dst), p[0], p[1], p[2], p[3]);
+                        for (int dst = 0; dst < CS; ++dst)
+                            st_async_v4(mapa(stage + soff[c], (uint32_t)dst), p[0], p[1], p[2], p[3], mapa(fb, (uint32_t)dst));
                     } else {
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + soff[c]), "r"(p[0]), "r"(p[1]),
-                                     "r"(p[2]), "r"(p[3]) : "memory");
+                        *reinterpret_cast<uint4 *>(smem_gen + (stage - smem_a) + soff[c]) = make_uint4(p[0], p[1], p[2], p[3]);
                     }
                     bstart[c] += kb_step;
                 }
-                // every writer fences its own stores towards the async proxy, then one lane per warp signals
-                if (CS > 1) fence_proxy_async_all(); else fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    const uint32_t fb = smem_u32(&bar_full_b[sb.idx]);
-                    if (CS > 1) {
-#pragma unroll
-                        for (int dst = 0; dst < CS; ++dst) mbar_arrive_cluster(mapa(fb, (uint32_t)dst));
-                    } else {
-                        mbar_arrive(fb);
-                    }
+                if (CS == 1) {
+                    fence_proxy_async_smem();
+                    mbar_arrive(fb);
                 }
+                if (prof) { pc0 += tc - tw; pc1 += clock64() - tc; }
                 sb.advance<SB>();
             }
+        }
+        if (prof && tg == 0) {
+            prof[blockIdx.x * 8 + 5] = pc0;
+            prof[blockIdx.x * 8 + 6] = pc1;
         }
     }
 
@@ -538,11 +562,24 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// cuTensorMapEncodeTiled needs a CUDA context current on the calling thread.  PyTorch's autograd worker
+// threads may not have touched the runtime yet when they call in here (device 0 is never "set"
+// explicitly and cached allocations make no API call), so bind the primary context once per thread:
+// the runtime adopts the driver context that is already current, or binds its default device otherwise.
+static void ensure_context() {
+    thread_local bool done = false;
+    if (!done) {
+        (void)cudaFree(nullptr);
+        done = true;
+    }
+}
+
 // bf16 matrix with `inner` contiguous elements per row, `outer` rows, row pitch ld elements.
 static int make_tmap(CUtensorMap *m, const void *base, int64_t inner, int64_t outer, int64_t ld, uint32_t box_inner,
                      uint32_t box_outer) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return RDB_ERR_DRIVER;
+    ensure_context();
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {box_inner, box_outer};
@@ -571,6 +608,13 @@ static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 bool umma_shape_ok_noise(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, const void *a, const void *d) {
     return M >= 1 && N >= 8 && Kc >= 8 && (N % 8) == 0 && (Kc % 8) == 0 && (lda % 8) == 0 && (ldd % 8) == 0 &&
            aligned16(a) && aligned16(d) && M < (1LL << 31) && N < (1LL << 31) && Kc < (1LL << 31);
+}
+
+static long long *g_prof = nullptr;
+static size_t g_prof_bytes = 0;
+void set_profile_buffer(void *p, size_t bytes) {
+    g_prof = reinterpret_cast<long long *>(p);
+    g_prof_bytes = p ? bytes : 0;
 }
 
 template <int CS, int MT, int BN, int SA, int SB>
@@ -606,7 +650,8 @@ static int launch_noise_gemm(void *d, void *d_t, const void *a, int64_t M, int64
     const int64_t nclusters = ctiles < max_clusters ? ctiles : max_clusters;
     cfg.gridDim = dim3((unsigned)(nclusters * CS));
     __nv_bfloat16 *dp = reinterpret_cast<__nv_bfloat16 *>(d), *dtp = reinterpret_cast<__nv_bfloat16 *>(d_t);
-    e = cudaLaunchKernelEx(&cfg, kern, ta, dp, ldd, dtp, ldd_t, M, N, Kc, lin, status);
+    long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 8 * sizeof(long long)) ? g_prof : nullptr;
+    e = cudaLaunchKernelEx(&cfg, kern, ta, dp, ldd, dtp, ldd_t, M, N, Kc, lin, status, prof);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
