@@ -76,9 +76,10 @@ const char *rdb_strerror(int code);
  * Process-wide tuning switches (not part of the reference surface; defaults are the tuned ones).
  *   RDB_OPT_NOISE_TILE   work unit of the generated-operand kernel; every hash is reused by
  *                        (cluster size) x (token sub-tiles) x 128 tokens:
- *                        0: 1 CTA,  4 sub-tiles, 128 generated rows      1: 1 CTA,  2 sub-tiles, 256 rows
- *                        2: 2 CTAs, 4 sub-tiles, 128 rows                3: 4 CTAs, 4 sub-tiles, 128 rows
- *                        4: 4 CTAs, 2 sub-tiles, 256 rows                5: 8 CTAs, 2 sub-tiles, 256 rows
+ *                        0: automatic (3 when there are at least two 512-token tiles, else 1)
+ *                        1: 1 CTA,  4 sub-tiles, 128 generated rows      2: 1 CTA,  2 sub-tiles, 256 rows
+ *                        3: 2 CTAs, 4 sub-tiles, 128 rows                4: 4 CTAs, 4 sub-tiles, 128 rows
+ *                        5: 4 CTAs, 2 sub-tiles, 256 rows                6: 8 CTAs, 2 sub-tiles, 256 rows
  *                        (CTAs of a cluster share each generated stage through distributed shared memory)
  * Returns the previous value, or RDB_ERR_UNSUPPORTED for an unknown key.
  */

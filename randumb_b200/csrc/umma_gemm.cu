@@ -663,12 +663,14 @@ void set_noise_cfg(int v) { g_noise_cfg = v; }
 int umma_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
                     int64_t ldd_t, Sq5Lin lin, int32_t *status, cudaStream_t st) {
     if (M == 0 || N == 0) return RDB_OK;
-    switch (g_noise_cfg) {
-        case 1: return launch_noise_gemm<1, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-        case 2: return launch_noise_gemm<2, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-        case 3: return launch_noise_gemm<4, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-        case 4: return launch_noise_gemm<4, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-        case 5: return launch_noise_gemm<8, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+    int cfg = g_noise_cfg;
+    if (cfg == 0) cfg = (M > 4 * BM) ? 3 : 1;   // two or more 512-token tiles: pair CTAs so they share the generated operand
+    switch (cfg) {
+        case 2: return launch_noise_gemm<1, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        case 3: return launch_noise_gemm<2, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        case 4: return launch_noise_gemm<4, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        case 5: return launch_noise_gemm<4, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        case 6: return launch_noise_gemm<8, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
         default: return launch_noise_gemm<1, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
     }
 }
