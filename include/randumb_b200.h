@@ -162,6 +162,27 @@ int rdb_gemv_fwd(float *y, const float *x, const float *coef, float *workspace, 
                  int64_t R, int64_t row0, uint32_t seed, void *stream);
 
 /*
+ * rdb_gemv_fwd for callers that have no device memory to hand over as workspace and may not allocate
+ * any: for example a serving loop whose memory was divided up completely at start-up, or a host runtime
+ * that forbids allocation calls on its request path.  (No counterpart in the reference, which allocates
+ * a fresh tensor for every intermediate.)  The R intermediate values live in a fixed array inside the
+ * library instead, so
+ *   - R may be at most RDB_GEMV_STATIC_MAX_R; a larger R returns RDB_ERR_TOO_LARGE and launches nothing;
+ *   - the library keeps RDB_GEMV_STATIC_MAX_R * 4 bytes on every GPU it is loaded on until exit;
+ *   - the call itself performs no cudaMalloc/cudaFree and calls no allocating library routine;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, cached
+ *     per device afterwards); make that first call with the device current and before any stream
+ *     capture is started;
+ *   - all calls on a device share the one array: two calls that overlap on the GPU (different streams)
+ *     race on it and may return wrong results; calls on one stream are safe.  The array keeps the last
+ *     call's values, which is harmless: every call overwrites the R entries it later reads.
+ * Results are bitwise those of rdb_gemv_fwd.
+ */
+#define RDB_GEMV_STATIC_MAX_R 16384
+int rdb_gemv_fwd_static(float *y, const float *x, const float *coef, int64_t K, int64_t N, int64_t R,
+                        int64_t row0, uint32_t seed, void *stream);
+
+/*
  * Batch-1 float32 backward: g = S^T dy (workspace, R floats), dx[K] = g C, dc[R,K] = g x^T.
  * dx or dc may be NULL.
  */

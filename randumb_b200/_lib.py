@@ -36,6 +36,7 @@ PROTOTYPES = {
                               _vp, _vp]),
     "rdb_linear_weight": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _u32, _i32, _vp]),
     "rdb_gemv_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
+    "rdb_gemv_fwd_static": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_gemv_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_gemm_noise": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i64, _i64, _u32, _i32,
                               _vp, _vp]),

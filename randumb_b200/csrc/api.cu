@@ -77,7 +77,7 @@ extern "C" const char *rdb_strerror(int code) {
         case RDB_ERR_WORKSPACE: return "workspace too small or misaligned";
         case RDB_ERR_UNSUPPORTED: return "combination of options not supported for this problem";
         case RDB_ERR_DRIVER: return "tensor-map encoding failed (driver entry point unavailable or rejected arguments)";
-        case RDB_ERR_TOO_LARGE: return "problem exceeds a launch limit";
+        case RDB_ERR_TOO_LARGE: return "problem exceeds a launch limit or a built-in maximum size";
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

@@ -4,6 +4,8 @@
 // (and writing dC) once: 128-bit loads, warp-shuffle reductions, the noise regenerated in
 // registers from (seed, row, k).  Same reference slot as the aten.mm override
 // (src/rten_cpp/RandumbTensor.py:942-946, 771-791) for a single input row.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace rdb {
@@ -133,6 +135,30 @@ __global__ void __launch_bounds__(256) gemv_dxdc_kernel(float *__restrict__ dx, 
     }
 }
 
+// Scratch of rdb_gemv_fwd_static: the R intermediate values z = C x.  It lives in the library image, so
+// every GPU that loads the library holds these 64 KB until the process exits.  In host code this name is
+// only a stand-in for the symbol; the device address is looked up once per device below.
+static __device__ __align__(256) float g_gemv_static_scratch[RDB_GEMV_STATIC_MAX_R];
+
+// Device address of the scratch array on the current device (looked up on first use, then cached).
+static int gemv_static_scratch(float **out) {
+    static std::mutex mu;
+    static float *per_device[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return RDB_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!per_device[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_gemv_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        per_device[dev] = reinterpret_cast<float *>(p);
+    }
+    *out = per_device[dev];
+    return RDB_OK;
+}
+
 }  // namespace rdb
 
 using namespace rdb;
@@ -151,6 +177,18 @@ extern "C" int rdb_gemv_fwd(float *y, const float *x, const float *coef, float *
     }
     gemv_sz_kernel<<<(unsigned)cdiv64(N, 8), 256, 0, st>>>(y, workspace, N, R, sq5_lin_rows(seed, (uint32_t)row0, 0));
     return launch_status();
+}
+
+extern "C" int rdb_gemv_fwd_static(float *y, const float *x, const float *coef, int64_t K, int64_t N, int64_t R, int64_t row0,
+                                   uint32_t seed, void *stream) {
+    if (K < 0 || N < 0 || R < 0) return RDB_ERR_SHAPE;
+    if (R > RDB_GEMV_STATIC_MAX_R) return RDB_ERR_TOO_LARGE;   // the built-in scratch holds at most this many values
+    float *scratch = nullptr;
+    const int rc = gemv_static_scratch(&scratch);
+    if (rc) return rc;
+    // Same two kernels as rdb_gemv_fwd.  The first writes scratch[0..R) in full before the second reads
+    // it, so nothing left over from an earlier call is ever read and nothing needs clearing.
+    return rdb_gemv_fwd(y, x, coef, scratch, K, N, R, row0, seed, stream);
 }
 
 extern "C" int rdb_gemv_bwd(float *dx, float *dc, const float *dy, const float *x, const float *coef, float *workspace,
