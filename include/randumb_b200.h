@@ -87,11 +87,12 @@ const char *rdb_strerror(int code);
 int rdb_set_option(int key, int value);
 
 /*
- * Tuning aid.  While a device buffer of at least 64 bytes per CTA (148 * 64 covers any launch) is
- * registered, every launch of the generated-operand tensor-core kernel writes eight int64 SM-cycle
+ * Tuning aid.  While a device buffer of at least 128 bytes per CTA (148 * 128 covers any launch) is
+ * registered, every launch of the generated-operand tensor-core kernel writes sixteen int64 SM-cycle
  * counters per CTA into it: [0] MMA thread waiting for the streamed operand, [1] waiting for the generated
  * operand, [2] waiting for the epilogue to drain TMEM, [3] MMA thread total, [4] TMA thread waiting for a
- * free stage, [5] generator waiting for a free stage, [6] generator hashing and storing, [7] epilogue busy.
+ * free stage, [5] generator waiting for a free stage, [6] generator hashing and storing, [7] epilogue busy,
+ * [8] MMA thread in fences, [9] issuing MMAs, [10] issuing commits; the rest unused.
  * Pass NULL to switch it off (the default; the counters then cost nothing).
  */
 int rdb_set_profile_buffer(void *device_buffer, size_t bytes);
@@ -193,15 +194,14 @@ int rdb_gemv_bwd(float *dx, float *dc, const float *dy, const float *x, const fl
  * Building block: D[M,N] = A[M,Kc] * G^T where G is generated, never read from memory.
  *   transposed == 0:  G[n,k] = S[row0+n, col0+k]      (y = z S^T : contraction over noise columns)
  *   transposed == 1:  G[n,k] = S[row0+k, col0+n]      (g = dY S  : contraction over noise rows)
- * A is row-major with leading dimension lda; D row-major with ldd.  When d_t != NULL (bf16 tcgen05
- * kernel only) the transpose D^T[N,M] is written there as well (leading dimension ldd_t).
+ * A is row-major with leading dimension lda; D row-major with ldd.
  * a_dtype / d_dtype: RDB_F32 or RDB_BF16 (the tcgen05 kernel needs both bf16).
  * Same reference slot as rt_mm_grouped_kernel (src/rten_cpp/RandumbTensor.py:648-746), whose RT
  * operand is regenerated tile by tile inside the kernel.
  */
-int rdb_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda,
-                   int64_t ldd, int64_t ldd_t, int a_dtype, int d_dtype, int transposed, int64_t row0,
-                   int64_t col0, uint32_t seed, int impl, int32_t *status, void *stream);
+int rdb_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
+                   int a_dtype, int d_dtype, int transposed, int64_t row0, int64_t col0, uint32_t seed,
+                   int impl, int32_t *status, void *stream);
 
 /*
  * Building block: dense D[M,N] = op(A) * op(B)^T, float32 accumulation.

@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "librandumb_b200.so")
+# RANDUMB_B200_LIB points at a library built elsewhere (same C ABI); default is the in-tree build.
+LIB_PATH = os.environ.get("RANDUMB_B200_LIB") or os.path.join(_HERE, "lib", "librandumb_b200.so")
 
 # constants mirrored from include/randumb_b200.h
 F32, BF16 = 0, 1
@@ -38,8 +39,7 @@ PROTOTYPES = {
     "rdb_gemv_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_gemv_fwd_static": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_gemv_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
-    "rdb_gemm_noise": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i64, _i64, _u32, _i32,
-                              _vp, _vp]),
+    "rdb_gemm_noise": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i64, _i64, _u32, _i32, _vp, _vp]),
     "rdb_gemm_dense": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp,
                               _vp]),
     "rdb_materialize_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _u32, _vp]),

@@ -106,22 +106,19 @@ extern "C" int rdb_set_profile_buffer(void *device_buffer, size_t bytes) {
     return RDB_OK;
 }
 
-extern "C" int rdb_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
-                              int64_t ldd_t, int a_dtype, int d_dtype, int transposed, int64_t row0, int64_t col0,
-                              uint32_t seed, int impl, int32_t *status, void *stream) {
+extern "C" int rdb_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, int a_dtype,
+                              int d_dtype, int transposed, int64_t row0, int64_t col0, uint32_t seed, int impl,
+                              int32_t *status, void *stream) {
     if (M < 0 || N < 0 || Kc < 0 || lda < Kc || ldd < N) return RDB_ERR_SHAPE;
     if (M == 0 || N == 0) return RDB_OK;
     if (!d || (Kc > 0 && !a)) return RDB_ERR_NULL;
     if ((a_dtype != RDB_F32 && a_dtype != RDB_BF16) || (d_dtype != RDB_F32 && d_dtype != RDB_BF16)) return RDB_ERR_DTYPE;
-    if (d_t && ldd_t < M) return RDB_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
     const Sq5Lin lin = transposed ? sq5_lin_cols(seed, (uint32_t)row0, (uint32_t)col0)
                                   : sq5_lin_rows(seed, (uint32_t)row0, (uint32_t)col0);
-    const bool can = a_dtype == RDB_BF16 && d_dtype == RDB_BF16 && umma_shape_ok_noise(M, N, Kc, lda, ldd, a, d) &&
-                     (!d_t || ((ldd_t % 8) == 0));
+    const bool can = a_dtype == RDB_BF16 && d_dtype == RDB_BF16 && umma_shape_ok_noise(M, N, Kc, lda, ldd, a, d);
     if (impl == RDB_IMPL_UMMA && !can) return RDB_ERR_UNSUPPORTED;
-    if (impl != RDB_IMPL_SIMT && can) return umma_gemm_noise(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-    if (d_t) return RDB_ERR_UNSUPPORTED;
+    if (impl != RDB_IMPL_SIMT && can) return umma_gemm_noise(d, a, M, N, Kc, lda, ldd, lin, status, st);
     return simt_gemm(d, d_dtype, ldd, 1, a, a_dtype, lda, 1, nullptr, RDB_F32, 0, 0, lin, M, N, Kc, st);
 }
 
@@ -197,7 +194,7 @@ extern "C" int rdb_linear_fwd(void *y, const void *x, const void *coef, void *wo
             void *z = ws + w.off[0];
             rc = umma_gemm_dense(z, x, coef, T, R, K, K, K, R, RDB_BF16, 1, 1, status, st);
             if (rc) return rc;
-            return umma_gemm_noise(y, nullptr, z, T, N, R, R, N, 0, rows, status, st);
+            return umma_gemm_noise(y, z, T, N, R, R, N, rows, status, st);
         }
         if (dtype == RDB_F32 && T == 1)
             return rdb_gemv_fwd((float *)y, (const float *)x, (const float *)coef, (float *)(ws + w.off[0]), K, N, R, row0,
@@ -243,7 +240,7 @@ extern "C" int rdb_linear_bwd(void *dx, void *dc, const void *dy, const void *x,
         if (im == RDB_IMPL_UMMA) {
             void *g = ws + w.off[0];
             // g = dY S ; dX = g C (C read in place as an MN-major B operand) ; dC = g^T x (both operands MN-major)
-            rc = umma_gemm_noise(g, nullptr, dy, T, R, N, N, R, 0, cols, status, st);
+            rc = umma_gemm_noise(g, dy, T, R, N, N, R, cols, status, st);
             if (rc) return rc;
             if (dx) {
                 rc = umma_gemm_dense(dx, g, coef, T, K, R, R, K, K, RDB_BF16, 1, 0, status, st);

@@ -40,8 +40,8 @@ int simt_gemm(void *d, int d_dtype, int64_t d_rs, int64_t d_cs, const void *a, i
 void set_noise_cfg(int v);
 void set_profile_buffer(void *p, size_t bytes);
 bool umma_shape_ok_noise(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, const void *a, const void *d);
-int umma_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
-                    int64_t ldd_t, Sq5Lin lin, int32_t *status, cudaStream_t stream);
+int umma_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, Sq5Lin lin,
+                    int32_t *status, cudaStream_t stream);
 bool umma_shape_ok_dense(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int d_dtype,
                          int a_kmajor, int b_kmajor, const void *a, const void *b, const void *d);
 int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda,

@@ -201,6 +201,20 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
     return d;
 }
 
+// The same descriptor split in two 32-bit halves: the high word is constant for a kernel, the low word is
+// the (address >> 4) field plus the leading byte offset, so stepping through a tile is one 32-bit add.
+__host__ __device__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
 // Instruction descriptor for kind::f16 with bf16 inputs and float32 accumulation.
 // a_mn / b_mn: 0 = operand is K-major in shared memory, 1 = MN-major.
 __host__ __device__ constexpr uint32_t idesc_bf16_f32(uint32_t m, uint32_t n, uint32_t a_mn, uint32_t b_mn) {

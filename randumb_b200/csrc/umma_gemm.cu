@@ -98,7 +98,7 @@ struct NoiseCfg {
     static constexpr int ROWS_PER_CTA = BN / CS;                       // noise rows of a stage this CTA generates
     static constexpr int CHUNKS = (ROWS_PER_CTA * 8) / GEN_THREADS;    // 16-byte chunks per generator thread per stage
     static_assert(MT * BN <= TMEM_COLS, "accumulators exceed TMEM");
-    static_assert(BN % 32 == 0 && BN <= 256, "BN");
+    static_assert(BN % 64 == 0 && BN <= 256, "BN");
     static_assert(CS == 1 || CS == 2 || CS == 4 || CS == 8, "cluster size");
     static_assert(BN % CS == 0 && (ROWS_PER_CTA * 8) % GEN_THREADS == 0 && CHUNKS >= 1, "generator chunking");
 };
@@ -108,12 +108,11 @@ struct NoiseCfg {
 // (distributed shared memory), so one hash is amortised over CS * MT * 128 tokens.
 template <int CS, int MT, int BN, int SA, int SB>
 __global__ void __launch_bounds__(NoiseCfg<CS, MT, BN, SA, SB>::THREADS, 1)
-noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__restrict__ d, int64_t ldd,
-                  __nv_bfloat16 *__restrict__ d_t, int64_t ldd_t, int64_t M, int64_t N, int64_t Kc, Sq5Lin lin,
-                  int32_t *status, long long *prof) {
+noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__restrict__ d, int64_t ldd, int64_t M,
+                  int64_t N, int64_t Kc, Sq5Lin lin, int32_t *status, long long *prof) {
     using Cfg = NoiseCfg<CS, MT, BN, SA, SB>;
     // prof (optional): 8 cycle counters per CTA -- where each role waits; see rdb_set_profile_buffer
-    long long pc0 = 0, pc1 = 0, pc2 = 0;
+    long long pc0 = 0, pc1 = 0, pc2 = 0, pc3 = 0, pc4 = 0, pc5 = 0;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full_a[SA], bar_empty_a[SA], bar_full_b[SB], bar_empty_b[SB], bar_tmem_full, bar_tmem_empty;
     __shared__ uint32_t tmem_holder;
@@ -188,7 +187,7 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                     st.advance<SA>();
                 }
             }
-            if (prof) prof[blockIdx.x * 8 + 4] = pc0;
+            if (prof) prof[blockIdx.x * 16 + 4] = pc0;
             // Loads still in flight complete on their own barriers; wait for them (bounded) so the
             // CTA does not retire with copies targeting its shared memory.
             if (!ok) {
@@ -228,19 +227,24 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                         ok = false;
                         break;
                     }
+                    const long long tf0 = prof ? clock64() : 0;
                     if (CS > 1) fence_proxy_async_smem();  // the stage arrived as stores from other threads/CTAs
                     tc_fence_after_sync();
-                    const uint32_t a_stage = smem_a + sa.idx * Cfg::A_STAGE;
-                    const uint32_t b_stage = smem_b + sb.idx * Cfg::B_STAGE;
+                    const long long tf1 = prof ? clock64() : 0;
+                    // descriptors: constant high word, low word = stage address field + a compile-time step
+                    constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+                    const uint32_t a_lo = smem_desc_lo(smem_a + sa.idx * Cfg::A_STAGE, 0);
+                    const uint32_t b_lo = smem_desc_lo(smem_b + sb.idx * Cfg::B_STAGE, 0);
 #pragma unroll
                     for (int s = 0; s < MT; ++s) {
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
-                            const uint64_t adesc = smem_desc_sw128(a_stage + s * SUB_BYTES + k * UMMA_K * 2, 0, 1024);
-                            const uint64_t bdesc = smem_desc_sw128(b_stage + k * UMMA_K * 2, 0, 1024);
+                            const uint64_t adesc = pack_desc(a_lo + ((s * SUB_BYTES + k * UMMA_K * 2) >> 4), desc_hi);
+                            const uint64_t bdesc = pack_desc(b_lo + ((k * UMMA_K * 2) >> 4), desc_hi);
                             umma_bf16(tmem_base + s * BN, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
                         }
                     }
+                    const long long tf2 = prof ? clock64() : 0;
                     umma_commit(smem_u32(&bar_empty_a[sa.idx]));
                     // the stage is rewritten by every CTA's generators: tell all of them it is free here
                     if (CS > 1) {
@@ -249,6 +253,7 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                     } else {
                         umma_commit(smem_u32(&bar_empty_b[sb.idx]));
                     }
+                    if (prof) { pc3 += tf1 - tf0; pc4 += tf2 - tf1; pc5 += clock64() - tf2; }
                     sa.advance<SA>();
                     sb.advance<SB>();
                 }
@@ -256,10 +261,13 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                 tphase ^= 1;
             }
             if (prof) {
-                prof[blockIdx.x * 8 + 0] = pc0;
-                prof[blockIdx.x * 8 + 1] = pc1;
-                prof[blockIdx.x * 8 + 2] = pc2;
-                prof[blockIdx.x * 8 + 3] = clock64() - t_start;
+                prof[blockIdx.x * 16 + 0] = pc0;
+                prof[blockIdx.x * 16 + 1] = pc1;
+                prof[blockIdx.x * 16 + 2] = pc2;
+                prof[blockIdx.x * 16 + 3] = clock64() - t_start;
+                prof[blockIdx.x * 16 + 8] = pc3;
+                prof[blockIdx.x * 16 + 9] = pc4;
+                prof[blockIdx.x * 16 + 10] = pc5;
             }
         }
     } else if (warp < Cfg::FIRST_GEN_WARP) {
@@ -279,19 +287,19 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             for (int s = 0; s < MT; ++s) {
                 const int64_t row = m0 + s * BM + q * 32 + lane;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * BN + c0), r);
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    // two 32-column loads in flight per wait
+                    uint32_t r0[32], r1[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * BN + c0);
+                    tmem_ld_32x32(taddr, r0);
+                    tmem_ld_32x32(taddr + 32, r1);
                     tmem_ld_wait();
                     const int64_t col = n0 + c0;
-                    const int ncols = (int)((N - col) < 32 ? (N - col) : 32);
-                    if (row < M && ncols > 0) {
-                        store_row32<__nv_bfloat16>(d + row * ldd + col, r, ncols);
-                        if (d_t) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (j < ncols) d_t[(col + j) * ldd_t + row] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                        }
+                    const int nc0 = (int)((N - col) < 32 ? (N - col) : 32);
+                    const int nc1 = (int)((N - col - 32) < 32 ? (N - col - 32) : 32);
+                    if (row < M) {
+                        if (nc0 > 0) store_row32<__nv_bfloat16>(d + row * ldd + col, r0, nc0);
+                        if (nc1 > 0) store_row32<__nv_bfloat16>(d + row * ldd + col + 32, r1, nc1);
                     }
                 }
             }
@@ -300,7 +308,7 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             tphase ^= 1;
             if (prof) pc0 += clock64() - te;
         }
-        if (prof && warp == Cfg::FIRST_EPI_WARP && lane == 0) prof[blockIdx.x * 8 + 7] = pc0;
+        if (prof && warp == Cfg::FIRST_EPI_WARP && lane == 0) prof[blockIdx.x * 16 + 7] = pc0;
     } else {
         // ------------------------------------------------------------------ generators (8 warps)
         const int tg = threadIdx.x - Cfg::FIRST_GEN_WARP * 32;
@@ -360,8 +368,8 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             }
         }
         if (prof && tg == 0) {
-            prof[blockIdx.x * 8 + 5] = pc0;
-            prof[blockIdx.x * 8 + 6] = pc1;
+            prof[blockIdx.x * 16 + 5] = pc0;
+            prof[blockIdx.x * 16 + 6] = pc1;
         }
     }
 
@@ -495,11 +503,13 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_base + st.idx * Cfg::STAGE;
-                    const uint32_t sbm = sa + Cfg::A_STAGE;
+                    constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+                    const uint32_t a_lo = smem_desc_lo(sa, A_LBO);
+                    const uint32_t b_lo = smem_desc_lo(sa + Cfg::A_STAGE, B_LBO);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t adesc = smem_desc_sw128(sa + k * A_KSTEP, A_LBO, 1024);
-                        const uint64_t bdesc = smem_desc_sw128(sbm + k * B_KSTEP, B_LBO, 1024);
+                        const uint64_t adesc = pack_desc(a_lo + ((k * A_KSTEP) >> 4), desc_hi);
+                        const uint64_t bdesc = pack_desc(b_lo + ((k * B_KSTEP) >> 4), desc_hi);
                         umma_bf16(tacc, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&bar_empty[st.idx]));
@@ -618,8 +628,8 @@ void set_profile_buffer(void *p, size_t bytes) {
 }
 
 template <int CS, int MT, int BN, int SA, int SB>
-static int launch_noise_gemm(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
-                             int64_t ldd_t, Sq5Lin lin, int32_t *status, cudaStream_t st) {
+static int launch_noise_gemm(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, Sq5Lin lin,
+                             int32_t *status, cudaStream_t st) {
     using Cfg = NoiseCfg<CS, MT, BN, SA, SB>;
     CUtensorMap ta;
     int rc = make_tmap(&ta, a, Kc, M, lda, BK, BM);
@@ -649,9 +659,9 @@ static int launch_noise_gemm(void *d, void *d_t, const void *a, int64_t M, int64
     }
     const int64_t nclusters = ctiles < max_clusters ? ctiles : max_clusters;
     cfg.gridDim = dim3((unsigned)(nclusters * CS));
-    __nv_bfloat16 *dp = reinterpret_cast<__nv_bfloat16 *>(d), *dtp = reinterpret_cast<__nv_bfloat16 *>(d_t);
-    long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 8 * sizeof(long long)) ? g_prof : nullptr;
-    e = cudaLaunchKernelEx(&cfg, kern, ta, dp, ldd, dtp, ldd_t, M, N, Kc, lin, status, prof);
+    __nv_bfloat16 *dp = reinterpret_cast<__nv_bfloat16 *>(d);
+    long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 16 * sizeof(long long)) ? g_prof : nullptr;
+    e = cudaLaunchKernelEx(&cfg, kern, ta, dp, ldd, M, N, Kc, lin, status, prof);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
@@ -660,18 +670,18 @@ static int launch_noise_gemm(void *d, void *d_t, const void *a, int64_t M, int64
 static int g_noise_cfg = 0;
 void set_noise_cfg(int v) { g_noise_cfg = v; }
 
-int umma_gemm_noise(void *d, void *d_t, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd,
-                    int64_t ldd_t, Sq5Lin lin, int32_t *status, cudaStream_t st) {
+int umma_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, Sq5Lin lin,
+                    int32_t *status, cudaStream_t st) {
     if (M == 0 || N == 0) return RDB_OK;
     int cfg = g_noise_cfg;
     if (cfg == 0) cfg = (M > 4 * BM) ? 3 : 1;   // two or more 512-token tiles: pair CTAs so they share the generated operand
     switch (cfg) {
-        case 2: return launch_noise_gemm<1, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-        case 3: return launch_noise_gemm<2, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-        case 4: return launch_noise_gemm<4, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-        case 5: return launch_noise_gemm<4, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-        case 6: return launch_noise_gemm<8, 2, 256, 3, 3>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
-        default: return launch_noise_gemm<1, 4, 128, 2, 4>(d, d_t, a, M, N, Kc, lda, ldd, ldd_t, lin, status, st);
+        case 2: return launch_noise_gemm<1, 2, 256, 3, 3>(d, a, M, N, Kc, lda, ldd, lin, status, st);
+        case 3: return launch_noise_gemm<2, 4, 128, 2, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);
+        case 4: return launch_noise_gemm<4, 4, 128, 2, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);
+        case 5: return launch_noise_gemm<4, 2, 256, 3, 3>(d, a, M, N, Kc, lda, ldd, lin, status, st);
+        case 6: return launch_noise_gemm<8, 2, 256, 3, 3>(d, a, M, N, Kc, lda, ldd, lin, status, st);
+        default: return launch_noise_gemm<1, 4, 128, 2, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);
     }
 }
 

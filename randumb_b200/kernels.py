@@ -207,20 +207,19 @@ def gemv_bwd(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, r
 
 # ------------------------------------------------------------------------------------------ building blocks
 def gemm_noise(a: torch.Tensor, n: int, seed: int, transposed: bool = False, row0: int = 0, col0: int = 0,
-               impl: int = IMPL_AUTO, out_dtype: Optional[torch.dtype] = None, want_transpose: bool = False):
+               impl: int = IMPL_AUTO, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """D[M, n] = a[M, Kc] @ G.T with G generated (see rdb_gemm_noise)."""
     dev = _need_cuda(a)
     assert a.dim() == 2 and a.is_contiguous()
     M, Kc = a.shape
     out_dtype = out_dtype or a.dtype
     d = torch.empty((M, n), dtype=out_dtype, device=dev)
-    d_t = torch.empty((n, M), dtype=out_dtype, device=dev) if want_transpose else None
     with torch.cuda.device(dev):
-        rc = _lib.lib().rdb_gemm_noise(_ptr(d), _ptr(d_t), _ptr(a), M, n, Kc, Kc, n, M, _dt(a.dtype), _dt(out_dtype),
+        rc = _lib.lib().rdb_gemm_noise(_ptr(d), _ptr(a), M, n, Kc, Kc, n, _dt(a.dtype), _dt(out_dtype),
                                        1 if transposed else 0, row0, col0, _seed(seed), impl, _ptr(status_buffer(dev)),
                                        _stream(dev))
     _lib.check(rc, "rdb_gemm_noise")
-    return (d, d_t) if want_transpose else d
+    return d
 
 
 def gemm_dense(a: torch.Tensor, b: torch.Tensor, a_kmajor: bool = True, b_kmajor: bool = True,

@@ -48,7 +48,7 @@ def test_argument_errors_are_caught_on_host(built_lib):
     assert L.rdb_linear_fwd(None, None, None, None, 0, 4, 4, 4, 4, 0, 0, 0, 0, 0, None, None) == -1   # null y
     assert L.rdb_linear_fwd(None, None, None, None, 0, 0, 4, 4, 4, 0, 0, 0, 0, 0, None, None) == 0    # T == 0
     assert L.rdb_linear_bwd(None, None, None, None, None, None, 0, 4, 4, 4, 4, 0, 0, 0, 0, 0, None, None) == 0  # nothing asked
-    assert L.rdb_gemm_noise(None, None, None, 4, 4, 4, 2, 4, 0, 0, 0, 0, 0, 0, 0, 0, None, None) == -2  # lda < Kc
+    assert L.rdb_gemm_noise(None, None, 4, 4, 4, 2, 4, 0, 0, 0, 0, 0, 0, 0, None, None) == -2  # lda < Kc
     assert L.rdb_gemm_dense(None, None, None, 4, 4, 4, 4, 4, 2, 0, 0, 0, 1, 1, 0, None, None) == -2     # ldd < N
     assert L.rdb_set_option(99, 1) == -6
 

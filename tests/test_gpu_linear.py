@@ -137,13 +137,6 @@ def test_dense_products_all_operand_layouts(K, akm, bkm, out):
     assert O.close(d2, ref, 1e-2 if out == torch.bfloat16 else 1e-5)
 
 
-def test_transposed_output_of_generated_product(K):
-    g = torch.Generator().manual_seed(5)
-    A = torch.randn(600, 1000, generator=g).bfloat16().cuda()
-    d, dt = K.gemm_noise(A, 136, 11, True, 0, impl=K.IMPL_UMMA, want_transpose=True)
-    assert torch.equal(d.t().contiguous(), dt)
-
-
 # ---- edge cases ----------------------------------------------------------------------------------------
 def test_empty_and_degenerate(K):
     dev = "cuda"
