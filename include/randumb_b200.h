@@ -74,13 +74,13 @@ const char *rdb_strerror(int code);
 
 /*
  * Process-wide tuning switches (not part of the reference surface; defaults are the tuned ones).
- *   RDB_OPT_NOISE_TILE   work unit of the generated-operand kernel; every hash is reused by
- *                        (cluster size) x (token sub-tiles) x 128 tokens:
- *                        0: automatic (3 when there are at least two 512-token tiles, else 1)
- *                        1: 1 CTA,  4 sub-tiles, 128 generated rows      2: 1 CTA,  2 sub-tiles, 256 rows
- *                        3: 2 CTAs, 4 sub-tiles, 128 rows                4: 4 CTAs, 4 sub-tiles, 128 rows
- *                        5: 4 CTAs, 2 sub-tiles, 256 rows                6: 8 CTAs, 2 sub-tiles, 256 rows
- *                        (CTAs of a cluster share each generated stage through distributed shared memory)
+ *   RDB_OPT_NOISE_TILE   kernel variant / work unit of the generated-operand product:
+ *                        0: automatic (7 for more than 512 tokens with a contraction of at most 4096, else 1)
+ *                        single-CTA MMAs (cta_group::1), (cluster size, token sub-tiles, generated rows):
+ *                          1: (1, 4, 128)   2: (1, 2, 256)   3: (2, 4, 128)   4: (4, 4, 128)   5: (4, 2, 256)   6: (1, 4, 128) with a deeper ring
+ *                          CTAs of a cluster share each generated stage through distributed shared memory
+ *                        CTA-pair MMAs (cta_group::2), 512 tokens x 256 generated rows per pair:
+ *                          7: one pair per cluster   8: two pairs   9: four pairs sharing the generated rows
  * Returns the previous value, or RDB_ERR_UNSUPPORTED for an unknown key.
  */
 #define RDB_OPT_NOISE_TILE 1

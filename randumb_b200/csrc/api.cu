@@ -94,7 +94,7 @@ extern "C" int rdb_set_option(int key, int value) {
     switch (key) {
         case RDB_OPT_NOISE_TILE:
             prev = g_noise_tile;
-            g_noise_tile = (value >= 0 && value <= 6) ? value : 0;
+            g_noise_tile = (value >= 0 && value <= 9) ? value : 0;
             set_noise_cfg(g_noise_tile);
             return prev;
         default: return RDB_ERR_UNSUPPORTED;

@@ -102,6 +102,15 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     return true;
 }
 
+// Whole-warp wait: lane 0 polls the barrier, the result is broadcast.  Keeps 31 of 32 threads from hammering
+// the barrier word while asynchronous arrivals (TMA bytes, st.async bytes, remote arrives) try to update it.
+template <bool CLUSTER>
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = CLUSTER ? mbar_wait_cluster(bar, parity, abort_flag) : mbar_wait(bar, parity, abort_flag);
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---------------------------------------------------------------- thread-block clusters
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -123,6 +132,14 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t caddr, uint32_t a, uint32
 __device__ __forceinline__ void st_async_v4(uint32_t caddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t cbar) {
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
                  ::"r"(caddr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(cbar) : "memory");
+}
+// Bulk copy of `bytes` (multiple of 16) from this CTA's shared memory into the shared memory of a CTA of the
+// cluster; completes `bytes` transaction bytes on `cbar`, an mbarrier in the destination CTA.  One
+// instruction moves a whole slice -- the cluster interconnect handles few large packets far better than
+// many 16-byte ones.  No multicast is involved.
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t cdst, uint32_t src, uint32_t bytes, uint32_t cbar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(cdst), "r"(src), "r"(bytes), "r"(cbar) : "memory");
 }
 // Arrive on a barrier that may live in another CTA of the cluster (release at cluster scope).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t caddr) {
@@ -170,6 +187,35 @@ __device__ __forceinline__ void tmem_relinquish() {
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// ---- CTA-pair (cta_group::2) forms: both CTAs of an even/odd pair allocate together; one thread of the
+// even CTA issues MMAs whose 256 rows are split over the two CTAs' TMEM and whose B operand is read half
+// from each CTA's shared memory.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// `bar` is a shared::cluster address: the barrier may live in either CTA of the pair (or of the cluster).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base_lane + i),

@@ -70,6 +70,26 @@ __device__ __forceinline__ void store_row32<float>(float *dst, const uint32_t (&
     }
 }
 
+// One 32-column slice of an accumulator row -> 32 bf16 = 64 contiguous bytes of the output row.
+__device__ __forceinline__ void store_row32_bf16(__nv_bfloat16 *dst, const uint32_t (&r)[32], int ncols, bool wide) {
+    uint32_t p[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        p[j] = *reinterpret_cast<uint32_t *>(&h);
+    }
+    if (wide && ncols == 32) {   // two 256-bit stores: whole 32-byte sectors per instruction
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(p[0]), "r"(p[1]), "r"(p[2]),
+                     "r"(p[3]), "r"(p[4]), "r"(p[5]), "r"(p[6]), "r"(p[7]) : "memory");
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16), "r"(p[8]), "r"(p[9]), "r"(p[10]),
+                     "r"(p[11]), "r"(p[12]), "r"(p[13]), "r"(p[14]), "r"(p[15]) : "memory");
+    } else {
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+            if (v * 8 < ncols) *reinterpret_cast<uint4 *>(dst + v * 8) = make_uint4(p[4 * v], p[4 * v + 1], p[4 * v + 2], p[4 * v + 3]);
+    }
+}
+
 struct PipeState {
     uint32_t idx = 0, phase = 0;
     template <int STAGES> __device__ __forceinline__ void advance() {
@@ -277,7 +297,7 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
         for (int64_t ct = cluster_id; ct < total_ctiles; ct += num_clusters) {
             const int64_t m0 = m_base(ct);
             const int64_t n0 = (ct % tiles_n) * BN;
-            if (!mbar_wait(smem_u32(&bar_tmem_full), tphase, abortp)) {
+            if (!mbar_wait_warp<false>(smem_u32(&bar_tmem_full), tphase, abortp)) {
                 raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
                 break;
             }
@@ -380,6 +400,342 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ================================================================================================
+// noise_pair_kernel: the generated-operand product on CTA pairs (tcgen05 cta_group::2)
+// ================================================================================================
+// A pair of CTAs computes 512 tokens x 256 generated rows per work unit.  Every MMA has M = 256 (rows
+// 0-127 from the even CTA's shared memory and TMEM, rows 128-255 from the odd CTA's), N = 256 with each CTA
+// holding one half (128 rows) of the generated operand, so a CTA reads only 8 KB of shared memory per MMA
+// instead of 12 KB and the tensor pipe is no longer limited by shared-memory bandwidth.
+// NP pairs form one thread-block cluster (2*NP CTAs) and work on NP token tiles against the SAME generated
+// rows: the NP CTAs that need the same half hash 128/NP rows each and send their 16-byte chunks to each
+// other with asynchronous distributed-shared-memory stores (transaction bytes complete the receiver's
+// `full` barrier).  Only plain TMA loads, st.async, mapa, remote mbarrier arrives and cluster barriers cross
+// CTAs.
+//
+// Per-CTA barriers of ring stage s:
+//   full[s]      A sub-tiles (TMA) and this CTA's half of the generated stage (st.async) have landed;
+//                on the even CTA it also counts one arrival from the odd CTA ("my part is in place too")
+//   free_[s]     the pair's MMAs have finished reading the stage (commit from the even CTA's MMA thread)
+//   free_all[s]  ... in all NP CTAs that receive the same generated half (NP > 1)
+template <int NP, int D>
+struct PairCfg {
+    static constexpr int MT = 2;                                       // accumulators per CTA (256 columns each)
+    static constexpr int BN = 256;                                     // generated rows per work unit
+    static constexpr int HALF = BN / 2;                                // ... of which this CTA holds 128
+    static constexpr int A_PART = MT * SUB_BYTES;
+    static constexpr int B_PART = HALF * BK * 2;
+    static constexpr int STAGE = A_PART + B_PART;
+    static constexpr int GEN_WARPS = 8;
+    static constexpr int GEN_THREADS = GEN_WARPS * 32;
+    static constexpr int FIRST_EPI_WARP = 2;
+    static constexpr int FIRST_GEN_WARP = 6;
+    static constexpr int FULL_RELAY_WARP = FIRST_GEN_WARP + GEN_WARPS;  // odd CTA -> even CTA: "stage is full here"
+    static constexpr int FREE_RELAY_WARP = FULL_RELAY_WARP + 1;         // "stage is free here" -> the CTAs that write into it
+    static constexpr int THREADS = (FREE_RELAY_WARP + 1) * 32;
+    static constexpr int SMEM_DYN = D * STAGE + 1024;
+    static constexpr int GEN_ROWS = HALF / NP;                          // rows of the half this CTA hashes
+    static constexpr int CHUNKS = (GEN_ROWS * 8) / GEN_THREADS;
+    static_assert(NP == 1 || NP == 2 || NP == 4, "pairs per cluster");
+    static_assert((GEN_ROWS * 8) % GEN_THREADS == 0 && CHUNKS >= 1, "generator chunking");
+    static_assert(SMEM_DYN <= 232448 - 512, "shared memory");
+};
+
+template <int NP, int D>
+__global__ void __launch_bounds__(PairCfg<NP, D>::THREADS, 1)
+noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__restrict__ d, int64_t ldd, int64_t M,
+                  int64_t N, int64_t Kc, Sq5Lin lin, int32_t *status, long long *prof) {
+    using Cfg = PairCfg<NP, D>;
+    long long pc0 = 0, pc1 = 0, pc2 = 0;
+    constexpr int MT = Cfg::MT, BN = Cfg::BN;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[D], bar_free[D], bar_free_all[D], bar_tmem_full, bar_tmem_empty[MT];
+    __shared__ uint32_t tmem_holder;
+    __shared__ int abort_flag;
+
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;   // stage s: A sub-tiles, then this CTA's half of the generated tile
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t half = rank & 1;          // which 128 generated rows / which 128 token rows of every MMA live here
+    const uint32_t pair = rank >> 1;
+    const bool leader = (half == 0);         // the even CTA of the pair issues the MMAs
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < D; ++s) {
+            // TMA thread's arrive.expect_tx (+ the odd CTA's "complete" on the even CTA); the generated bytes
+            // arrive as transaction bytes of asynchronous stores
+            mbar_init(smem_u32(&bar_full[s]), leader ? 2 : 1);
+            mbar_init(smem_u32(&bar_free[s]), 1);
+            mbar_init(smem_u32(&bar_free_all[s]), NP);
+        }
+        mbar_init(smem_u32(&bar_tmem_full), 1);
+        for (int s = 0; s < MT; ++s) mbar_init(smem_u32(&bar_tmem_empty[s]), 8);   // 4 epilogue warps of each CTA of the pair
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(&tmem_holder), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+    volatile int *abortp = &abort_flag;
+
+    const int64_t tiles_n = (N + BN - 1) / BN;
+    const int64_t tiles_m = (M + (int64_t)MT * 2 * BM - 1) / ((int64_t)MT * 2 * BM);   // 512-token pair tiles
+    const int64_t ctiles_m = (tiles_m + NP - 1) / NP;
+    const int64_t total_ctiles = ctiles_m * tiles_n;
+    const int64_t cluster_id = blockIdx.x / (2 * NP);
+    const int64_t num_clusters = gridDim.x / (2 * NP);
+    const int num_kb = (int)((Kc + BK - 1) / BK);
+    // first token row of this pair's tile; accumulator s of this CTA covers rows m0 + s*256 + half*128 + [0,128)
+    auto m_base = [&](int64_t ct) { return ((ct / tiles_n) * NP + pair) * (int64_t)MT * 2 * BM; };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (this CTA's A rows)
+        if (lane == 0) {
+            prefetch_tmap(&tmap_a);
+            PipeState st;
+            bool ok = true;
+            for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
+                const int64_t m0 = m_base(ct) + half * BM;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const long long tw = prof ? clock64() : 0;
+                    if (!mbar_wait_cluster(smem_u32(&bar_free[st.idx]), st.phase ^ 1, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    if (prof) pc0 += clock64() - tw;
+                    const uint32_t fb = smem_u32(&bar_full[st.idx]);
+                    mbar_arrive_expect_tx(fb, Cfg::STAGE);   // A bytes by TMA + the generated half by st.async
+#pragma unroll
+                    for (int s = 0; s < MT; ++s)
+                        tma_load_2d(smem_base + st.idx * Cfg::STAGE + s * SUB_BYTES, &tmap_a, fb, kb * BK,
+                                    (int32_t)(m0 + s * 2 * BM));
+                    st.advance<D>();
+                }
+            }
+            if (prof) prof[blockIdx.x * 16 + 4] = pc0;
+            if (!ok) {
+                for (int s = 0; s < D; ++s) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&bar_full[s]), 0) && !mbar_try_wait(smem_u32(&bar_full[s]), 1)) {
+                        if (clock64() - t0 > 20000000LL) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (even CTA of the pair only)
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BN, 0, 0);
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t peer = rank ^ 1u;
+            PipeState st;
+            uint32_t tphase = 0;
+            bool ok = true;
+            const long long t_start = prof ? clock64() : 0;
+            for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
+                for (int kb = 0; kb < num_kb && ok; ++kb) {
+                    const long long tw = prof ? clock64() : 0;
+                    if (!mbar_wait_cluster(smem_u32(&bar_full[st.idx]), st.phase, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
+                        ok = false;
+                        break;
+                    }
+                    if (prof) pc0 += clock64() - tw;
+                    fence_proxy_async_smem();
+                    tc_fence_after_sync();
+                    const uint32_t a_lo = smem_desc_lo(smem_base + st.idx * Cfg::STAGE, 0);
+                    const uint32_t b_lo = smem_desc_lo(smem_base + st.idx * Cfg::STAGE + Cfg::A_PART, 0);
+#pragma unroll
+                    for (int s = 0; s < MT; ++s) {
+                        if (kb == 0) {
+                            // accumulator s is reusable once both CTAs' epilogues have drained it
+                            const long long te = prof ? clock64() : 0;
+                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[s]), tphase ^ 1, abortp)) {
+                                raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            if (prof) pc2 += clock64() - te;
+                        }
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t adesc = pack_desc(a_lo + ((s * SUB_BYTES + k * UMMA_K * 2) >> 4), desc_hi);
+                            const uint64_t bdesc = pack_desc(b_lo + ((k * UMMA_K * 2) >> 4), desc_hi);
+                            umma_bf16_pair(tmem_base + s * BN, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                    }
+                    // the stage is free in both CTAs of the pair once these MMAs have completed
+                    umma_commit_pair(smem_u32(&bar_free[st.idx]));
+                    umma_commit_pair(mapa(smem_u32(&bar_free[st.idx]), peer));
+                    st.advance<D>();
+                }
+                if (ok) {
+                    umma_commit_pair(smem_u32(&bar_tmem_full));
+                    umma_commit_pair(mapa(smem_u32(&bar_tmem_full), peer));
+                }
+                tphase ^= 1;
+            }
+            if (prof) {
+                prof[blockIdx.x * 16 + 0] = pc0;
+                prof[blockIdx.x * 16 + 2] = pc2;
+                prof[blockIdx.x * 16 + 3] = clock64() - t_start;
+            }
+        }
+    } else if (warp < Cfg::FIRST_GEN_WARP) {
+        // ------------------------------------------------------------------ epilogue (4 warps, this CTA's 128 rows)
+        const int q = warp & 3;
+        const bool wide = ((ldd & 15) == 0) && ((reinterpret_cast<uintptr_t>(d) & 31) == 0);
+        const uint32_t leader_rank = rank & ~1u;
+        uint32_t tphase = 0;
+        for (int64_t ct = cluster_id; ct < total_ctiles; ct += num_clusters) {
+            const int64_t m0 = m_base(ct) + half * BM;
+            const int64_t n0 = (ct % tiles_n) * BN;
+            if (!mbar_wait_warp<true>(smem_u32(&bar_tmem_full), tphase, abortp)) {
+                raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
+                break;
+            }
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int s = 0; s < MT; ++s) {
+                const int64_t row = m0 + s * 2 * BM + q * 32 + lane;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    uint32_t r0[32], r1[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * BN + c0);
+                    tmem_ld_32x32(taddr, r0);
+                    tmem_ld_32x32(taddr + 32, r1);
+                    tmem_ld_wait();
+                    const int64_t col = n0 + c0;
+                    const int nc0 = (int)((N - col) < 32 ? (N - col) : 32);
+                    const int nc1 = (int)((N - col - 32) < 32 ? (N - col - 32) : 32);
+                    if (row < M) {
+                        if (nc0 > 0) store_row32_bf16(d + row * ldd + col, r0, nc0, wide);
+                        if (nc1 > 0) store_row32_bf16(d + row * ldd + col + 32, r1, nc1, wide);
+                    }
+                }
+                // accumulator s of this CTA is drained: tell the MMA thread of the pair
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[s]), leader_rank));
+            }
+            tphase ^= 1;
+        }
+    } else if (warp < Cfg::FULL_RELAY_WARP) {
+        // ------------------------------------------------------------------ generators (8 warps)
+        const int tg = threadIdx.x - Cfg::FIRST_GEN_WARP * 32;
+        constexpr int CHUNKS = Cfg::CHUNKS;
+        PipeState st;
+        bool ok = true;
+        for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
+            const int64_t n0 = (ct % tiles_n) * BN + half * Cfg::HALF;   // first generated row of this CTA's half
+            uint32_t bstart[CHUNKS];
+            uint32_t soff[CHUNKS];
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+                const int id = tg + c * Cfg::GEN_THREADS;
+                const int rowi = (int)pair * Cfg::GEN_ROWS + (id >> 3), ch = id & 7;   // row inside the half
+                bstart[c] = lin.base + (uint32_t)(n0 + rowi) * lin.sn + (uint32_t)(ch * 8) * lin.sk;
+                soff[c] = (uint32_t)(Cfg::A_PART + rowi * 128 + ((ch ^ (rowi & 7)) << 4));
+            }
+            const uint32_t kb_step = (uint32_t)BK * lin.sk;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const uint32_t wb = NP > 1 ? smem_u32(&bar_free_all[st.idx]) : smem_u32(&bar_free[st.idx]);
+                const long long tw = prof ? clock64() : 0;
+                if (!mbar_wait_cluster(wb, st.phase ^ 1, abortp)) {
+                    raise_abort(abortp, status, RDB_STATUS_TIMEOUT_GENERATOR);
+                    ok = false;
+                    break;
+                }
+                const long long tc = prof ? clock64() : 0;
+                const uint32_t stage = smem_base + st.idx * Cfg::STAGE;
+                const uint32_t fb = smem_u32(&bar_full[st.idx]);
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c) {
+                    uint32_t p[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float f0 = sq5_to_float(sq5_tail(bstart[c] + (uint32_t)(2 * j) * lin.sk));
+                        const float f1 = sq5_to_float(sq5_tail(bstart[c] + (uint32_t)(2 * j + 1) * lin.sk));
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(f0, f1);
+                        p[j] = *reinterpret_cast<uint32_t *>(&h2);
+                    }
+                    // asynchronous 16-byte stores to every CTA of the cluster that holds this half (this CTA included);
+                    // each completes its bytes on the receiver's `full` barrier -- no fence, no separate arrive
+#pragma unroll
+                    for (int qd = 0; qd < NP; ++qd) {
+                        const uint32_t dst = 2u * qd + half;
+                        st_async_v4(mapa(stage + soff[c], dst), p[0], p[1], p[2], p[3], mapa(fb, dst));
+                    }
+                    bstart[c] += kb_step;
+                }
+                if (prof) { pc0 += tc - tw; pc1 += clock64() - tc; }
+                st.advance<D>();
+            }
+        }
+        if (prof && tg == 0) {
+            prof[blockIdx.x * 16 + 5] = pc0;
+            prof[blockIdx.x * 16 + 6] = pc1;
+        }
+    } else if (warp == Cfg::FULL_RELAY_WARP) {
+        // ------------------------------------------------------------------ odd CTA: tell the even CTA a stage is complete here
+        if (lane == 0 && !leader) {
+            const uint32_t leader_rank = rank & ~1u;
+            PipeState st;
+            bool ok = true;
+            for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_cluster(smem_u32(&bar_full[st.idx]), st.phase, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    fence_proxy_async_smem();
+                    mbar_arrive_cluster(mapa(smem_u32(&bar_full[st.idx]), leader_rank));
+                    st.advance<D>();
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ tell the CTAs that write this half that the stage is free
+        if (lane == 0 && NP > 1) {
+            PipeState st;
+            bool ok = true;
+            for (int64_t ct = cluster_id; ct < total_ctiles && ok; ct += num_clusters) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_cluster(smem_u32(&bar_free[st.idx]), st.phase, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_GENERATOR);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fa = smem_u32(&bar_free_all[st.idx]);
+#pragma unroll
+                    for (int qd = 0; qd < NP; ++qd) mbar_arrive_cluster(mapa(fa, 2u * qd + half));
+                    st.advance<D>();
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();   // no CTA retires (or frees TMEM) while a peer may still use it
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -525,7 +881,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int64_t m0 = (tile / tiles_n) * BM;
             const int64_t n0 = (tile % tiles_n) * BN;
-            if (!mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, abortp)) {
+            if (!mbar_wait_warp<false>(smem_u32(&bar_tmem_full[acc]), acc_phase, abortp)) {
                 raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
                 break;
             }
@@ -666,6 +1022,43 @@ static int launch_noise_gemm(void *d, const void *a, int64_t M, int64_t N, int64
     return launch_status();
 }
 
+template <int NP, int D>
+static int launch_noise_pair(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, Sq5Lin lin,
+                             int32_t *status, cudaStream_t st) {
+    using Cfg = PairCfg<NP, D>;
+    constexpr int CSZ = 2 * NP;
+    CUtensorMap ta;
+    int rc = make_tmap(&ta, a, Kc, M, lda, BK, BM);
+    if (rc) return rc;
+    auto kern = noise_pair_kernel<NP, D>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
+    if (e != cudaSuccess) return (int)e;
+    const int64_t ctiles = cdiv64(cdiv64(M, 4 * BM), NP) * cdiv64(N, Cfg::BN);
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(Cfg::THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_DYN;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CSZ;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(CSZ);
+    int max_clusters = sm_count() / CSZ, n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) max_clusters = n;
+    else (void)cudaGetLastError();
+    const int64_t nclusters = ctiles < max_clusters ? ctiles : max_clusters;
+    cfg.gridDim = dim3((unsigned)(nclusters * CSZ));
+    __nv_bfloat16 *dp = reinterpret_cast<__nv_bfloat16 *>(d);
+    long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 16 * sizeof(long long)) ? g_prof : nullptr;
+    e = cudaLaunchKernelEx(&cfg, kern, ta, dp, ldd, M, N, Kc, lin, status, prof);
+    if (e != cudaSuccess) return (int)e;
+    return launch_status();
+}
+
 // RDB_OPT_NOISE_TILE: (cluster size, token sub-tiles, generated rows) per work unit
 static int g_noise_cfg = 0;
 void set_noise_cfg(int v) { g_noise_cfg = v; }
@@ -674,13 +1067,18 @@ int umma_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, in
                     int32_t *status, cudaStream_t st) {
     if (M == 0 || N == 0) return RDB_OK;
     int cfg = g_noise_cfg;
-    if (cfg == 0) cfg = (M > 4 * BM) ? 3 : 1;   // two or more 512-token tiles: pair CTAs so they share the generated operand
+    // more than one 512-token tile and a short contraction (many tiles, epilogue matters): CTA pairs (cta_group::2);
+    // otherwise one CTA per 512-token tile
+    if (cfg == 0) cfg = (M > 4 * BM && Kc <= 4096) ? 7 : 1;
     switch (cfg) {
         case 2: return launch_noise_gemm<1, 2, 256, 3, 3>(d, a, M, N, Kc, lda, ldd, lin, status, st);
         case 3: return launch_noise_gemm<2, 4, 128, 2, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);
         case 4: return launch_noise_gemm<4, 4, 128, 2, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);
         case 5: return launch_noise_gemm<4, 2, 256, 3, 3>(d, a, M, N, Kc, lda, ldd, lin, status, st);
-        case 6: return launch_noise_gemm<8, 2, 256, 3, 3>(d, a, M, N, Kc, lda, ldd, lin, status, st);
+        case 6: return launch_noise_gemm<1, 4, 128, 2, 6>(d, a, M, N, Kc, lda, ldd, lin, status, st);
+        case 7: return launch_noise_pair<1, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);
+        case 8: return launch_noise_pair<2, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);
+        case 9: return launch_noise_pair<4, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);
         default: return launch_noise_gemm<1, 4, 128, 2, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);
     }
 }

@@ -84,7 +84,7 @@ def test_bf16_layer_tensor_cores(K, T, Kin, N, R, seed, row0):
     _check(K, T, Kin, N, R, torch.bfloat16, seed, row0, K.PATH_FACTORED, K.IMPL_UMMA, BF16_TOL)
 
 
-@pytest.mark.parametrize("tile", [1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("tile", [1, 2, 3, 4, 5, 6, 7, 8, 9])
 def test_bf16_layer_every_work_unit_shape(K, tile):
     """Every (cluster size, sub-tiles, generated rows) variant of the generated-operand kernel, on a shape
     with ragged tiles and an odd number of token tiles per cluster."""
