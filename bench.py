@@ -188,7 +188,8 @@ def metric_name(workload):
 
 def workload_config(name, cfg, gpus):
     par = {"gemm": f"dp{gpus} (tokens per rank fixed, dC all-reduce)" if gpus > 1 else "single GPU",
-           "sharded": f"output rows split over {gpus} ranks, dC and dX all-reduce" if gpus > 1 else "single GPU",
+           "sharded": f"output rows split over {gpus} ranks (zero weight traffic); z all-gather, g all-reduce, dX all-gather, "
+                      f"dC all-reduce" if gpus > 1 else "single GPU",
            "gemv": "replicas only"}[name]
     return {"workload": f"{name}: x[{cfg['T']}x{cfg['K']}] {cfg['dtype']}, virtual W[{cfg['N']}x{cfg['K']}], d_c={cfg['R']}, "
                         f"seed={cfg['seed']}, fwd + dX + dC",
@@ -216,9 +217,10 @@ def run_ours(args, cfg):
     dt = torch.bfloat16 if cfg["dtype"] == "bf16" else torch.float32
     T, Kin, N, R, seed = cfg["T"], cfg["K"], cfg["N"], cfg["R"], cfg["seed"]
     row0, n_local = 0, N
-    if args.workload == "sharded" and world > 1:
-        lo, hi = rb.parallel.shard_range(N, world, rank)
-        row0, n_local = lo, hi - lo
+    plan = None
+    if args.workload == "sharded":
+        plan = rb.parallel.ShardedLayerPlan(T, N, world, rank)
+        row0, n_local = plan.row_lo, plan.row_hi - plan.row_lo
     g = torch.Generator().manual_seed(1003 + (rank if args.workload == "gemm" else 0))
     x_host = torch.randn(T, Kin, generator=g).to(dt).pin_memory()
     C = (torch.randn(R, Kin, generator=torch.Generator().manual_seed(7)) * cfg["coef_std"]).to(dt).to(dev)
@@ -227,12 +229,15 @@ def run_ours(args, cfg):
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.workload == "gemv" else None
 
     def step():
+        if plan is not None and world > 1:
+            # rows split over ranks: z all-gather, g all-reduce, dX all-gather, dC all-reduce
+            y = rb.parallel.sharded_forward(x, C, seed, plan)
+            dx, dc = rb.parallel.sharded_backward(dy, x, C, seed, plan)
+            return y, dx, dc
         y = K.linear_fwd(x, C, seed, n_local, row0)
         dx, dc = K.linear_bwd(dy, x, C, seed, row0)
         if world > 1:
             dist.all_reduce(dc)
-            if args.workload == "sharded":
-                dist.all_reduce(dx)
         return y, dx, dc
 
     def barrier():
@@ -313,9 +318,8 @@ def run_ours(args, cfg):
         value = world * bytes_step * args.steps / (elapsed_ms * 1e-3) / 1e9
         unit = "GB/s"
     else:
-        # every rank's algorithmic work; for the sharded layer the rows (and so the work) are split
-        per_rank = algorithmic_flops(T, Kin, n_local, R) if args.workload == "sharded" else algorithmic_flops(T, Kin, N, R)
-        total = per_rank * world if args.workload == "gemm" else _sum_over_ranks(per_rank, world, dev)
+        # data parallel: every rank does the whole layer on its own tokens; sharded: the ranks split ONE layer
+        total = algorithmic_flops(T, Kin, N, R) * (world if args.workload == "gemm" else 1)
         value = total * args.steps / (elapsed_ms * 1e-3) / 1e12
         unit = "TFLOP/s"
 
@@ -344,14 +348,6 @@ def run_ours(args, cfg):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
-
-
-def _sum_over_ranks(v, world, dev):
-    import torch.distributed as dist
-    t = torch.tensor([v], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t)
-    return float(t.item())
 
 
 def launches_per_step(workload, T):
@@ -394,6 +390,8 @@ def run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier):
         consumed[i % 2].record(torch.cuda.current_stream(dev))
         if world > 1:
             dist.all_reduce(coef.grad)
+            if args.workload == "sharded":
+                dist.all_reduce(xin.grad)              # every rank holds only its rows' contribution to dX
         val = float(loss.item())                       # device -> host read of the step's result
         coef.grad = None
         bufs[i % 2].requires_grad_(False)
@@ -426,8 +424,7 @@ def run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier):
         work = world * (3 * R * Kin * 4 + 4 * (3 * Kin + 2 * N + 2 * R)) / 1e9
         unit = "GB/s"
     else:
-        per_rank = algorithmic_flops(T, Kin, n_local, R)
-        work = (per_rank * world if args.workload == "gemm" else _sum_over_ranks(per_rank, world, dev)) / 1e12
+        work = algorithmic_flops(T, Kin, N, R) * (world if args.workload == "gemm" else 1) / 1e12
         unit = "TFLOP/s"
     return {"value": work * n_e2e / (ms * 1e-3), "unit": unit, "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
             "d2h_bytes_per_step": 4, "steps": n_e2e, "ms_per_step": ms / n_e2e,

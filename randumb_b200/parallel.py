@@ -3,8 +3,9 @@ exchanges the path has.
 
 * Row sharding of one large virtual layer: rank r owns output rows ``[r*N/G, (r+1)*N/G)`` and
   regenerates exactly those noise rows from ``(seed, row0)`` -- no weight bytes ever move.  The only
-  traffic is activations: optionally the output ``y`` (all-gathered along features) in forward, and the
-  sums over ranks of the input gradient and of ``dC`` in backward.
+  traffic is activations: ``sharded_forward`` / ``sharded_backward`` split the row-independent products by
+  tokens and exchange the small ``z`` (all-gather) and ``g`` (all-reduce), then ``dX`` (all-gather) and
+  ``dC`` (all-reduce); ``RowShardedRandumbLinear`` is the simple module form (optionally all-gathers ``y``).
 * Data parallel training: every rank holds all of ``C``; the coefficient gradients are summed with one
   flat all-reduce per step.  (The reference's only parallelism is DDP in its GPT app:
   modded-nanogpt/train_gpt2.py:261, 346, 441.)
@@ -142,6 +143,66 @@ class RowShardedRandumbLinear(torch.nn.Module):
             y2 = all_gather_cols(y.reshape(-1, y.shape[-1]), [hi - lo for lo, hi in self.ranges], self.group)
             y = y2.reshape(*lead, self.out_features)
         return y
+
+
+# ------------------------------------------------------------------------------------------------
+# row-sharded layer with the row-independent products split by tokens
+# ------------------------------------------------------------------------------------------------
+def _all_gather_rows_plain(x: torch.Tensor, sizes: Sequence[int], group) -> torch.Tensor:
+    if len(sizes) == 1:
+        return x
+    if all(n == sizes[0] for n in sizes):
+        out = x.new_empty((sum(sizes), x.shape[1]))
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        return out
+    return torch.cat(_gather_blocks(x, sizes, 0, group), dim=0)
+
+
+class ShardedLayerPlan:
+    """Who computes what when output rows are split over ``world`` ranks.
+
+    Rank r owns noise rows ``[row_lo, row_hi)`` (regenerated locally from ``row0 = row_lo``) and, for the
+    products that do not depend on the row split (``z = x C^T``, ``dX = g C``, ``dC = g^T x``), the token
+    slice ``[tok_lo, tok_hi)``; computing those on every rank would cost more than the sharded part.
+    """
+
+    def __init__(self, tokens: int, out_features: int, world: int, rank: int):
+        self.world, self.rank = world, rank
+        self.row_ranges = all_shard_ranges(out_features, world)
+        self.tok_ranges = all_shard_ranges(tokens, world)
+        self.row_lo, self.row_hi = self.row_ranges[rank]
+        self.tok_lo, self.tok_hi = self.tok_ranges[rank]
+        self.tok_sizes = [hi - lo for lo, hi in self.tok_ranges]
+
+
+def sharded_forward(x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan, group=None) -> torch.Tensor:
+    """y[:, row_lo:row_hi] for replicated x[T, K], coef[R, K]: token-sliced z, all-gather z (T x R, small),
+    then the generated-operand product for this rank's rows.  bf16, tensor-core kernels."""
+    from . import kernels as K
+    z_loc = K.gemm_dense(x[plan.tok_lo:plan.tok_hi].contiguous(), coef)                      # [t_r, R]
+    z = _all_gather_rows_plain(z_loc, plan.tok_sizes, group) if plan.world > 1 else z_loc
+    return K.gemm_noise(z, plan.row_hi - plan.row_lo, seed, False, plan.row_lo)               # [T, n_r]
+
+
+def sharded_backward(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan,
+                     group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(dX[T, K], dC[R, K]) from this rank's slice dY[:, row_lo:row_hi]: the partial g = dY_r S_r is summed over
+    ranks (T x R, small), then dX and dC are computed for this rank's tokens and exchanged."""
+    from . import kernels as K
+    R = coef.shape[0]
+    g = K.gemm_noise(dy_local.contiguous(), R, seed, True, plan.row_lo)                       # partial [T, R]
+    if plan.world > 1:
+        dist.all_reduce(g, group=group)
+    g_loc = g[plan.tok_lo:plan.tok_hi].contiguous()
+    x_loc = x[plan.tok_lo:plan.tok_hi].contiguous()
+    dx_loc = K.gemm_dense(g_loc, coef, True, False)                                           # [t_r, K]
+    dc = K.gemm_dense(g_loc, x_loc, False, False)                                             # partial [R, K]
+    if plan.world > 1:
+        dist.all_reduce(dc, group=group)
+        dx = _all_gather_rows_plain(dx_loc, plan.tok_sizes, group)
+    else:
+        dx = dx_loc
+    return dx, dc
 
 
 # ------------------------------------------------------------------------------------------------
