@@ -299,7 +299,7 @@ def run_ours(args, cfg):
         avg_ms = sum(a.elapsed_time(b) for a, b in evs) / len(evs)
         flops_launch = 2.0 * T * n_local * R
         achieved = flops_launch / (avg_ms * 1e-3) / 1e12
-        roofline = {"bound": "tensor", "kernel": "noise_gemm_kernel (y = z S^T and g = dY S launches)", "achieved": achieved,
+        roofline = {"bound": "tensor", "kernel": "noise_pair_kernel (y = z S^T) and noise_gemm_kernel (g = dY S), average over both launches", "achieved": achieved,
                     "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                     "peak_source": f"{peaks['src']} burst bf16", "avg_launch_ms": avg_ms, "traffic": NOISE_GEMM_DRAM_BYTES.get(args.workload)}
     else:
@@ -355,9 +355,9 @@ def launches_per_step(workload, T):
     return 4 if workload == "gemv" else 5
 
 
-# DRAM bytes per launch of noise_gemm_kernel from the ncu capture summarised under profiles/
-# (dram__bytes_read.sum + dram__bytes_write.sum, scaled to the full launch); None until captured.
-NOISE_GEMM_DRAM_BYTES = {"gemm": None, "sharded": None}
+# DRAM bytes per launch of the generated-operand kernels: dram__bytes_read.sum + dram__bytes_write.sum of the
+# ncu capture summarised under profiles/ (2048-token case, 70.7 MB), scaled by tokens to the 8192-token launch.
+NOISE_GEMM_DRAM_BYTES = {"gemm": 2.83e8, "sharded": None}
 
 
 def run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier):
