@@ -436,7 +436,8 @@ struct PairCfg {
     static constexpr int FULL_RELAY_WARP = FIRST_GEN_WARP + GEN_WARPS;  // odd CTA -> even CTA: "stage is full here"
     static constexpr int FREE_RELAY_WARP = FULL_RELAY_WARP + 1;         // "stage is free here" -> the CTAs that write into it
     static constexpr int THREADS = (FREE_RELAY_WARP + 1) * 32;
-    static constexpr int SMEM_DYN = D * STAGE + 1024;
+    static constexpr int OUT_STAGING = 4 * 2 * 32 * 128;               // per epilogue warp: two [32 rows x 64 columns] bf16 boxes
+    static constexpr int SMEM_DYN = D * STAGE + OUT_STAGING + 1024;
     static constexpr int GEN_ROWS = HALF / NP;                          // rows of the half this CTA hashes
     static constexpr int CHUNKS = (GEN_ROWS * 8) / GEN_THREADS;
     static_assert(NP == 1 || NP == 2 || NP == 4, "pairs per cluster");
@@ -446,7 +447,7 @@ struct PairCfg {
 
 template <int NP, int D>
 __global__ void __launch_bounds__(PairCfg<NP, D>::THREADS, 1)
-noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__restrict__ d, int64_t ldd, int64_t M,
+noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_d, int64_t M,
                   int64_t N, int64_t Kc, Sq5Lin lin, int32_t *status, long long *prof) {
     using Cfg = PairCfg<NP, D>;
     long long pc0 = 0, pc1 = 0, pc2 = 0;
@@ -596,9 +597,11 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
         }
     } else if (warp < Cfg::FIRST_GEN_WARP) {
         // ------------------------------------------------------------------ epilogue (4 warps, this CTA's 128 rows)
+        // TMEM -> registers -> bf16 -> swizzled staging in shared memory -> TMA tile stores: the global writes
+        // are whole 128-byte rows issued by one lane, asynchronous, and clipped at the tensor edges by the TMA.
         const int q = warp & 3;
-        const bool wide = ((ldd & 15) == 0) && ((reinterpret_cast<uintptr_t>(d) & 31) == 0);
         const uint32_t leader_rank = rank & ~1u;
+        const uint32_t stag = smem_base + D * Cfg::STAGE + (uint32_t)(warp - Cfg::FIRST_EPI_WARP) * 8192u;   // two 4 KB boxes
         uint32_t tphase = 0;
         for (int64_t ct = cluster_id; ct < total_ctiles; ct += num_clusters) {
             const int64_t m0 = m_base(ct) + half * BM;
@@ -610,29 +613,54 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
             tc_fence_after_sync();
 #pragma unroll 1
             for (int s = 0; s < MT; ++s) {
-                const int64_t row = m0 + s * 2 * BM + q * 32 + lane;
+                const int64_t row_w = m0 + s * 2 * BM + q * 32;    // first row of this warp's 32-row slab
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 64) {
-                    uint32_t r0[32], r1[32];
-                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * BN + c0);
-                    tmem_ld_32x32(taddr, r0);
-                    tmem_ld_32x32(taddr + 32, r1);
-                    tmem_ld_wait();
-                    const int64_t col = n0 + c0;
-                    const int nc0 = (int)((N - col) < 32 ? (N - col) : 32);
-                    const int nc1 = (int)((N - col - 32) < 32 ? (N - col - 32) : 32);
-                    if (row < M) {
-                        if (nc0 > 0) store_row32_bf16(d + row * ldd + col, r0, nc0, wide);
-                        if (nc1 > 0) store_row32_bf16(d + row * ldd + col + 32, r1, nc1, wide);
+                for (int c0 = 0; c0 < BN; c0 += 128) {
+                    // the previous stores of this warp must have finished reading the staging boxes
+                    if (lane == 0) bulk_wait_group_read0();
+                    __syncwarp();
+#pragma unroll
+                    for (int hb = 0; hb < 2; ++hb) {
+                        uint32_t r0[32], r1[32];
+                        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * BN + c0 + hb * 64);
+                        tmem_ld_32x32(taddr, r0);
+                        tmem_ld_32x32(taddr + 32, r1);
+                        tmem_ld_wait();
+                        const uint32_t rowaddr = stag + hb * 4096u + (uint32_t)lane * 128u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t pk[4], pl[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 2 * e]), __uint_as_float(r0[j * 8 + 2 * e + 1]));
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r1[j * 8 + 2 * e]), __uint_as_float(r1[j * 8 + 2 * e + 1]));
+                                pk[e] = *reinterpret_cast<uint32_t *>(&h0);
+                                pl[e] = *reinterpret_cast<uint32_t *>(&h1);
+                            }
+                            // 16-byte chunk j (columns 8j..8j+7) and chunk 4+j (columns 32+8j..) of this lane's 128-byte row
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)((j ^ (lane & 7)) << 4)),
+                                         "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)(((4 + j) ^ (lane & 7)) << 4)),
+                                         "r"(pl[0]), "r"(pl[1]), "r"(pl[2]), "r"(pl[3]) : "memory");
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row_w < M) {
+                        const int64_t col = n0 + c0;
+                        if (col < N) tma_store_2d(&tmap_d, stag, (int32_t)col, (int32_t)row_w);
+                        if (col + 64 < N) tma_store_2d(&tmap_d, stag + 4096u, (int32_t)(col + 64), (int32_t)row_w);
+                        bulk_commit_group();
                     }
                 }
-                // accumulator s of this CTA is drained: tell the MMA thread of the pair
+                // accumulator s of this CTA has been read out: tell the MMA thread of the pair
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[s]), leader_rank));
             }
             tphase ^= 1;
         }
+        if (lane == 0) bulk_wait_group0();   // all output tiles written before the CTA retires
     } else if (warp < Cfg::FULL_RELAY_WARP) {
         // ------------------------------------------------------------------ generators (8 warps)
         const int tg = threadIdx.x - Cfg::FIRST_GEN_WARP * 32;
@@ -1027,8 +1055,10 @@ static int launch_noise_pair(void *d, const void *a, int64_t M, int64_t N, int64
                              int32_t *status, cudaStream_t st) {
     using Cfg = PairCfg<NP, D>;
     constexpr int CSZ = 2 * NP;
-    CUtensorMap ta;
+    CUtensorMap ta, td;
     int rc = make_tmap(&ta, a, Kc, M, lda, BK, BM);
+    if (rc) return rc;
+    rc = make_tmap(&td, d, N, M, ldd, 64, 32);   // output tiles of 32 rows x 64 columns
     if (rc) return rc;
     auto kern = noise_pair_kernel<NP, D>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
@@ -1052,9 +1082,8 @@ static int launch_noise_pair(void *d, const void *a, int64_t M, int64_t N, int64
     else (void)cudaGetLastError();
     const int64_t nclusters = ctiles < max_clusters ? ctiles : max_clusters;
     cfg.gridDim = dim3((unsigned)(nclusters * CSZ));
-    __nv_bfloat16 *dp = reinterpret_cast<__nv_bfloat16 *>(d);
     long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 16 * sizeof(long long)) ? g_prof : nullptr;
-    e = cudaLaunchKernelEx(&cfg, kern, ta, dp, ldd, M, N, Kc, lin, status, prof);
+    e = cudaLaunchKernelEx(&cfg, kern, ta, td, M, N, Kc, lin, status, prof);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
