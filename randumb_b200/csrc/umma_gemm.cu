@@ -470,7 +470,8 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int s = 0; s < D; ++s) {
             // TMA thread's arrive.expect_tx (+ the odd CTA's "complete" on the even CTA); the generated bytes
             // arrive as transaction bytes of asynchronous stores
-            mbar_init(smem_u32(&bar_full[s]), leader ? 2 : 1);
+            // TMA thread's arrive.expect_tx (+ the odd CTA's "complete" on the even CTA) + every local generator thread
+            mbar_init(smem_u32(&bar_full[s]), (leader ? 2 : 1) + Cfg::GEN_THREADS);
             mbar_init(smem_u32(&bar_free[s]), 1);
             mbar_init(smem_u32(&bar_free_all[s]), NP);
         }
@@ -517,7 +518,8 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     }
                     if (prof) pc0 += clock64() - tw;
                     const uint32_t fb = smem_u32(&bar_full[st.idx]);
-                    mbar_arrive_expect_tx(fb, Cfg::STAGE);   // A bytes by TMA + the generated half by st.async
+                    // A bytes by TMA + the rows of the generated half that other pairs' CTAs send here
+                    mbar_arrive_expect_tx(fb, Cfg::A_PART + (NP - 1) * Cfg::GEN_ROWS * BK * 2);
 #pragma unroll
                     for (int s = 0; s < MT; ++s)
                         tma_load_2d(smem_base + st.idx * Cfg::STAGE + s * SUB_BYTES, &tmap_a, fb, kb * BK,
@@ -700,15 +702,19 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         __nv_bfloat162 h2 = __floats2bfloat162_rn(f0, f1);
                         p[j] = *reinterpret_cast<uint32_t *>(&h2);
                     }
-                    // asynchronous 16-byte stores to every CTA of the cluster that holds this half (this CTA included);
-                    // each completes its bytes on the receiver's `full` barrier -- no fence, no separate arrive
+                    // own copy: plain store; the other CTAs that hold this half get asynchronous 16-byte stores that
+                    // complete their bytes on the receiver's `full` barrier
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + soff[c]), "r"(p[0]), "r"(p[1]), "r"(p[2]),
+                                 "r"(p[3]) : "memory");
 #pragma unroll
                     for (int qd = 0; qd < NP; ++qd) {
                         const uint32_t dst = 2u * qd + half;
-                        st_async_v4(mapa(stage + soff[c], dst), p[0], p[1], p[2], p[3], mapa(fb, dst));
+                        if (dst != rank) st_async_v4(mapa(stage + soff[c], dst), p[0], p[1], p[2], p[3], mapa(fb, dst));
                     }
                     bstart[c] += kb_step;
                 }
+                fence_proxy_async_smem();
+                mbar_arrive(fb);
                 if (prof) { pc0 += tc - tw; pc1 += clock64() - tc; }
                 st.advance<D>();
             }
