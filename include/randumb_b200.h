@@ -218,10 +218,13 @@ int rdb_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, 
  * Reference 1-D-coefficient form (every existing randumb model):
  *   out[n] = sum_m S[sq(n), m] * coef[m],  sq(n) = (n % Q)*stride_Q + (n / Q)*stride_P,  float32 [P,Q].
  * Stands in for rten::materialize_fwd (src/rten_cpp/RandumbTensor.py:235-290, 371-381) and
- * rten_cpp::materialize_fwd (csrc/cuda/rten.cu:74-152); the fused random bias is not included.
+ * rten_cpp::materialize_fwd (csrc/cuda/rten.cu:74-152).
+ * scale_bias: null, or a device pointer to one float; when given, the fused random bias of the reference
+ * (RAND_BIAS branch, src/rten_cpp/RandumbTensor.py:283-286) is added:
+ *   out[n] += scale_bias[0] * noise1d(sq(n))     (the 1-D hash of the same index, no prime multiply).
  */
 int rdb_materialize_fwd(float *out, const float *coef, int64_t M, int64_t P, int64_t Q, int64_t stride_P,
-                        int64_t stride_Q, uint32_t seed, void *stream);
+                        int64_t stride_Q, const float *scale_bias, uint32_t seed, void *stream);
 
 /*
  * dcoef[m] = sum_n S[n,m] * dout[n] over the flattened contiguous dout (float32), deterministic
@@ -231,6 +234,28 @@ int rdb_materialize_fwd(float *out, const float *coef, int64_t M, int64_t P, int
 size_t rdb_materialize_bwd_workspace_bytes(int64_t Nel, int64_t M);
 int rdb_materialize_bwd(float *dcoef, const float *dout, float *workspace, int64_t Nel, int64_t M,
                         uint32_t seed, void *stream);
+
+/*
+ * Gradient of the random-bias scale: dbias[0] = sum_n dout[n] * noise1d(n) over the flattened contiguous
+ * dout (float32), deterministic reduction order.  Stands in for rten::scale_bias_bwd
+ * (src/rten_cpp/RandumbTensor.py:400-420).  workspace: rdb_scale_bias_bwd_workspace_bytes(Nel) bytes.
+ */
+size_t rdb_scale_bias_bwd_workspace_bytes(int64_t Nel);
+int rdb_scale_bias_bwd(float *dbias, const float *dout, float *workspace, int64_t Nel, uint32_t seed,
+                       void *stream);
+
+/*
+ * Rows of a virtual (vocab, rowsize) embedding matrix in the 1-D-coefficient form:
+ *   out[i, j] = sum_m S[idx[i]*rowsize + j, m] * coef[m]     out float32 [n_idx, rowsize], row pitch ld_out
+ *   dcoef[m]  = sum_{i,j} S[idx[i]*rowsize + j, m] * dout[i, j]   (dout contiguous; repeated indices add)
+ * idx: n_idx int64 row numbers on the device.  Stand in for rten::embed_fwd / rten::embed_bwd
+ * (src/rten_cpp/RandumbTensor.py:999-1056, 1060-1107, 1121-1134).  The backward pass is deterministic;
+ * workspace: rdb_materialize_bwd_workspace_bytes(n_idx*rowsize, M) bytes.
+ */
+int rdb_embed_fwd(float *out, const int64_t *idx, const float *coef, int64_t n_idx, int64_t rowsize, int64_t M,
+                  int64_t ld_out, uint32_t seed, void *stream);
+int rdb_embed_bwd(float *dcoef, const float *dout, const int64_t *idx, float *workspace, int64_t n_idx,
+                  int64_t rowsize, int64_t M, uint32_t seed, void *stream);
 
 #ifdef __cplusplus
 }

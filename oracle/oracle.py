@@ -87,14 +87,24 @@ def noise_bf16(rows: int, cols: int, seed: int, row0: int = 0, col0: int = 0) ->
 # ----------------------------------------------------------------------------------------------
 # 1-D coefficient form of the reference (materialise forward / backward)
 # ----------------------------------------------------------------------------------------------
-def materialize_fwd(coef: np.ndarray, P: int, Q: int, stride_P: int, stride_Q: int, seed: int) -> np.ndarray:
-    """out[n] = sum_m S[sq(n), m] * coef[m];  sq(n) = (n % Q)*stride_Q + (n // Q)*stride_P."""
+def _rows_dot(rows: np.ndarray, coef: np.ndarray, seed: int) -> np.ndarray:
+    """sum_m S[rows[n], m] * coef[m] for a vector of noise row numbers (float64 accumulation)."""
+    with np.errstate(over="ignore"):
+        pos = (PRIME * (rows & 0xFFFFFFFF).astype(np.uint32))[:, None] + np.arange(coef.size, dtype=np.uint32)[None, :]
+    S = bits_to_f32(_mix(pos, seed)).astype(np.float64)
+    return S @ coef.astype(np.float64)
+
+
+def materialize_fwd(coef: np.ndarray, P: int, Q: int, stride_P: int, stride_Q: int, seed: int,
+                    scale_bias: float | None = None) -> np.ndarray:
+    """out[n] = sum_m S[sq(n), m] * coef[m] (+ scale_bias * noise1d(sq(n)));  sq(n) = (n % Q)*stride_Q + (n // Q)*stride_P.
+    Reference: src/rten_cpp/RandumbTensor.py:235-290 (bias branch :283-286)."""
     n = np.arange(P * Q, dtype=np.int64)
     sq = (n % Q) * stride_Q + (n // Q) * stride_P
-    with np.errstate(over="ignore"):
-        pos = (PRIME * (sq & 0xFFFFFFFF).astype(np.uint32))[:, None] + np.arange(coef.size, dtype=np.uint32)[None, :]
-    S = bits_to_f32(_mix(pos, seed)).astype(np.float64)
-    return (S @ coef.astype(np.float64)).reshape(P, Q)
+    out = _rows_dot(sq, coef, seed)
+    if scale_bias is not None:
+        out = out + float(scale_bias) * bits_to_f32(_mix((sq & 0xFFFFFFFF).astype(np.uint32), seed)).astype(np.float64)
+    return out.reshape(P, Q)
 
 
 def materialize_bwd(dout: np.ndarray, M: int, seed: int) -> np.ndarray:
@@ -102,6 +112,31 @@ def materialize_bwd(dout: np.ndarray, M: int, seed: int) -> np.ndarray:
     d = dout.reshape(-1).astype(np.float64)
     S = noise_f32(d.size, M, seed).astype(np.float64)
     return S.T @ d
+
+
+def scale_bias_bwd(dout: np.ndarray, seed: int) -> float:
+    """sum_n dout_flat[n] * noise1d(n).  Reference: src/rten_cpp/RandumbTensor.py:400-407."""
+    d = dout.reshape(-1).astype(np.float64)
+    return float(bits_to_f32(noise_bits_1d(d.size, seed)).astype(np.float64) @ d)
+
+
+def _embed_rows(idx: np.ndarray, rowsize: int) -> np.ndarray:
+    i = idx.reshape(-1).astype(np.int64)
+    return (i[:, None] * rowsize + np.arange(rowsize, dtype=np.int64)[None, :]).reshape(-1)
+
+
+def embed_fwd(idx: np.ndarray, coef: np.ndarray, rowsize: int, seed: int) -> np.ndarray:
+    """out[i, j] = sum_m S[idx[i]*rowsize + j, m] * coef[m].  Reference: src/rten_cpp/RandumbTensor.py:999-1056."""
+    return _rows_dot(_embed_rows(idx, rowsize), coef, seed).reshape(idx.size, rowsize)
+
+
+def embed_bwd(idx: np.ndarray, dout: np.ndarray, M: int, rowsize: int, seed: int) -> np.ndarray:
+    """dcoef[m] = sum_{i,j} S[idx[i]*rowsize + j, m] * dout[i, j].  Reference: src/rten_cpp/RandumbTensor.py:1060-1107."""
+    rows = _embed_rows(idx, rowsize)
+    with np.errstate(over="ignore"):
+        pos = (PRIME * (rows & 0xFFFFFFFF).astype(np.uint32))[:, None] + np.arange(M, dtype=np.uint32)[None, :]
+    S = bits_to_f32(_mix(pos, seed)).astype(np.float64)
+    return S.T @ dout.reshape(-1).astype(np.float64)
 
 
 # ----------------------------------------------------------------------------------------------

@@ -42,9 +42,13 @@ PROTOTYPES = {
     "rdb_gemm_noise": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i64, _i64, _u32, _i32, _vp, _vp]),
     "rdb_gemm_dense": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp,
                               _vp]),
-    "rdb_materialize_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _u32, _vp]),
+    "rdb_materialize_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _u32, _vp]),
     "rdb_materialize_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "rdb_materialize_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _u32, _vp]),
+    "rdb_scale_bias_bwd_workspace_bytes": (_sz, [_i64]),
+    "rdb_scale_bias_bwd": (_i32, [_vp, _vp, _vp, _i64, _u32, _vp]),
+    "rdb_embed_fwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
+    "rdb_embed_bwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _u32, _vp]),
 }
 
 _lib = None

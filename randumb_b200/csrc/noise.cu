@@ -83,17 +83,34 @@ static int launch_noise(void *out, int64_t rows, int64_t cols, int64_t ld, int64
 }
 
 // ---- materialise forward (1-D coefficient vector) ---------------------------------------------
+// Element n of the output is a dot product of noise row rowsel(n) with the coefficient vector.  Two row
+// selections share the kernels: a strided view of a virtual tensor (sq(n), the reference's Form R) and rows of
+// a virtual (vocab, rowsize) embedding matrix picked by an index vector.
 constexpr int MAT_CHUNK = 1024;
 
+struct RowSel {
+    const int64_t *idx;   // null: strided view; else embedding rows
+    int64_t Q, stride_P, stride_Q;   // strided view
+    int64_t rowsize, n_idx;          // embedding
+};
+
+__device__ __forceinline__ uint32_t noise_row_of(const RowSel &rs, int64_t n) {
+    if (rs.idx) {
+        const int64_t i = n / rs.rowsize;
+        return (uint32_t)(rs.idx[i] * rs.rowsize + (n - i * rs.rowsize));
+    }
+    return (uint32_t)((n % rs.Q) * rs.stride_Q + (n / rs.Q) * rs.stride_P);
+}
+
 __global__ void materialize_fwd_kernel(float *__restrict__ out, const float *__restrict__ coef, int64_t M, int64_t Nel,
-                                       int64_t Q, int64_t stride_P, int64_t stride_Q, uint32_t seed) {
+                                       RowSel rs, int64_t ld_out, const float *__restrict__ scale_bias, uint32_t seed) {
     __shared__ float coef_s[MAT_CHUNK];
     const int64_t n = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     const bool live = n < Nel;
-    uint32_t rowpos = 0;
+    uint32_t row = 0, rowpos = 0;
     if (live) {
-        const int64_t sq = (n % Q) * stride_Q + (n / Q) * stride_P;
-        rowpos = ((uint32_t)sq * SQ5_PRIME) * SQ5_N1 + seed;
+        row = noise_row_of(rs, n);
+        rowpos = (row * SQ5_PRIME) * SQ5_N1 + seed;
     }
     float acc = 0.0f;
     for (int64_t m0 = 0; m0 < M; m0 += MAT_CHUNK) {
@@ -109,7 +126,15 @@ __global__ void materialize_fwd_kernel(float *__restrict__ out, const float *__r
             }
         }
     }
-    if (live) out[n] = acc;
+    if (!live) return;
+    // fused random bias: scale * 1-D noise of the same row index (no prime multiply)
+    if (scale_bias) acc = fmaf(scale_bias[0], sq5_to_float(sq5_tail(row * SQ5_N1 + seed)), acc);
+    if (rs.idx) {
+        const int64_t i = n / rs.rowsize;
+        out[i * ld_out + (n - i * rs.rowsize)] = acc;
+    } else {
+        out[n] = acc;
+    }
 }
 
 // ---- materialise backward: partial[split][m] then ordered sum over splits ----------------------
@@ -118,7 +143,7 @@ constexpr int BWD_THREADS = 256;
 constexpr int64_t BWD_SPAN = 8192;  // dout elements per split
 
 __global__ void materialize_bwd_partial_kernel(float *__restrict__ partial, const float *__restrict__ dout, int64_t Nel,
-                                               int64_t M, uint32_t seed) {
+                                               int64_t M, RowSel rs, uint32_t seed) {
     __shared__ float red[BWD_MB][BWD_THREADS];
     const int64_t m0 = (int64_t)blockIdx.x * BWD_MB;
     const int64_t split = blockIdx.y;
@@ -129,7 +154,8 @@ __global__ void materialize_bwd_partial_kernel(float *__restrict__ partial, cons
     for (int j = 0; j < BWD_MB; ++j) acc[j] = 0.0f;
     for (int64_t n = n_lo + threadIdx.x; n < n_hi; n += BWD_THREADS) {
         const float d = dout[n];
-        const uint32_t b0 = ((uint32_t)n * SQ5_PRIME + (uint32_t)m0) * SQ5_N1 + seed;
+        const uint32_t row = rs.idx ? noise_row_of(rs, n) : (uint32_t)n;   // the gradient arrives contiguous
+        const uint32_t b0 = (row * SQ5_PRIME + (uint32_t)m0) * SQ5_N1 + seed;
 #pragma unroll
         for (int j = 0; j < BWD_MB; ++j) acc[j] = fmaf(sq5_to_float(sq5_tail(b0 + (uint32_t)j * SQ5_N1)), d, acc[j]);
     }
@@ -153,6 +179,54 @@ __global__ void materialize_bwd_final_kernel(float *__restrict__ dcoef, const fl
     float acc = 0.0f;
     for (int64_t s = 0; s < nsplit; ++s) acc += partial[s * M + m];
     dcoef[m] = acc;
+}
+
+// ---- gradient of the random-bias scale: sum_n dout[n] * noise1d(n) -----------------------------
+__global__ void scale_bias_bwd_partial_kernel(float *__restrict__ partial, const float *__restrict__ dout, int64_t Nel,
+                                              uint32_t seed) {
+    __shared__ float red[BWD_THREADS];
+    const int64_t n_lo = (int64_t)blockIdx.x * BWD_SPAN;
+    const int64_t n_hi = (n_lo + BWD_SPAN) < Nel ? (n_lo + BWD_SPAN) : Nel;
+    float acc = 0.0f;
+    for (int64_t n = n_lo + threadIdx.x; n < n_hi; n += BWD_THREADS)
+        acc = fmaf(sq5_to_float(sq5_tail((uint32_t)n * SQ5_N1 + seed)), dout[n], acc);
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = BWD_THREADS / 2; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) partial[blockIdx.x] = red[0];
+}
+
+__global__ void scale_bias_bwd_final_kernel(float *__restrict__ dbias, const float *__restrict__ partial, int64_t nsplit) {
+    __shared__ float red[BWD_THREADS];
+    float acc = 0.0f;
+    for (int64_t s = threadIdx.x; s < nsplit; s += BWD_THREADS) acc += partial[s];
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = BWD_THREADS / 2; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) dbias[0] = red[0];
+}
+
+static int launch_materialize_bwd(float *dcoef, const float *dout, float *workspace, int64_t Nel, int64_t M,
+                                  const RowSel &rs, uint32_t seed, cudaStream_t st) {
+    if (Nel == 0) {
+        cudaError_t e = cudaMemsetAsync(dcoef, 0, (size_t)M * sizeof(float), st);
+        return e == cudaSuccess ? RDB_OK : (int)e;
+    }
+    if (!dout || !workspace) return RDB_ERR_NULL;
+    const int64_t nsplit = cdiv64(Nel, BWD_SPAN);
+    if (nsplit > 65535) return RDB_ERR_TOO_LARGE;
+    dim3 grid((unsigned)cdiv64(M, BWD_MB), (unsigned)nsplit);
+    materialize_bwd_partial_kernel<<<grid, BWD_THREADS, 0, st>>>(workspace, dout, Nel, M, rs, seed);
+    int rc = launch_status();
+    if (rc) return rc;
+    materialize_bwd_final_kernel<<<(unsigned)cdiv64(M, 128), 128, 0, st>>>(dcoef, workspace, M, nsplit);
+    return launch_status();
 }
 
 }  // namespace rdb
@@ -184,14 +258,15 @@ extern "C" int rdb_noise_1d(float *out, int64_t n, int64_t idx0, uint32_t seed, 
 }
 
 extern "C" int rdb_materialize_fwd(float *out, const float *coef, int64_t M, int64_t P, int64_t Q, int64_t stride_P,
-                                   int64_t stride_Q, uint32_t seed, void *stream) {
+                                   int64_t stride_Q, const float *scale_bias, uint32_t seed, void *stream) {
     if (M < 0 || P < 0 || Q < 0) return RDB_ERR_SHAPE;
     const int64_t Nel = P * Q;
     if (Nel == 0) return RDB_OK;
     if (!out || (M > 0 && !coef)) return RDB_ERR_NULL;
     if (cdiv64(Nel, 128) > 0x7fffffffLL) return RDB_ERR_TOO_LARGE;
-    materialize_fwd_kernel<<<(unsigned)cdiv64(Nel, 128), 128, 0, (cudaStream_t)stream>>>(out, coef, M, Nel, Q, stride_P,
-                                                                                       stride_Q, seed);
+    RowSel rs{nullptr, Q, stride_P, stride_Q, 0, 0};
+    materialize_fwd_kernel<<<(unsigned)cdiv64(Nel, 128), 128, 0, (cudaStream_t)stream>>>(out, coef, M, Nel, rs, 0,
+                                                                                       scale_bias, seed);
     return launch_status();
 }
 
@@ -205,18 +280,54 @@ extern "C" int rdb_materialize_bwd(float *dcoef, const float *dout, float *works
     if (Nel < 0 || M < 0) return RDB_ERR_SHAPE;
     if (M == 0) return RDB_OK;
     if (!dcoef) return RDB_ERR_NULL;
+    RowSel rs{nullptr, 1, 1, 1, 0, 0};
+    return launch_materialize_bwd(dcoef, dout, workspace, Nel, M, rs, seed, (cudaStream_t)stream);
+}
+
+extern "C" size_t rdb_scale_bias_bwd_workspace_bytes(int64_t Nel) {
+    if (Nel <= 0) return 0;
+    return (size_t)cdiv64(Nel, BWD_SPAN) * sizeof(float);
+}
+
+extern "C" int rdb_scale_bias_bwd(float *dbias, const float *dout, float *workspace, int64_t Nel, uint32_t seed,
+                                  void *stream) {
+    if (Nel < 0) return RDB_ERR_SHAPE;
+    if (!dbias) return RDB_ERR_NULL;
     cudaStream_t st = (cudaStream_t)stream;
     if (Nel == 0) {
-        cudaError_t e = cudaMemsetAsync(dcoef, 0, (size_t)M * sizeof(float), st);
+        cudaError_t e = cudaMemsetAsync(dbias, 0, sizeof(float), st);
         return e == cudaSuccess ? RDB_OK : (int)e;
     }
     if (!dout || !workspace) return RDB_ERR_NULL;
     const int64_t nsplit = cdiv64(Nel, BWD_SPAN);
-    if (nsplit > 65535) return RDB_ERR_TOO_LARGE;
-    dim3 grid((unsigned)cdiv64(M, BWD_MB), (unsigned)nsplit);
-    materialize_bwd_partial_kernel<<<grid, BWD_THREADS, 0, st>>>(workspace, dout, Nel, M, seed);
+    if (nsplit > 0x7fffffffLL) return RDB_ERR_TOO_LARGE;
+    scale_bias_bwd_partial_kernel<<<(unsigned)nsplit, BWD_THREADS, 0, st>>>(workspace, dout, Nel, seed);
     int rc = launch_status();
     if (rc) return rc;
-    materialize_bwd_final_kernel<<<(unsigned)cdiv64(M, 128), 128, 0, st>>>(dcoef, workspace, M, nsplit);
+    scale_bias_bwd_final_kernel<<<1, BWD_THREADS, 0, st>>>(dbias, workspace, nsplit);
     return launch_status();
+}
+
+extern "C" int rdb_embed_fwd(float *out, const int64_t *idx, const float *coef, int64_t n_idx, int64_t rowsize, int64_t M,
+                             int64_t ld_out, uint32_t seed, void *stream) {
+    if (n_idx < 0 || rowsize < 0 || M < 0 || ld_out < rowsize) return RDB_ERR_SHAPE;
+    const int64_t Nel = n_idx * rowsize;
+    if (Nel == 0) return RDB_OK;
+    if (!out || !idx || (M > 0 && !coef)) return RDB_ERR_NULL;
+    if (cdiv64(Nel, 128) > 0x7fffffffLL) return RDB_ERR_TOO_LARGE;
+    RowSel rs{idx, 1, 1, 1, rowsize, n_idx};
+    materialize_fwd_kernel<<<(unsigned)cdiv64(Nel, 128), 128, 0, (cudaStream_t)stream>>>(out, coef, M, Nel, rs, ld_out,
+                                                                                       nullptr, seed);
+    return launch_status();
+}
+
+extern "C" int rdb_embed_bwd(float *dcoef, const float *dout, const int64_t *idx, float *workspace, int64_t n_idx,
+                             int64_t rowsize, int64_t M, uint32_t seed, void *stream) {
+    if (n_idx < 0 || rowsize < 0 || M < 0) return RDB_ERR_SHAPE;
+    if (M == 0) return RDB_OK;
+    if (!dcoef) return RDB_ERR_NULL;
+    const int64_t Nel = n_idx * rowsize;
+    if (Nel > 0 && !idx) return RDB_ERR_NULL;
+    RowSel rs{idx, 1, 1, 1, rowsize, n_idx};
+    return launch_materialize_bwd(dcoef, dout, workspace, Nel, M, rs, seed, (cudaStream_t)stream);
 }

@@ -242,8 +242,11 @@ def gemm_dense(a: torch.Tensor, b: torch.Tensor, a_kmajor: bool = True, b_kmajor
 
 
 # ------------------------------------------------------------------------------------------ 1-D coefficient form
-def materialize_fwd(coef: torch.Tensor, size, strides, seed: int) -> torch.Tensor:
+def materialize_fwd(coef: torch.Tensor, size, strides, seed: int, scale_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``scale_bias``: None, or a one-element float32 device tensor; adds ``scale_bias * noise1d(sq(n))``."""
     dev = _need_cuda(coef)
+    if scale_bias is not None:
+        assert scale_bias.numel() == 1 and scale_bias.dtype == torch.float32 and scale_bias.device == dev
     assert coef.dim() == 1 and coef.dtype == torch.float32 and coef.is_contiguous()
     size = list(size)
     strides = list(strides)
@@ -255,7 +258,8 @@ def materialize_fwd(coef: torch.Tensor, size, strides, seed: int) -> torch.Tenso
         raise RuntimeError("materialize_fwd handles 1-D and 2-D outputs")
     out = torch.empty(size, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        rc = _lib.lib().rdb_materialize_fwd(_ptr(out), _ptr(coef), coef.numel(), P, Q, sP, sQ, _seed(seed), _stream(dev))
+        rc = _lib.lib().rdb_materialize_fwd(_ptr(out), _ptr(coef), coef.numel(), P, Q, sP, sQ,
+                                            _ptr(scale_bias) if scale_bias is not None else None, _seed(seed), _stream(dev))
     _lib.check(rc, "rdb_materialize_fwd")
     return out
 
@@ -272,4 +276,50 @@ def materialize_bwd(dout: torch.Tensor, dcoefs_size: int, seed: int) -> torch.Te
         rc = L.rdb_materialize_bwd(_ptr(dcoef), _ptr(dout), _ptr(ws), dout.numel(), int(dcoefs_size), _seed(seed),
                                    _stream(dev))
     _lib.check(rc, "rdb_materialize_bwd")
+    return dcoef
+
+
+def scale_bias_bwd(dout: torch.Tensor, seed: int) -> torch.Tensor:
+    """``sum_n dout[n] * noise1d(n)`` over the flattened contiguous gradient; one-element float32 tensor."""
+    dev = _need_cuda(dout)
+    assert dout.is_contiguous(), "dout is not contiguous, backwards pass might give incorrect results."
+    dout = dout.reshape(-1).to(torch.float32)
+    L = _lib.lib()
+    dbias = torch.empty((1,), dtype=torch.float32, device=dev)
+    ws = torch.empty((max(L.rdb_scale_bias_bwd_workspace_bytes(dout.numel()) // 4, 1),), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = L.rdb_scale_bias_bwd(_ptr(dbias), _ptr(dout), _ptr(ws), dout.numel(), _seed(seed), _stream(dev))
+    _lib.check(rc, "rdb_scale_bias_bwd")
+    return dbias
+
+
+# ------------------------------------------------------------------------------------------ embedding rows
+def embed_fwd(idx: torch.Tensor, coef: torch.Tensor, rowsize: int, seed: int) -> torch.Tensor:
+    """Rows ``idx`` of the virtual (vocab, rowsize) matrix: float32 ``[*idx.shape, rowsize]``."""
+    dev = _need_cuda(coef)
+    assert coef.dim() == 1 and coef.dtype == torch.float32 and coef.is_contiguous()
+    assert idx.device == dev and not idx.is_floating_point(), "idx must be an integer tensor on the device of coef"
+    flat = idx.reshape(-1).to(torch.int64).contiguous()
+    out = torch.empty((flat.numel(), int(rowsize)), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_embed_fwd(_ptr(out), _ptr(flat), _ptr(coef), flat.numel(), int(rowsize), coef.numel(),
+                                      int(rowsize), _seed(seed), _stream(dev))
+    _lib.check(rc, "rdb_embed_fwd")
+    return out.reshape(*idx.shape, int(rowsize))
+
+
+def embed_bwd(idx: torch.Tensor, dout: torch.Tensor, dcoefs_size: int, rowsize: int, seed: int) -> torch.Tensor:
+    dev = _need_cuda(dout)
+    assert idx.device == dev and not idx.is_floating_point()
+    flat = idx.reshape(-1).to(torch.int64).contiguous()
+    dout = dout.reshape(-1).to(torch.float32).contiguous()
+    assert dout.numel() == flat.numel() * int(rowsize), "dout must hold one row of rowsize values per index"
+    L = _lib.lib()
+    dcoef = torch.empty((int(dcoefs_size),), dtype=torch.float32, device=dev)
+    nbytes = L.rdb_materialize_bwd_workspace_bytes(dout.numel(), int(dcoefs_size))
+    ws = torch.empty((max(nbytes // 4, 1),), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = L.rdb_embed_bwd(_ptr(dcoef), _ptr(dout), _ptr(flat), _ptr(ws), flat.numel(), int(rowsize), int(dcoefs_size),
+                             _seed(seed), _stream(dev))
+    _lib.check(rc, "rdb_embed_bwd")
     return dcoef

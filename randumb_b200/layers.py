@@ -58,7 +58,18 @@ class RandumbModuleMixin(nn.Module):
         for name, buf in list(self._buffers.items()):
             if isinstance(buf, RandumbTensor):
                 coef = getattr(self, f"{name}_coef")
-                self._buffers[name] = CreateRandumbTensor(coef, buf.seed, buf.shape, buf.scale_bias, buf.fused_bias, buf.row0)
+                scale_bias = getattr(self, f"{name}_scale_bias", buf.scale_bias)
+                self._buffers[name] = CreateRandumbTensor(coef, buf.seed, buf.shape, scale_bias, buf.fused_bias, buf.row0)
+
+    def init_rt_scale_bias(self, val: float = 0.0) -> None:
+        """One trainable scale per virtual buffer for the fused random bias, registered as
+        ``<buffer>_scale_bias`` (reference: SillyLayers.py:116-120)."""
+        for name, buf in list(self._buffers.items()):
+            if isinstance(buf, RandumbTensor) and not buf.is_matrix_form:
+                coef = getattr(self, f"{name}_coef")
+                p = nn.Parameter(torch.tensor([val], dtype=coef.dtype, device=coef.device))
+                self.register_parameter(f"{name}_scale_bias", p)
+                self._buffers[name] = CreateRandumbTensor(coef, buf.seed, buf.shape, p, buf.fused_bias, buf.row0)
 
 
 class RandumbLinear(RandumbModuleMixin, nn.Module):
@@ -122,46 +133,95 @@ class SillyLinear(RandumbModuleMixin, nn.Module):
     """Reference-convention linear layer: weight and bias are both RandumbTensors.
 
     ``int_dim`` / ``seed``: list of two values or a generator (first for the weight, second for the
-    bias).  The weight uses the matrix-coefficient form (``weight_coef`` is ``[int_dim[0], in_features]``);
-    the bias keeps the reference's 1-D coefficient form (``bias_coef`` is ``[int_dim[1]]``) and is
-    materialised by ``rten::materialize_fwd``.  The reference's fused random bias (``rt_bias``) is not
-    part of this build.
+    bias).  ``coef_form="matrix"`` (default) gives the weight the matrix-coefficient form (``weight_coef`` is
+    ``[int_dim[0], in_features]``, fused tensor-core operator); ``coef_form="vector"`` is the reference's own
+    layer: ``weight_coef`` is ``[int_dim[0]]`` and the weight is materialised by ``rten::materialize_fwd``
+    before a dense product.  The bias always has the 1-D coefficient form (``bias_coef`` is ``[int_dim[1]]``).
+
+    ``rt_bias`` adds the reference's fused random bias ``scale_bias * noise1d`` to every 1-D-form tensor of the
+    layer, with one trainable ``<name>_scale_bias`` each; the layer then starts from zero coefficients and a
+    uniform random weight of nn.Linear's default bound (reference ``init_zero_coef_uniform_bias``:
+    SillyLayers.py:122-133).
     """
     num_seeds = 2
 
     def __init__(self, in_features: int, out_features: int, int_dim: Union[list, Generator], seed: Union[list, Generator],
-                 bias: bool = True, rt_bias: bool = False, device=None, dtype=None) -> None:
+                 bias: bool = True, rt_bias: bool = False, device=None, dtype=None, coef_form: str = "matrix") -> None:
         super().__init__()
-        if rt_bias:
-            raise NotImplementedError("rt_bias (fused random bias) is not part of this build")
-        self.in_features, self.out_features, self.rt_bias = in_features, out_features, rt_bias
+        if coef_form not in ("matrix", "vector"):
+            raise ValueError(f"coef_form must be 'matrix' or 'vector', got {coef_form!r}")
+        self.in_features, self.out_features, self.rt_bias, self.coef_form = in_features, out_features, rt_bias, coef_form
         self.int_dim = [next(int_dim) for _ in range(self.num_seeds)] if isinstance(int_dim, GeneratorType) else list(int_dim)
         self.seed = [next(seed) for _ in range(self.num_seeds)] if isinstance(seed, GeneratorType) else list(seed)
-        self.weight_coef = nn.Parameter(torch.empty((self.int_dim[0], in_features), dtype=dtype, device=device))
-        self.register_buffer("weight", CreateRandumbTensor(self.weight_coef, self.seed[0], (out_features, in_features)),
-                             persistent=False)
+        vector = coef_form == "vector"
+        wshape = (self.int_dim[0],) if vector else (self.int_dim[0], in_features)
+        self.weight_coef = nn.Parameter(torch.empty(wshape, dtype=dtype, device=device))
+        self.register_buffer("weight", CreateRandumbTensor(self.weight_coef, self.seed[0], (out_features, in_features),
+                                                           fused_bias=rt_bias and vector), persistent=False)
         if bias:
             self.bias_coef = nn.Parameter(torch.empty(self.int_dim[1], dtype=dtype, device=device))
-            self.register_buffer("bias", CreateRandumbTensor(self.bias_coef, self.seed[1], (out_features,)), persistent=False)
+            self.register_buffer("bias", CreateRandumbTensor(self.bias_coef, self.seed[1], (out_features,), fused_bias=rt_bias),
+                                 persistent=False)
         else:
             self.bias = None
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
         """Uniform coefficients with the variance that gives the virtual weight nn.Linear's default std
-        (reference ``init_kaiming_uniform``: SillyLayers.py:37-79)."""
+        (reference ``init_kaiming_uniform``: SillyLayers.py:37-79); with ``rt_bias`` the 1-D-form tensors start
+        from zero coefficients and a random-bias scale equal to nn.Linear's uniform bound instead."""
         out_std = kaiming_out_std(self.in_features)
         gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed[0] & 0x7FFFFFFFFFFFFFFF)
         with torch.no_grad():
-            bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[0])
-            self.weight_coef.uniform_(-bound, bound, generator=gen)
+            if self.rt_bias and self.coef_form == "vector":
+                self.weight_coef.zero_()
+            else:
+                bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[0])
+                self.weight_coef.uniform_(-bound, bound, generator=gen)
             if self.bias is not None:
-                bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[1])
-                self.bias_coef.uniform_(-bound, bound, generator=gen)
+                if self.rt_bias:
+                    self.bias_coef.zero_()
+                else:
+                    bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[1])
+                    self.bias_coef.uniform_(-bound, bound, generator=gen)
+        if self.rt_bias:
+            self.init_rt_scale_bias(math.sqrt(3.0) * out_std)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
         return F.linear(input, self.weight, self.bias)
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, int_dim={self.int_dim}, "
-                f"seeds={self.seed}, bias={self.bias is not None}")
+                f"seeds={self.seed}, bias={self.bias is not None}, coef_form={self.coef_form}, rt_bias={self.rt_bias}")
+
+
+class SillyEmbedding(RandumbModuleMixin, nn.Module):
+    """Embedding table that is a RandumbTensor in the 1-D coefficient form (reference:
+    SillyLayers.py:301-366): ``forward(idx)`` regenerates only the looked-up rows, ``rten::embed_fwd``.
+    ``padding_idx`` is not supported, as in the reference."""
+    num_seeds = 1
+
+    def __init__(self, num_embeddings: int, embedding_dim: int, int_dim: Union[list, Generator], seed: Union[list, Generator],
+                 padding_idx: Optional[int] = None, _freeze: bool = False, device="cuda", dtype=None) -> None:
+        super().__init__()
+        assert padding_idx is None, "padding_idx not supported"
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        self.int_dim = [next(int_dim) for _ in range(self.num_seeds)] if isinstance(int_dim, GeneratorType) else list(int_dim)
+        self.seed = [next(seed) for _ in range(self.num_seeds)] if isinstance(seed, GeneratorType) else list(seed)
+        self.weight_coef = nn.Parameter(torch.empty(self.int_dim[0], dtype=dtype, device=device), requires_grad=not _freeze)
+        self.register_buffer("weight", CreateRandumbTensor(self.weight_coef, self.seed[0], (num_embeddings, embedding_dim)),
+                             persistent=False)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        out_std = kaiming_out_std(self.embedding_dim)
+        gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed[0] & 0x7FFFFFFFFFFFFFFF)
+        with torch.no_grad():
+            bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[0])
+            self.weight_coef.uniform_(-bound, bound, generator=gen)
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        return ops.embed_fwd(input, self.weight_coef, self.embedding_dim, self.seed[0]).to(self.weight_coef.dtype)
+
+    def extra_repr(self) -> str:
+        return f"{self.num_embeddings}, {self.embedding_dim}, int_dim={self.int_dim}, seeds={self.seed}"

@@ -3,6 +3,8 @@
 Keeps the reference's operator names and schemas so existing call sites bind unchanged:
 
   rten::materialize_fwd / rten::materialize_bwd     src/rten_cpp/RandumbTensor.py:371-390
+  rten::scale_bias_bwd                              src/rten_cpp/RandumbTensor.py:414-420
+  rten::embed_fwd / rten::embed_bwd                 src/rten_cpp/RandumbTensor.py:1121-1134
   rten_cpp::sq5_gen_2d / rten_cpp::materialize_fwd  src/rten_cpp/csrc/rten.cpp:36-39, ops.py:8-13
 
 and adds the operators of the matrix-coefficient layer ``W = S @ C`` that fill the slot the
@@ -115,9 +117,8 @@ def _(rows, cols, seed, row0, dtype, device):
 def materialize_fwd(coefs: torch.Tensor, size: List[int], strides: List[int], seed: int,
                     scale_bias: Optional[torch.Tensor], fused_bias: bool) -> torch.Tensor:
     assert not (fused_bias and scale_bias is None), "scale_bias not initialized but fused_bias is True"
-    if fused_bias:
-        raise NotImplementedError("the fused random bias of materialize_fwd is not part of this build")
-    return K.materialize_fwd(coefs.float().contiguous(), size, strides, seed)
+    sb = scale_bias.detach().reshape(1).float().contiguous() if fused_bias else None
+    return K.materialize_fwd(coefs.float().contiguous(), size, strides, seed, sb)
 
 
 @materialize_fwd.register_fake
@@ -142,19 +143,87 @@ def _(dout, dcoefs_size, seed):
 materialize_bwd.register_kernel("cpu")(_cpu_raises("materialize_bwd"))
 
 
+@custom_op("rten::scale_bias_bwd", mutates_args=(), device_types="cuda")
+def scale_bias_bwd(dout: torch.Tensor, seed: int) -> torch.Tensor:
+    assert dout.is_contiguous(), "dout is not contiguous, backwards pass might give incorrect results."
+    return K.scale_bias_bwd(dout, seed)
+
+
+@scale_bias_bwd.register_fake
+def _(dout, seed):
+    return dout.new_empty((1,), dtype=torch.float32)
+
+
+scale_bias_bwd.register_kernel("cpu")(_cpu_raises("scale_bias_bwd"))
+
+
 def _mat_setup(ctx, inputs, output):
     coefs, size, strides, seed, scale_bias, fused_bias = inputs
     ctx.dcoefs_size = coefs.numel()
     ctx.seed = seed
     ctx.coef_dtype = coefs.dtype
+    ctx.fused_bias = fused_bias
+    ctx.bias_dtype = scale_bias.dtype if scale_bias is not None else None
+    ctx.bias_shape = scale_bias.shape if scale_bias is not None else None
 
 
 def _mat_backward(ctx, grad):
-    dcoefs = materialize_bwd(grad.contiguous(), ctx.dcoefs_size, ctx.seed).to(ctx.coef_dtype)
-    return dcoefs, None, None, None, None, None
+    grad = grad.contiguous()
+    dcoefs = materialize_bwd(grad, ctx.dcoefs_size, ctx.seed).to(ctx.coef_dtype)
+    dscale_bias = None
+    if ctx.fused_bias:
+        dscale_bias = scale_bias_bwd(grad, ctx.seed).to(ctx.bias_dtype).reshape(ctx.bias_shape)
+    return dcoefs, None, None, None, dscale_bias, None
 
 
 materialize_fwd.register_autograd(_mat_backward, setup_context=_mat_setup)
+
+
+# ------------------------------------------------------------------------------------------------
+# embedding rows of a virtual (vocab, rowsize) matrix (reference: RandumbTensor.py:1121-1160)
+# ------------------------------------------------------------------------------------------------
+@custom_op("rten::embed_fwd", mutates_args=(), device_types="cuda")
+def embed_fwd(idx: torch.Tensor, coefs: torch.Tensor, rowsize: int, seed: int) -> torch.Tensor:
+    return K.embed_fwd(idx, coefs.float().contiguous(), rowsize, seed)
+
+
+@embed_fwd.register_fake
+def _(idx, coefs, rowsize, seed):
+    return coefs.new_empty((*idx.shape, rowsize), dtype=torch.float32)
+
+
+embed_fwd.register_kernel("cpu")(_cpu_raises("embed_fwd"))
+
+
+@custom_op("rten::embed_bwd", mutates_args=(), device_types="cuda")
+def embed_bwd(idx: torch.Tensor, dout: torch.Tensor, dcoefs_size: int, rowsize: int, seed: int) -> torch.Tensor:
+    return K.embed_bwd(idx, dout.contiguous(), dcoefs_size, rowsize, seed)
+
+
+@embed_bwd.register_fake
+def _(idx, dout, dcoefs_size, rowsize, seed):
+    return dout.new_empty((dcoefs_size,), dtype=torch.float32)
+
+
+embed_bwd.register_kernel("cpu")(_cpu_raises("embed_bwd"))
+
+
+def _embed_setup(ctx, inputs, output):
+    idx, coefs, rowsize, seed = inputs
+    ctx.save_for_backward(idx)
+    ctx.dcoefs_size = coefs.numel()
+    ctx.rowsize = rowsize
+    ctx.seed = seed
+    ctx.coef_dtype = coefs.dtype
+
+
+def _embed_backward(ctx, grad):
+    (idx,) = ctx.saved_tensors
+    dcoefs = embed_bwd(idx, grad.contiguous(), ctx.dcoefs_size, ctx.rowsize, ctx.seed).to(ctx.coef_dtype)
+    return None, dcoefs, None, None
+
+
+embed_fwd.register_autograd(_embed_backward, setup_context=_embed_setup)
 
 
 # C++-namespace twins of the reference (rten.cpp:36-39); registered from Python onto the same C ABI.

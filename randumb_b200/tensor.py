@@ -217,13 +217,20 @@ class RandumbTensorConstructor(Function):
         ctx.seed = seed
         ctx.row0 = row0
         ctx.dtype = out.dtype
-        ctx.fused_bias = fused_bias
+        assert not (fused_bias and coefs.dim() == 2), "the fused random bias belongs to the 1-D coefficient form"
+        ctx.fused_bias = fused_bias and scale_bias is not None
+        ctx.bias_dtype = scale_bias.dtype if scale_bias is not None else None
+        ctx.bias_shape = scale_bias.shape if scale_bias is not None else None
         return out
 
     @staticmethod
     def backward(ctx, grad):
+        dscale_bias = None
         if len(ctx.coef_shape) == 1:
-            dcoefs = ops.materialize_bwd(grad.flatten().contiguous(), ctx.coef_shape[0], ctx.seed).to(ctx.dtype)
+            grad = grad.flatten().contiguous()
+            dcoefs = ops.materialize_bwd(grad, ctx.coef_shape[0], ctx.seed).to(ctx.dtype)
+            if ctx.fused_bias:
+                dscale_bias = ops.scale_bias_bwd(grad, ctx.seed).to(ctx.bias_dtype).reshape(ctx.bias_shape)
         else:
             R, _ = ctx.coef_shape
             # dC^T[K, R] = dW^T[K, N] @ S[N, R]: contraction over noise rows, dW^T as the streamed operand
@@ -231,7 +238,7 @@ class RandumbTensorConstructor(Function):
             dct = K.gemm_noise(dwt, R, ctx.seed, transposed=True, row0=ctx.row0, impl=K.IMPL_SIMT if dwt.dtype == torch.float32
                                else K.IMPL_AUTO)
             dcoefs = dct.t().contiguous().to(ctx.dtype)
-        return dcoefs, None, None, None, None, None
+        return dcoefs, None, None, dscale_bias, None, None
 
 
 def CreateRandumbTensor(coefs: torch.Tensor, seed: int, shape: Iterable, scale_bias: Optional[torch.Tensor] = None,

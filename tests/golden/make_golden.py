@@ -12,7 +12,8 @@ fixture file is an output of the reference code.
 
 Kernels executed (paths inside the reference project, file ``src/rten_cpp/RandumbTensor.py``):
   squirrel5_kernel_2d :78-99   squirrel5_kernel_1d :108-114   materialize_fwd_kernel :235-290
-  materialize_bwd_kernel :304-359   rt_mm_grouped_kernel :648-746
+  materialize_bwd_kernel :304-359   scale_bias_bwd_kernel :400-407   rt_mm_grouped_kernel :648-746
+  embed_fwd_kernel :998-1056   embed_bwd_kernel :1060-1107
 """
 import importlib.util
 import os
@@ -67,6 +68,40 @@ def ref_mat_fwd(rt, coef, P, Q, sP, sQ, seed):
     return out.numpy().copy()
 
 
+def ref_mat_fwd_bias(rt, coef, P, Q, sP, sQ, seed, scale_bias):
+    """materialise with the fused random bias: + scale_bias * sq5_1d(sq(n), seed)."""
+    out = torch.empty((P, Q), dtype=torch.float32)
+    N = P * Q
+    sb = torch.tensor([scale_bias], dtype=torch.float32)
+    rt.materialize_fwd_kernel[(cdiv(N, 32),)](out, coef, N, coef.numel(), seed, P, Q, sP, sQ, sb, 1,
+                                              BLOCK_SIZE_N=32, BLOCK_SIZE_M=8)
+    return out.numpy().copy()
+
+
+def ref_scale_bias_bwd(rt, dout, seed):
+    dbias = torch.zeros((1,), dtype=torch.float32)
+    rt.scale_bias_bwd_kernel[(cdiv(dout.numel(), 64),)](dbias, dout, dout.numel(), seed, BLOCK_SIZE_N=64)
+    return dbias.numpy().copy()
+
+
+def ref_embed_fwd(rt, idx, coef, rowsize, seed):
+    """Rows ``idx`` of the virtual (vocab, rowsize) embedding matrix."""
+    out = torch.empty((idx.numel(), rowsize), dtype=torch.float32)
+    BI, BR, BM = 16, 32, 8
+    grid = (cdiv(idx.numel(), BI), cdiv(rowsize, BR))
+    rt.embed_fwd_kernel[grid](out, coef, idx, rowsize, coef.numel(), idx.numel(), seed, out.stride(0),
+                              BLOCK_SIZE_ROW=BR, BLOCK_SIZE_M=BM, BLOCK_SIZE_IDX=BI)
+    return out.numpy().copy()
+
+
+def ref_embed_bwd(rt, idx, dout, M, rowsize, seed):
+    dcoef = torch.zeros((M,), dtype=torch.float32)
+    SPLIT, BN, BM = 4, 32, 4
+    rt.embed_bwd_kernel[(cdiv(M, BM), SPLIT)](dcoef, dout, idx, rowsize, M, idx.numel(), seed,
+                                              BLOCK_SIZE_N=BN, BLOCK_SIZE_M=BM, SPLIT_N=SPLIT)
+    return dcoef.numpy().copy()
+
+
 def ref_mat_bwd(rt, dout, M, seed):
     dcoef = torch.zeros((M,), dtype=torch.float32)
     SPLIT, BN, BM = 4, 64, 4
@@ -113,6 +148,20 @@ def main():
     dout = torch.randn(333, generator=g)
     out["matbwd_dout"] = dout.numpy().copy()
     out["matbwd_333_M24_seed1337"] = ref_mat_bwd(rt, dout, 24, 1337)
+
+    # --- fused random bias (1-D hash of the element index) ------------------------------------
+    out["matfwd_18x18_bias0p25_seed1337"] = ref_mat_fwd_bias(rt, coef, 18, 18, 18, 1, 1337, 0.25)
+    out["matfwd_18x10_transposed_bias_m0p5_seed5"] = ref_mat_fwd_bias(rt, coef, 18, 10, 1, 18, 5, -0.5)
+    out["scale_bias_bwd_333_seed1337"] = ref_scale_bias_bwd(rt, dout, 1337)
+
+    # --- embedding rows of a virtual (vocab, rowsize) matrix -----------------------------------
+    idx = torch.randint(0, 50, (13,), generator=g, dtype=torch.int64)
+    idx[3] = idx[7]                      # a repeated token
+    out["embed_idx"] = idx.numpy().copy()
+    out["embed_fwd_13x20_seed77"] = ref_embed_fwd(rt, idx, coef, 20, 77)
+    edout = torch.randn(13, 20, generator=g)
+    out["embed_dout"] = edout.numpy().copy()
+    out["embed_bwd_13x20_M24_seed77"] = ref_embed_bwd(rt, idx, edout, 24, 20, 77)
 
     # --- the reference's fused mat1 @ RT kernel --------------------------------------------
     P, Q, L = 40, 36, 33

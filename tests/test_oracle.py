@@ -76,6 +76,26 @@ def test_materialize_fwd_bwd_match_reference_kernels(golden):
     np.testing.assert_allclose(O.materialize_bwd(golden["matbwd_dout"], 24, 1337), golden["matbwd_333_M24_seed1337"], atol=1e-5)
 
 
+def test_fused_random_bias_matches_reference_kernels(golden):
+    coef = golden["matfwd_coef"]
+    np.testing.assert_allclose(O.materialize_fwd(coef, 18, 18, 18, 1, 1337, 0.25), golden["matfwd_18x18_bias0p25_seed1337"], atol=2e-6)
+    np.testing.assert_allclose(O.materialize_fwd(coef, 18, 10, 1, 18, 5, -0.5), golden["matfwd_18x10_transposed_bias_m0p5_seed5"],
+                               atol=2e-6)
+    # the bias term alone is scale * the reference's 1-D noise
+    diff = golden["matfwd_18x18_bias0p25_seed1337"] - golden["matfwd_18x18_contig_seed1337"]
+    np.testing.assert_allclose(diff.ravel()[:200], 0.25 * golden["noise1d_200_seed1337"], atol=2e-6)
+    np.testing.assert_allclose(O.scale_bias_bwd(golden["matbwd_dout"], 1337), golden["scale_bias_bwd_333_seed1337"][0], atol=1e-5)
+
+
+def test_embedding_rows_match_reference_kernels(golden):
+    idx, coef = golden["embed_idx"], golden["matfwd_coef"]
+    np.testing.assert_allclose(O.embed_fwd(idx, coef, 20, 77), golden["embed_fwd_13x20_seed77"], atol=2e-6)
+    np.testing.assert_allclose(O.embed_bwd(idx, golden["embed_dout"], 24, 20, 77), golden["embed_bwd_13x20_M24_seed77"], atol=1e-5)
+    # a looked-up row is the same row of the materialised (vocab, rowsize) matrix
+    full = O.materialize_fwd(coef, 50, 20, 20, 1, 77)
+    np.testing.assert_allclose(O.embed_fwd(idx, coef, 20, 77), full[idx], atol=1e-12)
+
+
 def test_reference_fused_mm_kernel(golden):
     """mat1 @ RT from the reference's rt_mm_grouped_kernel equals mat1 @ materialize(RT)."""
     W = O.materialize_fwd(golden["matfwd_coef"], 40, 36, 36, 1, 9)
