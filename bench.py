@@ -306,24 +306,41 @@ def run_ours(args, cfg):
 
     # ---- dominant kernel, timed live with CUDA events on the launching stream -------------------
     roofline, peaks = None, measured_peaks()
+    staged = args.workload != "gemv" and K.linear_stages_noise(T, Kin, n_local, R, dt, K.PATH_FACTORED)
     if args.workload != "gemv":
         z = torch.randn(T, R, device=dev).to(dt)
         reps = max(args.steps, 5)
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(2 * reps)]
-        for _ in range(2):
-            K.gemm_noise(z, n_local, seed, False, row0, impl=K.IMPL_UMMA)
-            K.gemm_noise(dy, R, seed, True, row0, impl=K.IMPL_UMMA)
-        torch.cuda.synchronize()
-        for i in range(reps):
-            evs[2 * i][0].record(); K.gemm_noise(z, n_local, seed, False, row0, impl=K.IMPL_UMMA); evs[2 * i][1].record()
-            evs[2 * i + 1][0].record(); K.gemm_noise(dy, R, seed, True, row0, impl=K.IMPL_UMMA); evs[2 * i + 1][1].record()
-        torch.cuda.synchronize()
-        avg_ms = sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+
+        def time_pair(f_y, f_g):
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(2 * reps)]
+            for _ in range(2):
+                f_y(); f_g()
+            torch.cuda.synchronize()
+            for i in range(reps):
+                evs[2 * i][0].record(); f_y(); evs[2 * i][1].record()
+                evs[2 * i + 1][0].record(); f_g(); evs[2 * i + 1][1].record()
+            torch.cuda.synchronize()
+            return sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+
         flops_launch = 2.0 * T * n_local * R
+        fused_ms = time_pair(lambda: K.gemm_noise(z, n_local, seed, False, row0, impl=K.IMPL_UMMA),
+                             lambda: K.gemm_noise(dy, R, seed, True, row0, impl=K.IMPL_UMMA))
+        fused = {"kernel": "noise_pair_kernel (y = z S^T) and noise_gemm_kernel (g = dY S): S regenerated in shared memory per 512-token tile",
+                 "avg_launch_ms": fused_ms, "achieved": flops_launch / (fused_ms * 1e-3) / 1e12}
+        if staged:
+            S = K.noise(n_local, R, seed, row0, 0, dt, dev)
+            avg_ms = time_pair(lambda: K.gemm_dense(z, S), lambda: K.gemm_dense(dy, S, True, False))
+            fill_ms = time_pair(lambda: K.noise(n_local, R, seed, row0, 0, dt, dev), lambda: None) * 2
+            kernel = ("dense_gemm_kernel (y = z S^T and g = dY S, average over both launches) on S hashed once per call into a "
+                      "bf16 scratch by noise_kernel")
+        else:
+            avg_ms, fill_ms, kernel = fused_ms, None, fused["kernel"]
         achieved = flops_launch / (avg_ms * 1e-3) / 1e12
-        roofline = {"bound": "tensor", "kernel": "noise_pair_kernel (y = z S^T) and noise_gemm_kernel (g = dY S), average over both launches", "achieved": achieved,
+        roofline = {"bound": "tensor", "kernel": kernel, "achieved": achieved,
                     "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
-                    "peak_source": f"{peaks['src']} burst bf16", "avg_launch_ms": avg_ms, "traffic": NOISE_GEMM_DRAM_BYTES.get(args.workload)}
+                    "peak_source": f"{peaks['src']} burst bf16", "avg_launch_ms": avg_ms,
+                    "traffic": (DENSE_ON_NOISE_DRAM_BYTES if staged else NOISE_GEMM_DRAM_BYTES).get(args.workload),
+                    "noise_fill_ms": fill_ms, "regenerate_in_kernel": fused if staged else None}
     else:
         # matrix-vector: bytes of C read twice and dC written once (+ the small vectors)
         bytes_step = 3 * R * Kin * 4 + 4 * (3 * Kin + 2 * N + 2 * R)
@@ -364,7 +381,7 @@ def run_ours(args, cfg):
             "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if args.workload == "sharded" else "weak", "vs_baseline": None,
             "dtype": cfg["dtype"], "data": "synthetic", "config": workload_config(args.workload, cfg, world),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(args.workload, T) * args.steps,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(args.workload, staged) * args.steps,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
         if eager_ms is not None:
@@ -375,14 +392,19 @@ def run_ours(args, cfg):
         dist.destroy_process_group()
 
 
-def launches_per_step(workload, T):
-    # forward: dense z + generated-operand y; backward: generated-operand g + dense dX + dense dC
-    return 4 if workload == "gemv" else 5
+def launches_per_step(workload, staged):
+    # forward: dense z + generated-operand y; backward: generated-operand g + dense dX + dense dC;
+    # with S staged, forward and backward each launch the noise kernel once more
+    if workload == "gemv":
+        return 4
+    return 7 if staged else 5
 
 
 # DRAM bytes per launch of the generated-operand kernels: dram__bytes_read.sum + dram__bytes_write.sum of the
 # ncu capture summarised under profiles/ (2048-token case, 70.7 MB), scaled by tokens to the 8192-token launch.
 NOISE_GEMM_DRAM_BYTES = {"gemm": 2.83e8, "sharded": None}
+# the same for the plain tensor-core product reading the staged S (filled in from the capture under profiles/)
+DENSE_ON_NOISE_DRAM_BYTES = {"gemm": None, "sharded": None}
 
 
 def run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier):

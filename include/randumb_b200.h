@@ -81,9 +81,19 @@ const char *rdb_strerror(int code);
  *                          CTAs of a cluster share each generated stage through distributed shared memory
  *                        CTA-pair MMAs (cta_group::2), 512 tokens x 256 generated rows per pair:
  *                          7: one pair per cluster   8: two pairs   9: four pairs sharing the generated rows
+ *   RDB_OPT_DENSE_PAIR   1 (default): plain bf16 products with more than 128 rows and columns run on CTA pairs
+ *                        (cta_group::2, 512 x 256 or 256 x 256 tiles); 0: always the single-CTA 128 x 256 kernel
+ *   RDB_OPT_STAGE_NOISE  how rdb_linear_fwd / rdb_linear_bwd (bf16, factored) obtain the noise operand:
+ *                        0 (default): automatic -- for 1024 tokens or more, S (bf16, N x R, never W) is written
+ *                           once per call into the workspace and consumed by the plain tensor-core product, which
+ *                           hashes every noise element once instead of once per 512-token tile; below that, and
+ *                           whenever S would exceed 1 GiB, the kernels regenerate S tile by tile in shared memory
+ *                        1: always regenerate tile by tile (no S in memory)   2: always stage when it fits
  * Returns the previous value, or RDB_ERR_UNSUPPORTED for an unknown key.
  */
 #define RDB_OPT_NOISE_TILE 1
+#define RDB_OPT_DENSE_PAIR 2
+#define RDB_OPT_STAGE_NOISE 3
 int rdb_set_option(int key, int value);
 
 /*
@@ -126,6 +136,13 @@ int rdb_noise_1d(float *out, int64_t n, int64_t idx0, uint32_t seed, void *strea
  */
 size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path,
                                   int impl);
+
+/*
+ * 1 when the linear entry points would, for this problem, write S (bf16, N x R) into the workspace once per call
+ * and run the plain tensor-core product on it; 0 when they regenerate S tile by tile inside the kernel (or use the
+ * float32 kernels); negative: error.  See RDB_OPT_STAGE_NOISE.  No reference counterpart (a planning query).
+ */
+int rdb_linear_stages_noise(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl);
 
 /*
  * Forward  y[T,N] = x[T,K] * W^T  with W regenerated from (seed, row0) and coef[R,K].

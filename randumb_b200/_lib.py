@@ -17,6 +17,8 @@ F32, BF16 = 0, 1
 PATH_AUTO, PATH_FACTORED, PATH_WPATH = 0, 1, 2
 IMPL_AUTO, IMPL_SIMT, IMPL_UMMA = 0, 1, 2
 OPT_NOISE_TILE = 1
+OPT_DENSE_PAIR = 2
+OPT_STAGE_NOISE = 3
 STATUS_NAMES = {0: "ok", 1: "producer wait expired", 2: "mma wait expired", 3: "epilogue wait expired",
                 4: "generator wait expired"}
 
@@ -32,6 +34,7 @@ PROTOTYPES = {
     "rdb_noise": (_i32, [_vp, _i32, _i64, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_noise_1d": (_i32, [_vp, _i64, _i64, _u32, _vp]),
     "rdb_linear_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64, _i64, _i32, _i32, _i32]),
+    "rdb_linear_stages_noise": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32]),
     "rdb_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32, _vp, _vp]),
     "rdb_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32,
                               _vp, _vp]),

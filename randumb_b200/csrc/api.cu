@@ -6,6 +6,8 @@
 namespace rdb {
 
 static int g_noise_tile = 0;    // RDB_OPT_NOISE_TILE
+static int g_dense_pair = 0;    // RDB_OPT_DENSE_PAIR
+static int g_stage_noise = 0;   // RDB_OPT_STAGE_NOISE
 
 // FLOP-count rule: factored costs 2TR(K+N) per result, the W path 2NRK + 2TNK.
 static int choose_path(int path, int64_t T, int64_t K, int64_t N, int64_t R) {
@@ -29,14 +31,23 @@ static int choose_impl(int impl, int64_t T, int64_t K, int64_t N, int64_t R, int
     return ok ? RDB_IMPL_UMMA : RDB_IMPL_SIMT;
 }
 
+// Whether the bf16 factored products take S from a staged copy in the workspace (hashing every element once per
+// call) or regenerate it tile by tile inside the kernel (once per 512-token tile, nothing in memory).
+static bool stage_noise(int64_t T, int64_t N, int64_t R) {
+    const bool fits = (double)N * (double)R * 2.0 <= 1073741824.0;
+    if (g_stage_noise == 1 || !fits) return false;
+    if (g_stage_noise == 2) return true;
+    return T >= 1024;
+}
+
 struct WsLayout {
     size_t off[4];
     size_t total;
 };
 
 // Workspace segments (each 1024-byte aligned):
-//   UMMA factored  fwd: z bf16[T,R]
-//                  bwd: g bf16[T,R]
+//   UMMA factored  fwd: z bf16[T,R], then S bf16[N,R] when the noise operand is staged
+//                  bwd: g bf16[T,R], then S bf16[N,R] when staged
 //   SIMT factored  fwd: z f32[T,R]           bwd: g f32[T,R]
 //   SIMT W path    fwd: W f32[N,K]           bwd: W f32[N,K], dW f32[N,K]
 static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, int path, int impl) {
@@ -45,6 +56,7 @@ static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, in
     if (path == RDB_PATH_FACTORED) {
         if (impl == RDB_IMPL_UMMA) {
             seg[0] = (size_t)T * R * 2;
+            if (stage_noise(T, N, R)) seg[1] = (size_t)N * R * 2;
         } else {
             seg[0] = (size_t)T * R * 4;
         }
@@ -96,6 +108,15 @@ extern "C" int rdb_set_option(int key, int value) {
             prev = g_noise_tile;
             g_noise_tile = (value >= 0 && value <= 9) ? value : 0;
             set_noise_cfg(g_noise_tile);
+            return prev;
+        case RDB_OPT_DENSE_PAIR:
+            prev = g_dense_pair;
+            g_dense_pair = value ? 1 : 0;
+            set_dense_pair(g_dense_pair);
+            return prev;
+        case RDB_OPT_STAGE_NOISE:
+            prev = g_stage_noise;
+            g_stage_noise = (value >= 0 && value <= 2) ? value : 0;
             return prev;
         default: return RDB_ERR_UNSUPPORTED;
     }
@@ -150,6 +171,14 @@ extern "C" size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64
     return ws_layout(op, T, K, N, R, p, im).total;
 }
 
+extern "C" int rdb_linear_stages_noise(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl) {
+    if (T <= 0 || K <= 0 || N <= 0 || R <= 0) return 0;
+    const int p = choose_path(path, T, K, N, R);
+    const int im = choose_impl(impl, T, K, N, R, dtype, p);
+    if (im < 0) return im;
+    return (p == RDB_PATH_FACTORED && im == RDB_IMPL_UMMA && stage_noise(T, N, R)) ? 1 : 0;
+}
+
 extern "C" int rdb_linear_weight(void *w, const void *coef, int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed,
                                  int dtype, void *stream) {
     if (K < 0 || N < 0 || R < 0) return RDB_ERR_SHAPE;
@@ -194,6 +223,12 @@ extern "C" int rdb_linear_fwd(void *y, const void *x, const void *coef, void *wo
             void *z = ws + w.off[0];
             rc = umma_gemm_dense(z, x, coef, T, R, K, K, K, R, RDB_BF16, 1, 1, status, st);
             if (rc) return rc;
+            if (stage_noise(T, N, R)) {
+                void *S = ws + w.off[1];
+                rc = rdb_noise(S, RDB_BF16, N, R, R, row0, 0, seed, stream);
+                if (rc) return rc;
+                return umma_gemm_dense(y, z, S, T, N, R, R, R, N, RDB_BF16, 1, 1, status, st);   // y = z S^T
+            }
             return umma_gemm_noise(y, z, T, N, R, R, N, rows, status, st);
         }
         if (dtype == RDB_F32 && T == 1)
@@ -240,7 +275,14 @@ extern "C" int rdb_linear_bwd(void *dx, void *dc, const void *dy, const void *x,
         if (im == RDB_IMPL_UMMA) {
             void *g = ws + w.off[0];
             // g = dY S ; dX = g C (C read in place as an MN-major B operand) ; dC = g^T x (both operands MN-major)
-            rc = umma_gemm_noise(g, dy, T, R, N, N, R, cols, status, st);
+            if (stage_noise(T, N, R)) {
+                void *S = ws + w.off[1];
+                rc = rdb_noise(S, RDB_BF16, N, R, R, row0, 0, seed, stream);
+                if (rc) return rc;
+                rc = umma_gemm_dense(g, dy, S, T, R, N, N, R, R, RDB_BF16, 1, 0, status, st);    // S read as an MN-major operand
+            } else {
+                rc = umma_gemm_noise(g, dy, T, R, N, N, R, cols, status, st);
+            }
             if (rc) return rc;
             if (dx) {
                 rc = umma_gemm_dense(dx, g, coef, T, K, R, R, K, K, RDB_BF16, 1, 0, status, st);

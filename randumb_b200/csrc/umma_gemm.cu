@@ -790,7 +790,7 @@ struct DenseCfg {
 template <int BN, int STAGES, int A_MN, int B_MN, typename OutT>
 __global__ void __launch_bounds__(DenseCfg<BN, STAGES>::THREADS, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  OutT *__restrict__ d, int64_t ldd, int64_t M, int64_t N, int64_t Kc, int32_t *status) {
+                  OutT *__restrict__ d, int64_t ldd, int64_t M, int64_t N, int64_t Kc, int m_fast, int32_t *status) {
     using Cfg = DenseCfg<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tmem_full[2], bar_tmem_empty[2];
@@ -830,8 +830,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             PipeState st;
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int32_t m0 = (int32_t)((tile / tiles_n) * BM);
-                const int32_t n0 = (int32_t)((tile % tiles_n) * BN);
+                const int32_t m0 = (int32_t)((m_fast ? tile % tiles_m : tile / tiles_n) * BM);
+                const int32_t n0 = (int32_t)((m_fast ? tile / tiles_m : tile % tiles_n) * BN);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&bar_empty[st.idx]), st.phase ^ 1, abortp)) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
@@ -913,8 +913,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int q = warp & 3;
         uint32_t acc = 0, acc_phase = 0;
         for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            const int64_t m0 = (tile / tiles_n) * BM;
-            const int64_t n0 = (tile % tiles_n) * BN;
+            const int64_t m0 = (m_fast ? tile % tiles_m : tile / tiles_n) * BM;
+            const int64_t n0 = (m_fast ? tile / tiles_m : tile % tiles_n) * BN;
             if (!mbar_wait_warp<false>(smem_u32(&bar_tmem_full[acc]), acc_phase, abortp)) {
                 raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
                 break;
@@ -941,6 +941,285 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ================================================================================================
+// dense_pair_kernel: D[M,N] = op(A) op(B)^T on CTA pairs (tcgen05 cta_group::2), bf16 output
+//
+// One pair owns a tile of MT*256 rows x 256 columns.  Each pair MMA is 256 x 256 x 16: the even CTA holds rows
+// [0,128) and the odd CTA rows [128,256) of the 256-row sub-tile in its TMEM lanes, and each CTA stages only its
+// own 128 rows of A and its own 128 of the 256 B rows, so a 64-wide k-block costs a CTA (MT+1)*16 KB of TMA
+// traffic for MT*128x256x64 MACs.  MT = 2 fills TMEM with one tile (two accumulators, released one by one to
+// the next tile); MT = 1 alternates between the two accumulators so the epilogue overlaps the next main loop.
+//
+//   warp 0      TMA producer (own A rows, own half of B)
+//   warp 1      MMA issuer (even CTA only); tcgen05.commit frees the stage in both CTAs
+//   warps 2-9   epilogue: TMEM -> bf16 -> swizzled staging -> TMA tile stores (two warps per lane quarter)
+//   warp 10     odd CTA: tells the even CTA when a stage has landed here
+// ================================================================================================
+template <int MT, int D>
+struct DensePairCfg {
+    static constexpr int BN = 256;
+    static constexpr int HALF = BN / 2;
+    static constexpr int A_PART = MT * SUB_BYTES;
+    static constexpr int B_PART = HALF * BK * 2;
+    static constexpr int STAGE = A_PART + B_PART;
+    static constexpr int EPI_WARPS = 8;
+    static constexpr int FIRST_EPI_WARP = 2;
+    static constexpr int RELAY_WARP = FIRST_EPI_WARP + EPI_WARPS;
+    static constexpr int THREADS = (RELAY_WARP + 1) * 32;
+    static constexpr int OUT_STAGING = EPI_WARPS * 4096;               // per epilogue warp: one [32 rows x 64 columns] bf16 box
+    static constexpr int SMEM_DYN = D * STAGE + OUT_STAGING + 1024;
+    static_assert(MT == 1 || MT == 2, "sub-tiles per pair tile");
+    static_assert(SMEM_DYN <= 232448 - 512, "shared memory");
+};
+
+template <int MT, int D, int A_MN, int B_MN>
+__global__ void __launch_bounds__(DensePairCfg<MT, D>::THREADS, 1)
+dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_d, int64_t M, int64_t N, int64_t Kc, int m_fast, int32_t *status) {
+    using Cfg = DensePairCfg<MT, D>;
+    constexpr int BN = Cfg::BN;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[D], bar_free[D], bar_tmem_full[2], bar_tmem_empty[2];
+    __shared__ uint32_t tmem_holder;
+    __shared__ int abort_flag;
+
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;   // stage s: A sub-tiles, then this CTA's half of the B tile
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t half = rank & 1;
+    const bool leader = (half == 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < D; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), leader ? 2 : 1);    // own TMA thread (+ the odd CTA's relay on the even CTA)
+            mbar_init(smem_u32(&bar_free[s]), 1);                 // one tcgen05.commit from the pair's MMA thread
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bar_tmem_full[s]), 1);
+            mbar_init(smem_u32(&bar_tmem_empty[s]), 2 * Cfg::EPI_WARPS);
+        }
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(&tmem_holder), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+    volatile int *abortp = &abort_flag;
+
+    const int64_t tiles_m = (M + (int64_t)MT * 2 * BM - 1) / ((int64_t)MT * 2 * BM);
+    const int64_t tiles_n = (N + BN - 1) / BN;
+    const int64_t total_tiles = tiles_m * tiles_n;
+    const int64_t pair_id = blockIdx.x >> 1;
+    const int64_t num_pairs = gridDim.x >> 1;
+    const int num_kb = (int)((Kc + BK - 1) / BK);
+    // consecutive tiles share the B panel (m_fast) or the A panel: the larger operand is the one streamed once
+    auto tile_m = [&](int64_t t) { return m_fast ? (t % tiles_m) : (t / tiles_n); };
+    auto tile_n = [&](int64_t t) { return m_fast ? (t / tiles_m) : (t % tiles_n); };
+    // accumulator and barrier parity used by sub-tile s of this CTA's it-th tile
+    auto acc_of = [&](int64_t it, int s) { return MT == 2 ? s : (int)(it & 1); };
+    auto par_of = [&](int64_t it) { return (uint32_t)(MT == 2 ? (it & 1) : ((it >> 1) & 1)); };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            prefetch_tmap(&tmap_a);
+            prefetch_tmap(&tmap_b);
+            PipeState st;
+            bool ok = true;
+            for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs) {
+                const int32_t m0 = (int32_t)(tile_m(t) * MT * 2 * BM + half * BM);
+                const int32_t n0 = (int32_t)(tile_n(t) * BN + half * Cfg::HALF);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_cluster(smem_u32(&bar_free[st.idx]), st.phase ^ 1, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = smem_u32(&bar_full[st.idx]);
+                    mbar_arrive_expect_tx(fb, Cfg::STAGE);
+                    const uint32_t sa = smem_base + st.idx * Cfg::STAGE;
+                    const uint32_t sb = sa + Cfg::A_PART;
+#pragma unroll
+                    for (int s = 0; s < MT; ++s) {
+                        if (A_MN) {
+#pragma unroll
+                            for (int i = 0; i < BM / 64; ++i)
+                                tma_load_2d(sa + s * SUB_BYTES + i * (64 * BK * 2), &tmap_a, fb, m0 + s * 2 * BM + i * 64, kb * BK);
+                        } else {
+                            tma_load_2d(sa + s * SUB_BYTES, &tmap_a, fb, kb * BK, m0 + s * 2 * BM);
+                        }
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int i = 0; i < Cfg::HALF / 64; ++i) tma_load_2d(sb + i * (64 * BK * 2), &tmap_b, fb, n0 + i * 64, kb * BK);
+                    } else {
+                        tma_load_2d(sb, &tmap_b, fb, kb * BK, n0);
+                    }
+                    st.advance<D>();
+                }
+            }
+            if (!ok) {
+                for (int s = 0; s < D; ++s) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&bar_full[s]), 0) && !mbar_try_wait(smem_u32(&bar_full[s]), 1)) {
+                        if (clock64() - t0 > 20000000LL) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (even CTA of the pair)
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BN, A_MN, B_MN);
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            constexpr uint32_t A_LBO = A_MN ? 64 * BK * 2 : 0, A_KSTEP = A_MN ? 2048 : UMMA_K * 2;
+            constexpr uint32_t B_LBO = B_MN ? 64 * BK * 2 : 0, B_KSTEP = B_MN ? 2048 : UMMA_K * 2;
+            const uint32_t peer = rank ^ 1u;
+            PipeState st;
+            bool ok = true;
+            int64_t it = 0;
+            for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
+                for (int kb = 0; kb < num_kb && ok; ++kb) {
+                    if (!mbar_wait_cluster(smem_u32(&bar_full[st.idx]), st.phase, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_base + st.idx * Cfg::STAGE;
+                    const uint32_t b_lo = smem_desc_lo(sa + Cfg::A_PART, B_LBO);
+#pragma unroll
+                    for (int s = 0; s < MT; ++s) {
+                        const int a = acc_of(it, s);
+                        if (kb == 0) {
+                            // the accumulator is reusable once both CTAs' epilogues have drained it
+                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[a]), par_of(it) ^ 1, abortp)) {
+                                raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                        }
+                        const uint32_t a_lo = smem_desc_lo(sa + s * SUB_BYTES, A_LBO);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t adesc = pack_desc(a_lo + ((k * A_KSTEP) >> 4), desc_hi);
+                            const uint64_t bdesc = pack_desc(b_lo + ((k * B_KSTEP) >> 4), desc_hi);
+                            umma_bf16_pair(tmem_base + a * BN, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                        if (kb == num_kb - 1) {
+                            umma_commit_pair(smem_u32(&bar_tmem_full[a]));
+                            umma_commit_pair(mapa(smem_u32(&bar_tmem_full[a]), peer));
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit_pair(smem_u32(&bar_free[st.idx]));
+                    umma_commit_pair(mapa(smem_u32(&bar_free[st.idx]), peer));
+                    st.advance<D>();
+                }
+            }
+        }
+    } else if (warp < Cfg::RELAY_WARP) {
+        // ------------------------------------------------------------------ epilogue (8 warps, this CTA's 128 rows)
+        const int ew = warp - Cfg::FIRST_EPI_WARP;
+        const int q = warp & 3;                      // TMEM lane quarter this warp may read
+        const int cg = ew >> 2;                      // which 128 of the 256 accumulator columns
+        const uint32_t leader_rank = rank & ~1u;
+        const uint32_t stag = smem_base + D * Cfg::STAGE + (uint32_t)ew * 4096u;
+        int64_t it = 0;
+        bool ok = true;
+        for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
+            const int64_t m0 = tile_m(t) * MT * 2 * BM + half * BM;
+            const int64_t n0 = tile_n(t) * BN;
+#pragma unroll 1
+            for (int s = 0; s < MT; ++s) {
+                const int a = acc_of(it, s);
+                if (!mbar_wait_warp<true>(smem_u32(&bar_tmem_full[a]), par_of(it), abortp)) {
+                    raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const int64_t row_w = m0 + s * 2 * BM + q * 32;    // first row of this warp's 32-row slab
+#pragma unroll 1
+                for (int hb = 0; hb < 2; ++hb) {
+                    const int c0 = cg * 128 + hb * 64;
+                    uint32_t r0[32], r1[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c0);
+                    tmem_ld_32x32(taddr, r0);
+                    tmem_ld_32x32(taddr + 32, r1);
+                    // the previous store of this warp must have finished reading the staging box
+                    if (lane == 0) bulk_wait_group_read0();
+                    __syncwarp();
+                    tmem_ld_wait();
+                    const uint32_t rowaddr = stag + (uint32_t)lane * 128u;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t pk[4], pl[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 2 * e]), __uint_as_float(r0[j * 8 + 2 * e + 1]));
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r1[j * 8 + 2 * e]), __uint_as_float(r1[j * 8 + 2 * e + 1]));
+                            pk[e] = *reinterpret_cast<uint32_t *>(&h0);
+                            pl[e] = *reinterpret_cast<uint32_t *>(&h1);
+                        }
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)((j ^ (lane & 7)) << 4)),
+                                     "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)(((4 + j) ^ (lane & 7)) << 4)),
+                                     "r"(pl[0]), "r"(pl[1]), "r"(pl[2]), "r"(pl[3]) : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row_w < M && n0 + c0 < N) {
+                        tma_store_2d(&tmap_d, stag, (int32_t)(n0 + c0), (int32_t)row_w);
+                        bulk_commit_group();
+                    }
+                }
+                // this warp's part of the accumulator has been read out: tell the MMA thread of the pair
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
+            }
+        }
+        if (lane == 0) bulk_wait_group0();   // all output tiles written before the CTA retires
+    } else {
+        // ------------------------------------------------------------------ odd CTA: a stage has landed here -> even CTA
+        if (lane == 0 && !leader) {
+            const uint32_t leader_rank = rank & ~1u;
+            PipeState st;
+            bool ok = true;
+            for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_cluster(smem_u32(&bar_full[st.idx]), st.phase, abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_cluster(mapa(smem_u32(&bar_full[st.idx]), leader_rank));
+                    st.advance<D>();
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();   // no CTA retires (or frees TMEM) while its peer may still use it
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -1143,13 +1422,93 @@ static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_
     if (e != cudaSuccess) return (int)e;
     const int64_t tiles = cdiv64(M, BM) * cdiv64(N, BN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, tb, reinterpret_cast<OutT *>(d), ldd, M, N, Kc, status);
+    // tiles that run at the same time share the panel of the larger operand, which is then streamed from memory once
+    const int m_fast = (M <= N) ? 1 : 0;
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, tb, reinterpret_cast<OutT *>(d), ldd, M, N, Kc, m_fast, status);
     return launch_status();
 }
+
+template <int MT, int D, int A_MN, int B_MN>
+static int launch_dense_pair(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
+                             int64_t ldd, int64_t tiles, int max_pairs, int32_t *status, cudaStream_t st) {
+    using Cfg = DensePairCfg<MT, D>;
+    CUtensorMap ta, tb, td;
+    int rc = A_MN ? make_tmap(&ta, a, M, Kc, lda, 64, BK) : make_tmap(&ta, a, Kc, M, lda, BK, BM);
+    if (rc) return rc;
+    rc = B_MN ? make_tmap(&tb, b, N, Kc, ldb, 64, BK) : make_tmap(&tb, b, Kc, N, ldb, BK, Cfg::HALF);
+    if (rc) return rc;
+    rc = make_tmap(&td, d, N, M, ldd, 64, 32);   // output tiles of 32 rows x 64 columns
+    if (rc) return rc;
+    auto kern = dense_pair_kernel<MT, D, A_MN, B_MN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(Cfg::THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_DYN;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int64_t npairs = tiles < max_pairs ? tiles : max_pairs;
+    cfg.gridDim = dim3((unsigned)(npairs * 2));
+    // stream the larger operand once: consecutive tiles share the B panel when A is the smaller matrix
+    const int m_fast = (M <= N) ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, Kc, m_fast, status);
+    if (e != cudaSuccess) return (int)e;
+    return launch_status();
+}
+
+// how many CTA pairs can be resident at once (one CTA per SM)
+static int max_resident_pairs() {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    if (dev == cached_dev && cached > 0) return cached;
+    auto kern = dense_pair_kernel<2, 4, 0, 0>;
+    int n = 0, fallback = sm_count() / 2;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DensePairCfg<2, 4>::SMEM_DYN) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.blockDim = dim3(DensePairCfg<2, 4>::THREADS);
+        cfg.dynamicSmemBytes = DensePairCfg<2, 4>::SMEM_DYN;
+        cfg.gridDim = dim3(2);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) n = 0;
+    }
+    (void)cudaGetLastError();
+    cached_dev = dev;
+    cached = n > 0 ? n : fallback;
+    return cached;
+}
+
+template <int A_MN, int B_MN>
+static int dense_pair_by_tile(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
+                              int64_t ldd, int32_t *status, cudaStream_t st) {
+    const int P = max_resident_pairs();
+    const int64_t t2 = cdiv64(M, 4 * BM) * cdiv64(N, 256), t1 = cdiv64(M, 2 * BM) * cdiv64(N, 256);
+    // time ~ waves x rows per tile; the 512-row tile moves fewer operand bytes per MAC, so it wins ties
+    const int64_t cost2 = cdiv64(t2, P) * 2, cost1 = cdiv64(t1, P);
+    if (cost2 <= cost1) return launch_dense_pair<2, 4, A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, t2, P, status, st);
+    return launch_dense_pair<1, 6, A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, t1, P, status, st);
+}
+
+static int g_dense_pair = 0;   // RDB_OPT_DENSE_PAIR
+void set_dense_pair(int v) { g_dense_pair = v; }
 
 template <int A_MN, int B_MN>
 static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
                         int64_t ldd, int d_dtype, int32_t *status, cudaStream_t st) {
+    if (d_dtype == RDB_BF16 && g_dense_pair && M > BM && N > BM)
+        return dense_pair_by_tile<A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
     if (d_dtype == RDB_BF16)
         return launch_dense<256, 4, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
     if (d_dtype == RDB_F32) return launch_dense<256, 4, A_MN, B_MN, float>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);

@@ -181,7 +181,7 @@ def sharded_forward(x: torch.Tensor, coef: torch.Tensor, seed: int, plan: Sharde
     from . import kernels as K
     z_loc = K.gemm_dense(x[plan.tok_lo:plan.tok_hi].contiguous(), coef)                      # [t_r, R]
     z = _all_gather_rows_plain(z_loc, plan.tok_sizes, group) if plan.world > 1 else z_loc
-    return K.gemm_noise(z, plan.row_hi - plan.row_lo, seed, False, plan.row_lo)               # [T, n_r]
+    return K.noise_product(z, plan.row_hi - plan.row_lo, seed, False, plan.row_lo)               # [T, n_r]
 
 
 def sharded_backward(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan,
@@ -190,7 +190,7 @@ def sharded_backward(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor
     ranks (T x R, small), then dX and dC are computed for this rank's tokens and exchanged."""
     from . import kernels as K
     R = coef.shape[0]
-    g = K.gemm_noise(dy_local.contiguous(), R, seed, True, plan.row_lo)                       # partial [T, R]
+    g = K.noise_product(dy_local.contiguous(), R, seed, True, plan.row_lo)                       # partial [T, R]
     if plan.world > 1:
         dist.all_reduce(g, group=group)
     g_loc = g[plan.tok_lo:plan.tok_hi].contiguous()

@@ -55,9 +55,21 @@ def test_argument_errors_are_caught_on_host(built_lib):
 
 def test_workspace_sizes(built_lib):
     L = _lib.lib()
-    # bf16 factored on tensor cores: z or g, bf16 [T, R]
-    assert L.rdb_linear_workspace_bytes(0, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == 8192 * 1024 * 2
-    assert L.rdb_linear_workspace_bytes(1, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == 8192 * 1024 * 2
+    # bf16 factored on tensor cores: z or g, bf16 [T, R], plus S bf16 [N, R] when the noise operand is staged
+    zg, S = 8192 * 1024 * 2, 16384 * 1024 * 2
+    assert L.rdb_linear_stages_noise(8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == 1
+    assert L.rdb_linear_workspace_bytes(0, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == zg + S
+    assert L.rdb_linear_workspace_bytes(1, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == zg + S
+    assert L.rdb_set_option(_lib.OPT_STAGE_NOISE, 1) == 0          # regenerate inside the kernel: nothing of S in memory
+    try:
+        assert L.rdb_linear_stages_noise(8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == 0
+        assert L.rdb_linear_workspace_bytes(0, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == zg
+    finally:
+        assert L.rdb_set_option(_lib.OPT_STAGE_NOISE, 0) == 1
+    # few tokens: one 512-token tile regenerates S once anyway; a noise block above 1 GiB is never staged
+    assert L.rdb_linear_stages_noise(512, 4096, 16384, 1024, _lib.BF16, 0, 0) == 0
+    assert L.rdb_linear_stages_noise(8192, 4096, 1 << 20, 1024, _lib.BF16, 0, 0) == 0
+    assert L.rdb_linear_stages_noise(8192, 4096, 16384, 1024, _lib.F32, 0, 0) == 0
     # fp32 factored: f32 [T, R]
     assert L.rdb_linear_workspace_bytes(0, 64, 784, 256, 64, _lib.F32, 0, 0) == 64 * 64 * 4
     # a 256 -> 10 head is cheaper through W: f32 [N, K] (+ dW in backward)

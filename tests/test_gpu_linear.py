@@ -89,11 +89,47 @@ def test_bf16_layer_every_work_unit_shape(K, tile):
     """Every (cluster size, sub-tiles, generated rows) variant of the generated-operand kernel, on a shape
     with ragged tiles and an odd number of token tiles per cluster."""
     prev = K.set_option(1, tile)
+    prev_stage = K.set_option(3, 1)          # regenerate S inside the kernel whatever the token count
     try:
         _check(K, 1500, 264, 520, 72, torch.bfloat16, 7, 10, K.PATH_FACTORED, K.IMPL_UMMA, BF16_TOL)
         _check(K, 100, 64, 136, 200, torch.bfloat16, 8, 0, K.PATH_FACTORED, K.IMPL_UMMA, BF16_TOL)
     finally:
         K.set_option(1, prev)
+        K.set_option(3, prev_stage)
+
+
+@pytest.mark.parametrize("T,Kin,N,R,seed,row0", [
+    (1500, 264, 520, 72, 7, 10),        # ragged tiles
+    (2048, 512, 1024, 256, 3, 65000),   # noise rows across 2^16
+    (8, 8, 8, 8, 3, 0), (100, 64, 136, 200, 8, 0)])
+def test_staged_noise_equals_regenerated_noise(K, T, Kin, N, R, seed, row0):
+    """S written once per call and read back by the plain product gives the bits of the kernels that regenerate S per
+    tile (same bf16 noise values, same accumulation order), and both agree with the oracle."""
+    x, C, dy = _inputs(T, Kin, N, R, torch.bfloat16, seed)
+    xg, Cg, dyg = x.cuda(), C.cuda(), dy.cuda()
+    outs = {}
+    for mode in (1, 2):
+        prev = K.set_option(3, mode)
+        try:
+            assert K.linear_stages_noise(T, Kin, N, R, torch.bfloat16, K.PATH_FACTORED, K.IMPL_UMMA) == (mode == 2)
+            y = K.linear_fwd(xg, Cg, seed, N, row0, path=K.PATH_FACTORED, impl=K.IMPL_UMMA)
+            dx, dc = K.linear_bwd(dyg, xg, Cg, seed, row0, path=K.PATH_FACTORED, impl=K.IMPL_UMMA)
+            outs[mode] = (y, dx, dc)
+        finally:
+            K.set_option(3, prev)
+    K.check_status()
+    for a, b in zip(outs[1], outs[2]):
+        assert torch.equal(a, b)
+    y, dx, dc = O.linear_reference(x, C, seed, N, row0, dy, dtype=torch.float32)
+    assert O.close(outs[2][0], y, BF16_TOL) and O.close(outs[2][1], dx, BF16_TOL) and O.close(outs[2][2], dc, BF16_TOL)
+    # the building block used by the row-sharded layer follows the same rule
+    z = torch.randn(T, R, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+    prev = K.set_option(3, 2)
+    try:
+        assert torch.equal(K.noise_product(z, N, seed, False, row0), K.gemm_noise(z, N, seed, False, row0))
+        assert torch.equal(K.noise_product(dyg, R, seed, True, row0), K.gemm_noise(dyg, R, seed, True, row0))
+    finally:
+        K.set_option(3, prev)
 
 
 @pytest.mark.parametrize("T,Kin,N,R,seed,row0,path", [(64, 80, 96, 16, 0, 0, 0), (33, 70, 45, 9, 5, 7, 2), (33, 70, 45, 9, 5, 7, 1)])
@@ -135,6 +171,27 @@ def test_dense_products_all_operand_layouts(K, akm, bkm, out):
     assert O.close(d, ref, 1e-2 if out == torch.bfloat16 else 1e-5)
     d2 = K.gemm_dense(a, b, akm, bkm, out_dtype=out, impl=K.IMPL_SIMT)
     assert O.close(d2, ref, 1e-2 if out == torch.bfloat16 else 1e-5)
+
+
+@pytest.mark.parametrize("akm,bkm", [(True, True), (True, False), (False, True), (False, False)])
+@pytest.mark.parametrize("M,N,Kc", [(1000, 520, 328), (2048, 264, 72), (136, 136, 8), (300, 1032, 4096)])
+def test_dense_products_on_cta_pairs(K, akm, bkm, M, N, Kc):
+    """The cta_group::2 kernel (512 x 256 and 256 x 256 pair tiles) against the single-CTA kernel: same bits."""
+    g = torch.Generator().manual_seed(5)
+    A = torch.randn(M, Kc, generator=g).bfloat16()
+    B = torch.randn(N, Kc, generator=g).bfloat16()
+    a = (A if akm else A.t().contiguous()).cuda()
+    b = (B if bkm else B.t().contiguous()).cuda()
+    outs = []
+    for pair in (0, 1):
+        prev = K.set_option(2, pair)
+        try:
+            outs.append(K.gemm_dense(a, b, akm, bkm, impl=K.IMPL_UMMA))
+        finally:
+            K.set_option(2, prev)
+    K.check_status()
+    assert torch.equal(outs[0], outs[1])
+    assert O.close(outs[1], A.float() @ B.float().t(), 1e-2)
 
 
 # ---- edge cases ----------------------------------------------------------------------------------------
