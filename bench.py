@@ -238,9 +238,11 @@ def run_ours(args, cfg):
             dx, dc = rb.parallel.sharded_backward(dy, x, C, seed, plan)
             return y, dx, dc
         y = K.linear_fwd(x, C, seed, n_local, row0)
-        dx, dc = K.linear_bwd(dy, x, C, seed, row0)
         if world > 1:
-            dist.all_reduce(dc)
+            # data parallel: dC first, its all-reduce overlapped with the dX product
+            dx, dc = rb.parallel.data_parallel_backward(dy, x, C, seed, row0)
+        else:
+            dx, dc = K.linear_bwd(dy, x, C, seed, row0)
         return y, dx, dc
 
     def barrier():
@@ -330,7 +332,14 @@ def run_ours(args, cfg):
         if staged:
             S = K.noise(n_local, R, seed, row0, 0, dt, dev)
             avg_ms = time_pair(lambda: K.gemm_dense(z, S), lambda: K.gemm_dense(dy, S, True, False))
-            fill_ms = time_pair(lambda: K.noise(n_local, R, seed, row0, 0, dt, dev), lambda: None) * 2
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(20):                  # back to back, so the interval is device time and not launch overhead
+                K.noise(n_local, R, seed, row0, 0, dt, dev)
+            e1.record()
+            torch.cuda.synchronize()
+            fill_ms = e0.elapsed_time(e1) / 20
             kernel = ("dense_gemm_kernel (y = z S^T and g = dY S, average over both launches) on S hashed once per call into a "
                       "bf16 scratch by noise_kernel")
         else:

@@ -81,8 +81,10 @@ const char *rdb_strerror(int code);
  *                          CTAs of a cluster share each generated stage through distributed shared memory
  *                        CTA-pair MMAs (cta_group::2), 512 tokens x 256 generated rows per pair:
  *                          7: one pair per cluster   8: two pairs   9: four pairs sharing the generated rows
- *   RDB_OPT_DENSE_PAIR   1 (default): plain bf16 products with more than 128 rows and columns run on CTA pairs
- *                        (cta_group::2, 512 x 256 or 256 x 256 tiles); 0: always the single-CTA 128 x 256 kernel
+ *   RDB_OPT_DENSE_PAIR   plain bf16 products with more than 128 rows and columns:
+ *                        1 (default): CTA pairs (cta_group::2, 512 x 256 tiles) when the tiles fill the resident
+ *                           pairs evenly, else the single-CTA 128 x 256 kernel
+ *                        0: always the single-CTA kernel   2: always CTA pairs
  *   RDB_OPT_STAGE_NOISE  how rdb_linear_fwd / rdb_linear_bwd (bf16, factored) obtain the noise operand:
  *                        0 (default): automatic -- for 1024 tokens or more, S (bf16, N x R, never W) is written
  *                           once per call into the workspace and consumed by the plain tensor-core product, which

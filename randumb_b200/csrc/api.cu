@@ -6,7 +6,7 @@
 namespace rdb {
 
 static int g_noise_tile = 0;    // RDB_OPT_NOISE_TILE
-static int g_dense_pair = 0;    // RDB_OPT_DENSE_PAIR
+static int g_dense_pair = 1;    // RDB_OPT_DENSE_PAIR
 static int g_stage_noise = 0;   // RDB_OPT_STAGE_NOISE
 
 // FLOP-count rule: factored costs 2TR(K+N) per result, the W path 2NRK + 2TNK.
@@ -111,7 +111,7 @@ extern "C" int rdb_set_option(int key, int value) {
             return prev;
         case RDB_OPT_DENSE_PAIR:
             prev = g_dense_pair;
-            g_dense_pair = value ? 1 : 0;
+            g_dense_pair = (value >= 0 && value <= 2) ? value : 1;
             set_dense_pair(g_dense_pair);
             return prev;
         case RDB_OPT_STAGE_NOISE:

@@ -59,6 +59,27 @@ __global__ void noise_kernel(void *__restrict__ out, int64_t rows, int64_t cols,
     }
 }
 
+// bf16 fast path (the staged noise operand of the tensor-core products): cols a multiple of 8, 16-byte aligned rows,
+// fewer than 2^31 groups.  One thread hashes 8 consecutive elements of a row and writes them with one 16-byte store;
+// all index arithmetic is 32-bit.
+__global__ void __launch_bounds__(256) noise_bf16x8_kernel(uint4 *__restrict__ out, uint32_t total, uint32_t cgroups,
+                                                           uint32_t ld_groups, Sq5Lin lin) {
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const uint32_t r = idx / cgroups;
+        const uint32_t cg = idx - r * cgroups;
+        const uint32_t b0 = lin.base + r * lin.sn + (cg << 3) * lin.sk;
+        uint32_t p[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float f0 = sq5_to_float(sq5_tail(b0 + (uint32_t)(2 * j) * lin.sk));
+            const float f1 = sq5_to_float(sq5_tail(b0 + (uint32_t)(2 * j + 1) * lin.sk));
+            __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+            p[j] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        out[(size_t)r * ld_groups + cg] = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+}
+
 __global__ void noise_1d_kernel(float *__restrict__ out, int64_t n, uint32_t idx0, uint32_t seed) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         out[i] = sq5_to_float(sq5_tail((idx0 + (uint32_t)i) * SQ5_N1 + seed));
@@ -77,6 +98,15 @@ static int launch_noise(void *out, int64_t rows, int64_t cols, int64_t ld, int64
                         cudaStream_t st) {
     if (rows == 0 || cols == 0) return RDB_OK;
     Sq5Lin lin = sq5_lin_rows(seed, (uint32_t)row0, (uint32_t)col0);
+    if (MODE == 2 && (cols & 7) == 0 && (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+        rows * (cols >> 3) < (1LL << 31)) {
+        const uint32_t total = (uint32_t)(rows * (cols >> 3));
+        const int64_t want = cdiv64(total, 256 * 4);           // about four groups (32 elements) per thread
+        const int grid = (int)(want < 148 * 8 ? (want < 1 ? 1 : want) : 148 * 8);
+        noise_bf16x8_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<uint4 *>(out), total, (uint32_t)(cols >> 3),
+                                                 (uint32_t)(ld >> 3), lin);
+        return launch_status();
+    }
     const int64_t items = rows * ((cols + 3) >> 2);
     noise_kernel<MODE><<<grid_for(items, 256), 256, 0, st>>>(out, rows, cols, ld, lin);
     return launch_status();

@@ -177,6 +177,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
         : "memory");
 }
 
+// The same load issued by one CTA of a pair: the bytes land in this CTA's shared memory, the transaction bytes are
+// completed on `cluster_bar`, a shared::cluster barrier address that may belong to the peer CTA (cta_group::2 form).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap *m, uint32_t cluster_bar, int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(cluster_bar), "r"(x), "r"(y)
+        : "memory");
+}
+
 // 2-D tile store shared -> global (bulk async group); rows/columns outside the tensor are clipped.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t smem_src, int32_t x, int32_t y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"

@@ -953,10 +953,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 // traffic for MT*128x256x64 MACs.  MT = 2 fills TMEM with one tile (two accumulators, released one by one to
 // the next tile); MT = 1 alternates between the two accumulators so the epilogue overlaps the next main loop.
 //
-//   warp 0      TMA producer (own A rows, own half of B)
+//   warp 0      TMA producer (own A rows, own half of B); the loads of both CTAs complete their transaction bytes on
+//               the even CTA's barrier (cta_group::2 form of the load), so the MMA thread waits on one barrier
 //   warp 1      MMA issuer (even CTA only); tcgen05.commit frees the stage in both CTAs
 //   warps 2-9   epilogue: TMEM -> bf16 -> swizzled staging -> TMA tile stores (two warps per lane quarter)
-//   warp 10     odd CTA: tells the even CTA when a stage has landed here
 // ================================================================================================
 template <int MT, int D>
 struct DensePairCfg {
@@ -967,8 +967,8 @@ struct DensePairCfg {
     static constexpr int STAGE = A_PART + B_PART;
     static constexpr int EPI_WARPS = 8;
     static constexpr int FIRST_EPI_WARP = 2;
-    static constexpr int RELAY_WARP = FIRST_EPI_WARP + EPI_WARPS;
-    static constexpr int THREADS = (RELAY_WARP + 1) * 32;
+    static constexpr int END_WARP = FIRST_EPI_WARP + EPI_WARPS;
+    static constexpr int THREADS = END_WARP * 32;
     static constexpr int OUT_STAGING = EPI_WARPS * 4096;               // per epilogue warp: one [32 rows x 64 columns] bf16 box
     static constexpr int SMEM_DYN = D * STAGE + OUT_STAGING + 1024;
     static_assert(MT == 1 || MT == 2, "sub-tiles per pair tile");
@@ -978,7 +978,8 @@ struct DensePairCfg {
 template <int MT, int D, int A_MN, int B_MN>
 __global__ void __launch_bounds__(DensePairCfg<MT, D>::THREADS, 1)
 dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ CUtensorMap tmap_d, int64_t M, int64_t N, int64_t Kc, int m_fast, int32_t *status) {
+                  const __grid_constant__ CUtensorMap tmap_d, int64_t M, int64_t N, int64_t Kc, int m_fast, int32_t *status, long long *prof) {
+    long long pc0 = 0, pc2 = 0;
     using Cfg = DensePairCfg<MT, D>;
     constexpr int BN = Cfg::BN;
     extern __shared__ uint8_t smem_raw[];
@@ -996,7 +997,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < D; ++s) {
-            mbar_init(smem_u32(&bar_full[s]), leader ? 2 : 1);    // own TMA thread (+ the odd CTA's relay on the even CTA)
+            mbar_init(smem_u32(&bar_full[s]), 1);                 // the even CTA's TMA thread; both CTAs' loads complete their bytes here
             mbar_init(smem_u32(&bar_free[s]), 1);                 // one tcgen05.commit from the pair's MMA thread
         }
         for (int s = 0; s < 2; ++s) {
@@ -1041,13 +1042,16 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 const int32_t m0 = (int32_t)(tile_m(t) * MT * 2 * BM + half * BM);
                 const int32_t n0 = (int32_t)(tile_n(t) * BN + half * Cfg::HALF);
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    const long long tw = prof ? clock64() : 0;
                     if (!mbar_wait_cluster(smem_u32(&bar_free[st.idx]), st.phase ^ 1, abortp)) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
                         ok = false;
                         break;
                     }
-                    const uint32_t fb = smem_u32(&bar_full[st.idx]);
-                    mbar_arrive_expect_tx(fb, Cfg::STAGE);
+                    if (prof) pc0 += clock64() - tw;
+                    // both CTAs' loads of a stage complete their bytes on the even CTA's barrier, where the MMA thread waits
+                    const uint32_t fb = mapa(smem_u32(&bar_full[st.idx]), rank & ~1u);
+                    if (leader) mbar_arrive_expect_tx(smem_u32(&bar_full[st.idx]), 2 * Cfg::STAGE);
                     const uint32_t sa = smem_base + st.idx * Cfg::STAGE;
                     const uint32_t sb = sa + Cfg::A_PART;
 #pragma unroll
@@ -1055,26 +1059,26 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         if (A_MN) {
 #pragma unroll
                             for (int i = 0; i < BM / 64; ++i)
-                                tma_load_2d(sa + s * SUB_BYTES + i * (64 * BK * 2), &tmap_a, fb, m0 + s * 2 * BM + i * 64, kb * BK);
+                                tma_load_2d_pair(sa + s * SUB_BYTES + i * (64 * BK * 2), &tmap_a, fb, m0 + s * 2 * BM + i * 64, kb * BK);
                         } else {
-                            tma_load_2d(sa + s * SUB_BYTES, &tmap_a, fb, kb * BK, m0 + s * 2 * BM);
+                            tma_load_2d_pair(sa + s * SUB_BYTES, &tmap_a, fb, kb * BK, m0 + s * 2 * BM);
                         }
                     }
                     if (B_MN) {
 #pragma unroll
-                        for (int i = 0; i < Cfg::HALF / 64; ++i) tma_load_2d(sb + i * (64 * BK * 2), &tmap_b, fb, n0 + i * 64, kb * BK);
+                        for (int i = 0; i < Cfg::HALF / 64; ++i) tma_load_2d_pair(sb + i * (64 * BK * 2), &tmap_b, fb, n0 + i * 64, kb * BK);
                     } else {
-                        tma_load_2d(sb, &tmap_b, fb, kb * BK, n0);
+                        tma_load_2d_pair(sb, &tmap_b, fb, kb * BK, n0);
                     }
                     st.advance<D>();
                 }
             }
+            if (prof) prof[blockIdx.x * 16 + 4] = pc0;
             if (!ok) {
-                for (int s = 0; s < D; ++s) {
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(smem_u32(&bar_full[s]), 0) && !mbar_try_wait(smem_u32(&bar_full[s]), 1)) {
-                        if (clock64() - t0 > 20000000LL) break;
-                    }
+                // gave up: let the loads already in flight land before the CTA may retire (their completions go to the
+                // even CTA's barriers, so this side can only wait out the time a load can take)
+                const long long t0 = clock64();
+                while (clock64() - t0 < 4000000LL) {
                 }
             }
         }
@@ -1089,38 +1093,50 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             PipeState st;
             bool ok = true;
             int64_t it = 0;
+            const long long t_start = prof ? clock64() : 0;
             for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
                 for (int kb = 0; kb < num_kb && ok; ++kb) {
+                    const long long tw = prof ? clock64() : 0;
                     if (!mbar_wait_cluster(smem_u32(&bar_full[st.idx]), st.phase, abortp)) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
                         ok = false;
                         break;
                     }
+                    if (prof) pc0 += clock64() - tw;
                     tc_fence_after_sync();
                     const uint32_t sa = smem_base + st.idx * Cfg::STAGE;
                     const uint32_t b_lo = smem_desc_lo(sa + Cfg::A_PART, B_LBO);
+                    if (kb == 0) {
 #pragma unroll
-                    for (int s = 0; s < MT; ++s) {
-                        const int a = acc_of(it, s);
-                        if (kb == 0) {
+                        for (int s = 0; s < MT; ++s) {
                             // the accumulator is reusable once both CTAs' epilogues have drained it
-                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[a]), par_of(it) ^ 1, abortp)) {
+                            const long long te = prof ? clock64() : 0;
+                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[acc_of(it, s)]), par_of(it) ^ 1, abortp)) {
                                 raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
                                 ok = false;
                                 break;
                             }
-                            tc_fence_after_sync();
+                            if (prof) pc2 += clock64() - te;
                         }
-                        const uint32_t a_lo = smem_desc_lo(sa + s * SUB_BYTES, A_LBO);
+                        tc_fence_after_sync();
+                    }
+                    if (!ok) break;
+                    // consecutive MMAs alternate between the accumulators and share the B slice
 #pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t bdesc = pack_desc(b_lo + ((k * B_KSTEP) >> 4), desc_hi);
+#pragma unroll
+                        for (int s = 0; s < MT; ++s) {
+                            const uint32_t a_lo = smem_desc_lo(sa + s * SUB_BYTES, A_LBO);
                             const uint64_t adesc = pack_desc(a_lo + ((k * A_KSTEP) >> 4), desc_hi);
-                            const uint64_t bdesc = pack_desc(b_lo + ((k * B_KSTEP) >> 4), desc_hi);
-                            umma_bf16_pair(tmem_base + a * BN, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                            umma_bf16_pair(tmem_base + acc_of(it, s) * BN, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
                         }
-                        if (kb == num_kb - 1) {
-                            umma_commit_pair(smem_u32(&bar_tmem_full[a]));
-                            umma_commit_pair(mapa(smem_u32(&bar_tmem_full[a]), peer));
+                    }
+                    if (kb == num_kb - 1) {
+#pragma unroll
+                        for (int s = 0; s < MT; ++s) {
+                            umma_commit_pair(smem_u32(&bar_tmem_full[acc_of(it, s)]));
+                            umma_commit_pair(mapa(smem_u32(&bar_tmem_full[acc_of(it, s)]), peer));
                         }
                     }
                     if (!ok) break;
@@ -1129,8 +1145,13 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     st.advance<D>();
                 }
             }
+            if (prof) {
+                prof[blockIdx.x * 16 + 0] = pc0;
+                prof[blockIdx.x * 16 + 2] = pc2;
+                prof[blockIdx.x * 16 + 3] = clock64() - t_start;
+            }
         }
-    } else if (warp < Cfg::RELAY_WARP) {
+    } else {
         // ------------------------------------------------------------------ epilogue (8 warps, this CTA's 128 rows)
         const int ew = warp - Cfg::FIRST_EPI_WARP;
         const int q = warp & 3;                      // TMEM lane quarter this warp may read
@@ -1193,24 +1214,6 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
         }
         if (lane == 0) bulk_wait_group0();   // all output tiles written before the CTA retires
-    } else {
-        // ------------------------------------------------------------------ odd CTA: a stage has landed here -> even CTA
-        if (lane == 0 && !leader) {
-            const uint32_t leader_rank = rank & ~1u;
-            PipeState st;
-            bool ok = true;
-            for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs) {
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait_cluster(smem_u32(&bar_full[st.idx]), st.phase, abortp)) {
-                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_cluster(mapa(smem_u32(&bar_full[st.idx]), leader_rank));
-                    st.advance<D>();
-                }
-            }
-        }
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -1457,7 +1460,8 @@ static int launch_dense_pair(void *d, const void *a, const void *b, int64_t M, i
     cfg.gridDim = dim3((unsigned)(npairs * 2));
     // stream the larger operand once: consecutive tiles share the B panel when A is the smaller matrix
     const int m_fast = (M <= N) ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, Kc, m_fast, status);
+    long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 16 * sizeof(long long)) ? g_prof : nullptr;
+    e = cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, Kc, m_fast, status, prof);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
@@ -1490,25 +1494,31 @@ static int max_resident_pairs() {
     return cached;
 }
 
-template <int A_MN, int B_MN>
-static int dense_pair_by_tile(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
-                              int64_t ldd, int32_t *status, cudaStream_t st) {
-    const int P = max_resident_pairs();
-    const int64_t t2 = cdiv64(M, 4 * BM) * cdiv64(N, 256), t1 = cdiv64(M, 2 * BM) * cdiv64(N, 256);
-    // time ~ waves x rows per tile; the 512-row tile moves fewer operand bytes per MAC, so it wins ties
-    const int64_t cost2 = cdiv64(t2, P) * 2, cost1 = cdiv64(t1, P);
-    if (cost2 <= cost1) return launch_dense_pair<2, 4, A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, t2, P, status, st);
-    return launch_dense_pair<1, 6, A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, t1, P, status, st);
+// Whether the CTA-pair kernel (512 x 256 tiles, one tile per pair at a time, epilogue not overlapped) is expected to
+// beat the single-CTA kernel (128 x 256 tiles, overlapped epilogue).  Measured on cfg-sized products: the pair kernel
+// wins by 7-15 % when its tiles fill the resident pairs evenly, and loses when a short contraction meets a ragged
+// last wave.
+static bool prefer_dense_pair(int64_t M, int64_t N, int64_t Kc, int P) {
+    if (M <= BM || N <= BM) return false;
+    const int64_t tiles = cdiv64(M, 4 * BM) * cdiv64(N, 256);
+    if (tiles * 5 < (int64_t)P * 4) return false;                       // fewer than 80 % of the pairs would work
+    if (tiles <= P) return true;
+    const double eff = (double)tiles / (double)(cdiv64(tiles, P) * P);  // share of the last wave that is used
+    return eff >= 0.95 || (Kc >= 4096 && eff >= 0.85);
 }
 
-static int g_dense_pair = 0;   // RDB_OPT_DENSE_PAIR
+static int g_dense_pair = 1;   // RDB_OPT_DENSE_PAIR
 void set_dense_pair(int v) { g_dense_pair = v; }
 
 template <int A_MN, int B_MN>
 static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
                         int64_t ldd, int d_dtype, int32_t *status, cudaStream_t st) {
-    if (d_dtype == RDB_BF16 && g_dense_pair && M > BM && N > BM)
-        return dense_pair_by_tile<A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
+    if (d_dtype == RDB_BF16 && g_dense_pair && M > BM && N > BM) {
+        const int P = max_resident_pairs();
+        if (g_dense_pair == 2 || prefer_dense_pair(M, N, Kc, P))
+            return launch_dense_pair<2, 4, A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, cdiv64(M, 4 * BM) * cdiv64(N, 256), P,
+                                                       status, st);
+    }
     if (d_dtype == RDB_BF16)
         return launch_dense<256, 4, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
     if (d_dtype == RDB_F32) return launch_dense<256, 4, A_MN, B_MN, float>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);

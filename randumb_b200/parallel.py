@@ -7,7 +7,8 @@ exchanges the path has.
   tokens and exchange the small ``z`` (all-gather) and ``g`` (all-reduce), then ``dX`` (all-gather) and
   ``dC`` (all-reduce); ``RowShardedRandumbLinear`` is the simple module form (optionally all-gathers ``y``).
 * Data parallel training: every rank holds all of ``C``; the coefficient gradients are summed with one
-  flat all-reduce per step.  (The reference's only parallelism is DDP in its GPT app:
+  flat all-reduce per step (``allreduce_coef_grads``), or per layer behind the dX product
+  (``data_parallel_backward``).  (The reference's only parallelism is DDP in its GPT app:
   modded-nanogpt/train_gpt2.py:261, 346, 441.)
 
 The collectives are plain NCCL calls on separate buffers; none of the compute kernels reads a peer's
@@ -202,6 +203,32 @@ def sharded_backward(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor
         dx = _all_gather_rows_plain(dx_loc, plan.tok_sizes, group)
     else:
         dx = dx_loc
+    return dx, dc
+
+
+# ------------------------------------------------------------------------------------------------
+# data-parallel backward with the dC all-reduce hidden behind the dX product
+# ------------------------------------------------------------------------------------------------
+def data_parallel_backward(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, row0: int = 0, group=None,
+                           average: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(dX[T, K], dC[R, K] summed over the ranks) for a replicated bf16 layer and this rank's tokens.
+
+    Same products as ``rdb_linear_bwd`` (g = dY S, dC = g^T x, dX = g C) but dC is computed first and its all-reduce
+    is started asynchronously, so the NVLink reduction runs while the tensor cores compute dX.  The returned dC is
+    safe to use on the current stream.
+    """
+    from . import kernels as K
+    R = coef.shape[0]
+    g = K.noise_product(dy, R, seed, True, row0)                                              # [T, R]
+    dc = K.gemm_dense(g, x, False, False)                                                     # [R, K]
+    work = None
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        work = dist.all_reduce(dc, op=dist.ReduceOp.SUM, group=group, async_op=True)
+    dx = K.gemm_dense(g, coef, True, False)                                                   # [T, K]
+    if work is not None:
+        work.wait()                       # makes the current stream wait for the reduction; the host does not block
+        if average:
+            dc /= dist.get_world_size(group)
     return dx, dc
 
 
