@@ -340,8 +340,8 @@ def run_ours(args, cfg):
             e1.record()
             torch.cuda.synchronize()
             fill_ms = e0.elapsed_time(e1) / 20
-            kernel = ("dense_gemm_kernel (y = z S^T and g = dY S, average over both launches) on S hashed once per call into a "
-                      "bf16 scratch by noise_kernel")
+            kernel = ("dense_pair_kernel (cta_group::2; dense_gemm_kernel where the tiles would not fill the CTA pairs): y = z S^T and "
+                      "g = dY S, average over both launches, on S hashed once per call into a bf16 scratch by noise_bf16x8_kernel")
         else:
             avg_ms, fill_ms, kernel = fused_ms, None, fused["kernel"]
         achieved = flops_launch / (avg_ms * 1e-3) / 1e12

@@ -1,6 +1,8 @@
 """Small, self-terminating cases of the generated-operand kernels for profilers and for the per-role counters.
 
     python -m randumb_b200.profile_case                 # 2 launches each of the y-shaped and g-shaped product (for ncu -k regex:noise_)
+    python -m randumb_b200.profile_case --staged        # 2 launches each of the noise fill and the two plain products on the staged S
+                                                        # (for ncu -k "regex:dense_|noise_bf16")
     python -m randumb_b200.profile_case --roles         # per-role cycle counters of every kernel variant at the headline shapes
     python -m randumb_b200.profile_case --tokens 2048 --out 16384 --dc 1024
 
@@ -26,6 +28,18 @@ def run_small(tokens: int, out: int, dc: int, seed: int = 42) -> None:
     for _ in range(2):
         K.gemm_noise(z, out, seed, False, impl=K.IMPL_UMMA)       # y = z S^T
         K.gemm_noise(dy, dc, seed, True, impl=K.IMPL_UMMA)        # g = dY S
+    torch.cuda.synchronize()
+    K.check_status()
+
+
+def run_staged(tokens: int, out: int, dc: int, seed: int = 42) -> None:
+    """The path the linear entry points take for 1024 tokens or more: S hashed once into bf16, then the plain products."""
+    z = torch.randn(tokens, dc, device="cuda").bfloat16()
+    dy = torch.randn(tokens, out, device="cuda").bfloat16()
+    assert K.linear_stages_noise(tokens, 8, out, dc, torch.bfloat16, K.PATH_FACTORED)
+    for _ in range(2):
+        K.noise_product(z, out, seed, False)       # noise fill + y = z S^T
+        K.noise_product(dy, dc, seed, True)        # noise fill + g = dY S
     torch.cuda.synchronize()
     K.check_status()
 
@@ -70,12 +84,15 @@ def run_roles(tokens: int, out: int, dc: int, seed: int = 42) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--roles", action="store_true")
+    ap.add_argument("--staged", action="store_true")
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--out", type=int, default=16384)
     ap.add_argument("--dc", type=int, default=1024)
     a = ap.parse_args()
     if a.roles:
         run_roles(a.tokens or 8192, a.out, a.dc)
+    elif a.staged:
+        run_staged(a.tokens or 4096, a.out, a.dc)
     else:
         run_small(a.tokens or 2048, a.out, a.dc)
     print("ok")
