@@ -412,8 +412,9 @@ def launches_per_step(workload, staged):
 # DRAM bytes per launch of the generated-operand kernels: dram__bytes_read.sum + dram__bytes_write.sum of the
 # ncu capture summarised under profiles/ (2048-token case, 70.7 MB), scaled by tokens to the 8192-token launch.
 NOISE_GEMM_DRAM_BYTES = {"gemm": 2.83e8, "sharded": None}
-# the same for the plain tensor-core product reading the staged S (filled in from the capture under profiles/)
-DENSE_ON_NOISE_DRAM_BYTES = {"gemm": None, "sharded": None}
+# the same for the plain tensor-core products reading the staged S: 4096-token capture under profiles/, token-proportional
+# terms doubled, average of the y-shaped (2.10e8) and g-shaped (3.11e8) launch
+DENSE_ON_NOISE_DRAM_BYTES = {"gemm": 2.6e8, "sharded": None}
 
 
 def run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier):

@@ -188,21 +188,34 @@ def sharded_forward(x: torch.Tensor, coef: torch.Tensor, seed: int, plan: Sharde
 def sharded_backward(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan,
                      group=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """(dX[T, K], dC[R, K]) from this rank's slice dY[:, row_lo:row_hi]: the partial g = dY_r S_r is summed over
-    ranks (T x R, small), then dX and dC are computed for this rank's tokens and exchanged."""
+    ranks (T x R, small) with every rank keeping only its token slice (reduce-scatter), then dX and dC are computed
+    for this rank's tokens and exchanged; the dX all-gather runs while the tensor cores compute dC."""
     from . import kernels as K
     R = coef.shape[0]
     g = K.noise_product(dy_local.contiguous(), R, seed, True, plan.row_lo)                       # partial [T, R]
-    if plan.world > 1:
-        dist.all_reduce(g, group=group)
-    g_loc = g[plan.tok_lo:plan.tok_hi].contiguous()
+    # the tensor forms of reduce-scatter / all-gather need equal shards and NCCL
+    equal = (all(n == plan.tok_sizes[0] for n in plan.tok_sizes) and plan.world > 1 and dist.get_backend(group) == "nccl")
+    if plan.world > 1 and equal:
+        g_loc = g.new_empty((plan.tok_sizes[0], R))
+        dist.reduce_scatter_tensor(g_loc, g, group=group)
+    else:
+        if plan.world > 1:
+            dist.all_reduce(g, group=group)
+        g_loc = g[plan.tok_lo:plan.tok_hi].contiguous()
     x_loc = x[plan.tok_lo:plan.tok_hi].contiguous()
     dx_loc = K.gemm_dense(g_loc, coef, True, False)                                           # [t_r, K]
-    dc = K.gemm_dense(g_loc, x_loc, False, False)                                             # partial [R, K]
-    if plan.world > 1:
+    if plan.world == 1:
+        return dx_loc, K.gemm_dense(g_loc, x_loc, False, False)
+    if equal:
+        dx = dx_loc.new_empty((sum(plan.tok_sizes), dx_loc.shape[1]))
+        work_dx = dist.all_gather_into_tensor(dx, dx_loc, group=group, async_op=True)
+        dc = K.gemm_dense(g_loc, x_loc, False, False)                                         # partial [R, K]
+        dist.all_reduce(dc, group=group)
+        work_dx.wait()
+    else:
+        dc = K.gemm_dense(g_loc, x_loc, False, False)
         dist.all_reduce(dc, group=group)
         dx = _all_gather_rows_plain(dx_loc, plan.tok_sizes, group)
-    else:
-        dx = dx_loc
     return dx, dc
 
 
