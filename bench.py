@@ -174,7 +174,7 @@ def run_reference(args, cfg):
         "impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.workload, cfg, args.gpus),
+        "config": workload_config(args.workload, cfg, args.gpus, args.replicate_grads),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -186,10 +186,12 @@ def metric_name(workload):
     return "fused PRNG-matmul fwd+bwd GB/s" if workload == "gemv" else "fused PRNG-matmul fwd+bwd TFLOP/s"
 
 
-def workload_config(name, cfg, gpus):
-    par = {"gemm": f"dp{gpus} (tokens per rank fixed, dC all-reduce)" if gpus > 1 else "single GPU",
-           "sharded": f"output rows split over {gpus} ranks (zero weight traffic); z all-gather, g all-reduce, dX all-gather, "
-                      f"dC all-reduce" if gpus > 1 else "single GPU",
+def workload_config(name, cfg, gpus, replicate_grads=False):
+    sharded = (f"output rows split over {gpus} ranks (zero weight traffic); y stays row-sharded; z all-gather, " +
+               ("g reduce-scatter, dX all-gather, dC all-reduce (gradients replicated on every rank)" if replicate_grads else
+                "g all-reduce; dX stays token-sharded and dC input-feature-sharded (every gradient element on one rank)"))
+    par = {"gemm": f"dp{gpus} (tokens per rank fixed, dC all-reduce behind the dX product)" if gpus > 1 else "single GPU",
+           "sharded": sharded if gpus > 1 else "single GPU",
            "gemv": "replicas only"}[name]
     return {"workload": f"{name}: x[{cfg['T']}x{cfg['K']}] {cfg['dtype']}, virtual W[{cfg['N']}x{cfg['K']}], d_c={cfg['R']}, "
                         f"seed={cfg['seed']}, fwd + dX + dC",
@@ -235,7 +237,7 @@ def run_ours(args, cfg):
         if plan is not None and world > 1:
             # rows split over ranks: z all-gather, g all-reduce, dX all-gather, dC all-reduce
             y = rb.parallel.sharded_forward(x, C, seed, plan)
-            dx, dc = rb.parallel.sharded_backward(dy, x, C, seed, plan)
+            dx, dc = rb.parallel.sharded_backward(dy, x, C, seed, plan, replicate=args.replicate_grads)
             return y, dx, dc
         y = K.linear_fwd(x, C, seed, n_local, row0)
         if world > 1:
@@ -389,7 +391,7 @@ def run_ours(args, cfg):
             "metric": metric_name(args.workload), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if args.workload == "sharded" else "weak", "vs_baseline": None,
-            "dtype": cfg["dtype"], "data": "synthetic", "config": workload_config(args.workload, cfg, world),
+            "dtype": cfg["dtype"], "data": "synthetic", "config": workload_config(args.workload, cfg, world, args.replicate_grads),
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(args.workload, staged) * args.steps,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
@@ -497,6 +499,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--replicate-grads", action="store_true",
+                    help="sharded workload: all-gather dX and all-reduce dC so that every rank holds both in full")
     ap.add_argument("--no-graph", action="store_true", help="gemv workload: launch the four kernels eagerly in the timed region")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]

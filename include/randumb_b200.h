@@ -91,11 +91,16 @@ const char *rdb_strerror(int code);
  *                           hashes every noise element once instead of once per 512-token tile; below that, and
  *                           whenever S would exceed 1 GiB, the kernels regenerate S tile by tile in shared memory
  *                        1: always regenerate tile by tile (no S in memory)   2: always stage when it fits
+ *   RDB_OPT_RESERVE_SMS  0 (default) .. 64: SMs the persistent plain-product kernels leave without a CTA.  Their CTAs
+ *                        take a whole SM each for the length of the launch, so a collective enqueued beside them
+ *                        (an NCCL all-reduce of the previous product's result) only runs at the same time if some SMs
+ *                        are left free; set around the launch that should overlap, then restore.
  * Returns the previous value, or RDB_ERR_UNSUPPORTED for an unknown key.
  */
 #define RDB_OPT_NOISE_TILE 1
 #define RDB_OPT_DENSE_PAIR 2
 #define RDB_OPT_STAGE_NOISE 3
+#define RDB_OPT_RESERVE_SMS 4
 int rdb_set_option(int key, int value);
 
 /*

@@ -19,6 +19,7 @@ IMPL_AUTO, IMPL_SIMT, IMPL_UMMA = 0, 1, 2
 OPT_NOISE_TILE = 1
 OPT_DENSE_PAIR = 2
 OPT_STAGE_NOISE = 3
+OPT_RESERVE_SMS = 4
 STATUS_NAMES = {0: "ok", 1: "producer wait expired", 2: "mma wait expired", 3: "epilogue wait expired",
                 4: "generator wait expired"}
 

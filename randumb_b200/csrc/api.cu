@@ -8,6 +8,7 @@ namespace rdb {
 static int g_noise_tile = 0;    // RDB_OPT_NOISE_TILE
 static int g_dense_pair = 1;    // RDB_OPT_DENSE_PAIR
 static int g_stage_noise = 0;   // RDB_OPT_STAGE_NOISE
+static int g_reserve_sms = 0;   // RDB_OPT_RESERVE_SMS
 
 // FLOP-count rule: factored costs 2TR(K+N) per result, the W path 2NRK + 2TNK.
 static int choose_path(int path, int64_t T, int64_t K, int64_t N, int64_t R) {
@@ -117,6 +118,11 @@ extern "C" int rdb_set_option(int key, int value) {
         case RDB_OPT_STAGE_NOISE:
             prev = g_stage_noise;
             g_stage_noise = (value >= 0 && value <= 2) ? value : 0;
+            return prev;
+        case RDB_OPT_RESERVE_SMS:
+            prev = g_reserve_sms;
+            g_reserve_sms = (value >= 0 && value <= 64) ? value : 0;
+            set_reserve_sms(g_reserve_sms);
             return prev;
         default: return RDB_ERR_UNSUPPORTED;
     }

@@ -39,6 +39,7 @@ int simt_gemm(void *d, int d_dtype, int64_t d_rs, int64_t d_cs, const void *a, i
 // ---- implemented in umma_gemm.cu -------------------------------------------------------------
 void set_noise_cfg(int v);
 void set_dense_pair(int v);
+void set_reserve_sms(int v);
 void set_profile_buffer(void *p, size_t bytes);
 bool umma_shape_ok_noise(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, const void *a, const void *d);
 int umma_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, Sq5Lin lin,

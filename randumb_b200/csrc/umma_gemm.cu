@@ -1278,6 +1278,10 @@ static int make_tmap(CUtensorMap *m, const void *base, int64_t inner, int64_t ou
     return RDB_OK;
 }
 
+// RDB_OPT_RESERVE_SMS: SMs the persistent plain-product kernels leave idle, for a collective that should run beside them
+static int g_reserve_sms = 0;
+void set_reserve_sms(int v) { g_reserve_sms = v < 0 ? 0 : v; }
+
 static int sm_count() {
     int dev = 0, n = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 148;
@@ -1424,7 +1428,9 @@ static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
     if (e != cudaSuccess) return (int)e;
     const int64_t tiles = cdiv64(M, BM) * cdiv64(N, BN);
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    int ctas = sm_count() - g_reserve_sms;
+    if (ctas < 1) ctas = 1;
+    const int grid = (int)(tiles < ctas ? tiles : ctas);
     // tiles that run at the same time share the panel of the larger operand, which is then streamed from memory once
     const int m_fast = (M <= N) ? 1 : 0;
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, tb, reinterpret_cast<OutT *>(d), ldd, M, N, Kc, m_fast, status);
@@ -1456,7 +1462,9 @@ static int launch_dense_pair(void *d, const void *a, const void *b, int64_t M, i
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const int64_t npairs = tiles < max_pairs ? tiles : max_pairs;
+    int pairs = max_pairs - (g_reserve_sms + 1) / 2;
+    if (pairs < 1) pairs = 1;
+    const int64_t npairs = tiles < pairs ? tiles : pairs;
     cfg.gridDim = dim3((unsigned)(npairs * 2));
     // stream the larger operand once: consecutive tiles share the B panel when A is the smaller matrix
     const int m_fast = (M <= N) ? 1 : 0;

@@ -22,6 +22,11 @@ from typing import Callable, List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
+from . import _lib
+
+# SMs left without a CTA of the persistent product kernels while a collective runs beside them
+OVERLAP_SMS = 16
+
 
 # ------------------------------------------------------------------------------------------------
 # partition arithmetic
@@ -186,13 +191,27 @@ def sharded_forward(x: torch.Tensor, coef: torch.Tensor, seed: int, plan: Sharde
 
 
 def sharded_backward(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan,
-                     group=None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """(dX[T, K], dC[R, K]) from this rank's slice dY[:, row_lo:row_hi]: the partial g = dY_r S_r is summed over
-    ranks (T x R, small) with every rank keeping only its token slice (reduce-scatter), then dX and dC are computed
-    for this rank's tokens and exchanged; the dX all-gather runs while the tensor cores compute dC."""
+                     group=None, replicate: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Gradients from this rank's slice dY[:, row_lo:row_hi].
+
+    ``replicate=True``: (dX[T, K], dC[R, K]) complete on every rank.  The partial g = dY_r S_r is summed over ranks
+    (T x R, small) with every rank keeping only its token slice (reduce-scatter), then dX and dC are computed for this
+    rank's tokens and exchanged; the dX all-gather runs while the tensor cores compute dC.
+
+    ``replicate=False``: every gradient element is computed on exactly one rank and stays there -- returns
+    (dX[tok_lo:tok_hi, :], dC[:, k_lo:k_hi]) with ``k_lo, k_hi = shard_range(K, world, rank)``.  g is all-reduced
+    (the only exchange: T x R); dC is split by input features, which needs the full g but no reduction.
+    """
     from . import kernels as K
     R = coef.shape[0]
     g = K.noise_product(dy_local.contiguous(), R, seed, True, plan.row_lo)                       # partial [T, R]
+    if not replicate:
+        if plan.world > 1:
+            dist.all_reduce(g, group=group)
+        k_lo, k_hi = shard_range(x.shape[1], plan.world, plan.rank)
+        dx_loc = K.gemm_dense(g[plan.tok_lo:plan.tok_hi].contiguous(), coef, True, False)     # [t_r, K]
+        dc_cols = K.gemm_dense(g, x[:, k_lo:k_hi].contiguous(), False, False)                 # [R, k_r]
+        return dx_loc, dc_cols
     # the tensor forms of reduce-scatter / all-gather need equal shards and NCCL
     equal = (all(n == plan.tok_sizes[0] for n in plan.tok_sizes) and plan.world > 1 and dist.get_backend(group) == "nccl")
     if plan.world > 1 and equal:
@@ -209,7 +228,11 @@ def sharded_backward(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor
     if equal:
         dx = dx_loc.new_empty((sum(plan.tok_sizes), dx_loc.shape[1]))
         work_dx = dist.all_gather_into_tensor(dx, dx_loc, group=group, async_op=True)
-        dc = K.gemm_dense(g_loc, x_loc, False, False)                                         # partial [R, K]
+        prev = K.set_option(_lib.OPT_RESERVE_SMS, OVERLAP_SMS)
+        try:
+            dc = K.gemm_dense(g_loc, x_loc, False, False)                                     # partial [R, K]
+        finally:
+            K.set_option(_lib.OPT_RESERVE_SMS, prev)
         dist.all_reduce(dc, group=group)
         work_dx.wait()
     else:
@@ -237,7 +260,13 @@ def data_parallel_backward(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor
     work = None
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         work = dist.all_reduce(dc, op=dist.ReduceOp.SUM, group=group, async_op=True)
-    dx = K.gemm_dense(g, coef, True, False)                                                   # [T, K]
+    # the product kernels are persistent, one CTA per SM: leave a few SMs to the collective or it waits for them to retire
+    prev = K.set_option(_lib.OPT_RESERVE_SMS, OVERLAP_SMS) if work is not None else None
+    try:
+        dx = K.gemm_dense(g, coef, True, False)                                               # [T, K]
+    finally:
+        if prev is not None:
+            K.set_option(_lib.OPT_RESERVE_SMS, prev)
     if work is not None:
         work.wait()                       # makes the current stream wait for the reduction; the host does not block
         if average:

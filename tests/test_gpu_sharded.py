@@ -36,13 +36,17 @@ def _worker(rank, world, port, tmp):
         plan = rb.parallel.ShardedLayerPlan(T, N, world, rank)
         y_r = rb.parallel.sharded_forward(x, C, seed, plan)
         dx, dc = rb.parallel.sharded_backward(dy[:, plan.row_lo:plan.row_hi].contiguous(), x, C, seed, plan)
+        # nothing replicated: token slice of dX, input-feature slice of dC
+        lean_dx, lean_dc = rb.parallel.sharded_backward(dy[:, plan.row_lo:plan.row_hi].contiguous(), x, C, seed, plan,
+                                                        replicate=False)
         # data parallel: this rank's half of the tokens, dC all-reduced behind the dX product
         lo, hi = rank * (T // world), (rank + 1) * (T // world)
         dp_dx, dp_dc = rb.parallel.data_parallel_backward(dy[lo:hi].contiguous(), x[lo:hi].contiguous(), C, seed)
         torch.cuda.synchronize()
         K.check_status()
         torch.save({"y": y_r.cpu(), "dx": dx.cpu(), "dc": dc.cpu(), "rows": (plan.row_lo, plan.row_hi),
-                    "dp_dx": dp_dx.cpu(), "dp_dc": dp_dc.cpu(), "tok": (lo, hi)}, os.path.join(tmp, f"r{rank}.pt"))
+                    "dp_dx": dp_dx.cpu(), "dp_dc": dp_dc.cpu(), "tok": (lo, hi),
+                    "lean_dx": lean_dx.cpu(), "lean_dc": lean_dc.cpu()}, os.path.join(tmp, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -64,6 +68,9 @@ def test_two_rank_sharding_matches_single_gpu(tmp_path):
     for p in parts:                       # dX and dC are complete (and identical) on every rank
         assert O.close(p["dx"], dx_ref, 2e-2) and O.close(p["dc"], dc_ref, 2e-2)
     assert torch.equal(parts[0]["dx"], parts[1]["dx"]) and torch.equal(parts[0]["dc"], parts[1]["dc"])
+    # unreplicated gradients: the ranks' pieces tile dX by tokens and dC by input features
+    assert O.close(torch.cat([p["lean_dx"] for p in parts], dim=0), dx_ref, 2e-2)
+    assert O.close(torch.cat([p["lean_dc"] for p in parts], dim=1), dc_ref, 2e-2)
     # data parallel: token halves of dX, the same summed dC on both ranks
     for p in parts:
         lo, hi = p["tok"]
