@@ -5,6 +5,9 @@
  *   S[o,k] = squirrel5(uint32(198491317*o + k), seed)  in [-1,1]   (N x R, regenerated on the fly)
  *   C      = trainable coefficient matrix                          (R x K, row-major)
  * and   y = x W^T,   dX = dY W,   dC = S^T (dY^T X).
+ * W is never formed on the tensor-core path.  S is regenerated from the seed in every call: tile by tile in shared
+ * memory, or (1024 tokens or more) once per call as a transient bf16 copy in the caller's workspace -- see
+ * RDB_OPT_STAGE_NOISE.  Nothing of it survives the call.
  *
  * Conventions for every entry point
  *   - all pointers are DEVICE pointers owned by the caller (row-major, densely packed unless a
@@ -139,7 +142,9 @@ int rdb_noise_1d(float *out, int64_t n, int64_t idx0, uint32_t seed, void *strea
 
 /*
  * Bytes of scratch the linear entry points need for the given problem (op: 0 = forward,
- * 1 = backward).  The workspace must be 256-byte aligned.
+ * 1 = backward).  The workspace must be 256-byte aligned.  bf16 tensor-core path: T*R*2 bytes for z or g, plus
+ * N*R*2 bytes when the noise operand is staged (rdb_linear_stages_noise); the size depends on the option values
+ * in force, so query it after setting them.
  */
 size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path,
                                   int impl);
