@@ -128,6 +128,31 @@ def test_mnist_shaped_mlp_step(rb):
     assert O.close(l2.weight_coef.grad, C2.grad, 1e-5), O.rel_fro(l2.weight_coef.grad, C2.grad)
 
 
+def test_gpt2_shaped_mlp_block_step(rb):
+    """GPT-2-small MLP block (768 -> 3072 -> 768, d_c = 128, bf16, 2048 tokens, seeds from stepgen): forward, dX and both
+    coefficient gradients against explicit-noise autograd in float32 on the CPU (bf16-rounded inputs and coefficients)."""
+    g = torch.Generator().manual_seed(77)
+    seeds = rb.stepgen(13, 7)
+    c_fc = rb.RandumbLinear(768, 3072, 128, next(seeds), device="cuda", dtype=torch.bfloat16)
+    c_proj = rb.RandumbLinear(3072, 768, 128, next(seeds), device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(2, 1024, 768, generator=g).bfloat16()
+    dout = torch.randn(2, 1024, 768, generator=g).bfloat16()
+    xg = x.cuda().requires_grad_(True)
+    out = c_proj(F.gelu(c_fc(xg), approximate="tanh"))
+    out.backward(dout.cuda())
+    C1 = c_fc.weight_coef.detach().float().cpu().requires_grad_(True)
+    C2 = c_proj.weight_coef.detach().float().cpu().requires_grad_(True)
+    W1 = torch.from_numpy(O.noise_f32(3072, 128, 13)) @ C1
+    W2 = torch.from_numpy(O.noise_f32(768, 128, 20)) @ C2
+    xr = x.float().requires_grad_(True)
+    ref = F.linear(F.gelu(F.linear(xr, W1), approximate="tanh"), W2)
+    ref.backward(dout.float())
+    assert O.close(out.reshape(-1, 768), ref.reshape(-1, 768), 2e-2), O.rel_fro(out.reshape(-1, 768), ref.reshape(-1, 768))
+    assert O.close(xg.grad.reshape(-1, 768), xr.grad.reshape(-1, 768), 3e-2), O.rel_fro(xg.grad.reshape(-1, 768), xr.grad.reshape(-1, 768))
+    # two bf16 layers and a nonlinearity deep: the gradients carry both layers' rounding
+    assert O.rel_fro(c_fc.weight_coef.grad, C1.grad) < 3e-2 and O.rel_fro(c_proj.weight_coef.grad, C2.grad) < 3e-2
+
+
 def test_bf16_module_and_state_roundtrip(rb):
     m = rb.RandumbLinear(256, 384, 64, seed=11, bias=True, device="cuda", dtype=torch.bfloat16)
     x = torch.randn(4, 100, 256, device="cuda", dtype=torch.bfloat16)
