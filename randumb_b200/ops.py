@@ -226,6 +226,38 @@ def _embed_backward(ctx, grad):
 embed_fwd.register_autograd(_embed_backward, setup_context=_embed_setup)
 
 
+def rt_mm(mat1: torch.Tensor, coefs: torch.Tensor, size: List[int], strides: List[int], seed: int,
+          scale_bias: Optional[torch.Tensor] = None, fused_bias: bool = False) -> torch.Tensor:
+    """``mat1[L, P] @ RT[P, Q]`` for a RandumbTensor in the 1-D coefficient form, same call as the reference's
+    experimental ``rt_mm`` / ``rt_mm_grouped`` (src/rten_cpp/RandumbTensor.py:634-645, 758-769).
+
+    Every element of RT costs ``M`` hashes, so regenerating RT tiles inside a product would repeat that work once
+    per row block of ``mat1``; RT is materialised once (``rten::materialize_fwd``, differentiable in ``coefs`` and
+    ``scale_bias``) and multiplied by the library's own product kernels (differentiable in ``mat1``).
+    """
+    P, Q = size
+    assert mat1.dim() == 2 and mat1.size(1) == P, f"mm shape mismatch, received mat1 shape {tuple(mat1.size())} and rt shape {size}"
+    rt = materialize_fwd(coefs, list(size), list(strides), seed, scale_bias, fused_bias)
+    return _DenseMM.apply(mat1, rt.to(mat1.dtype))
+
+
+class _DenseMM(torch.autograd.Function):
+    """a[L, P] @ b[P, Q] on the library's product kernels (tensor cores for bf16, CUDA cores for float32)."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return K.gemm_dense(a.contiguous(), b.contiguous(), True, False)
+
+    @staticmethod
+    def backward(ctx, grad):
+        a, b = ctx.saved_tensors
+        grad = grad.contiguous()
+        da = K.gemm_dense(grad, b.contiguous(), True, True) if ctx.needs_input_grad[0] else None      # grad @ b^T
+        db = K.gemm_dense(a.contiguous(), grad, False, False) if ctx.needs_input_grad[1] else None   # a^T @ grad
+        return da, db
+
+
 # C++-namespace twins of the reference (rten.cpp:36-39); registered from Python onto the same C ABI.
 @custom_op("rten_cpp::sq5_gen_2d", mutates_args=())
 def sq5_gen_2d(M: int, N: int, seed: int) -> torch.Tensor:

@@ -135,6 +135,20 @@ def test_silly_embedding_module_step(rb):
     assert O.close(emb.weight_coef.grad, torch.from_numpy(want_g), 1e-5)
 
 
+def test_rt_mm_against_reference_kernel_output(rb, golden):
+    """mat1 @ RT: the reference's fused rt_mm_grouped kernel output, and gradients against the oracle."""
+    coef = torch.from_numpy(golden["matfwd_coef"]).cuda().requires_grad_(True)
+    mat1 = torch.from_numpy(golden["rtmm_mat1"]).cuda().requires_grad_(True)
+    out = rb.ops.rt_mm(mat1, coef, [40, 36], [36, 1], 9)
+    np.testing.assert_allclose(out.detach().cpu().numpy(), golden["rtmm_33x40_40x36_seed9"], atol=5e-5)
+    dout = torch.randn(33, 36, generator=torch.Generator().manual_seed(2))
+    out.backward(dout.cuda())
+    W = O.materialize_fwd(golden["matfwd_coef"], 40, 36, 36, 1, 9)
+    np.testing.assert_allclose(mat1.grad.cpu().numpy(), dout.double().numpy() @ W.T, atol=5e-5)
+    dW = golden["rtmm_mat1"].astype("float64").T @ dout.double().numpy()
+    np.testing.assert_allclose(coef.grad.cpu().numpy(), O.materialize_bwd(dW.astype("float32"), 24, 9), rtol=1e-4, atol=1e-4)
+
+
 def test_opcheck_vector_form_ops(rb):
     coef = torch.randn(12, device="cuda", requires_grad=True)
     idx = torch.randint(0, 30, (6,), device="cuda")
