@@ -80,6 +80,34 @@ __global__ void __launch_bounds__(256) noise_bf16x8_kernel(uint4 *__restrict__ o
     }
 }
 
+// Same for rows whose length is a multiple of 1024: one warp hashes a 1024-element row segment, each lane four groups of
+// 8 elements 256 apart (every store instruction of the warp writes 512 contiguous bytes), so the row/column split costs
+// one division per 32 hashes.
+__global__ void __launch_bounds__(256) noise_bf16_seg_kernel(uint4 *__restrict__ out, uint32_t total_segs, uint32_t segs_per_row,
+                                                             uint32_t ld_groups, Sq5Lin lin) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total_segs; w += warps) {
+        const uint32_t r = w / segs_per_row;
+        const uint32_t sg = w - r * segs_per_row;
+        const uint32_t b0 = lin.base + r * lin.sn + ((sg << 10) + (lane << 3)) * lin.sk;
+        uint4 *dst = out + (size_t)r * ld_groups + (sg << 7) + lane;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t b = b0 + (uint32_t)(c * 256) * lin.sk;
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float f0 = sq5_to_float(sq5_tail(b + (uint32_t)(2 * j) * lin.sk));
+                const float f1 = sq5_to_float(sq5_tail(b + (uint32_t)(2 * j + 1) * lin.sk));
+                __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                p[j] = *reinterpret_cast<uint32_t *>(&h);
+            }
+            dst[c * 32] = make_uint4(p[0], p[1], p[2], p[3]);
+        }
+    }
+}
+
 __global__ void noise_1d_kernel(float *__restrict__ out, int64_t n, uint32_t idx0, uint32_t seed) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         out[i] = sq5_to_float(sq5_tail((idx0 + (uint32_t)i) * SQ5_N1 + seed));
@@ -100,6 +128,14 @@ static int launch_noise(void *out, int64_t rows, int64_t cols, int64_t ld, int64
     Sq5Lin lin = sq5_lin_rows(seed, (uint32_t)row0, (uint32_t)col0);
     if (MODE == 2 && (cols & 7) == 0 && (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
         rows * (cols >> 3) < (1LL << 31)) {
+        if ((cols & 1023) == 0) {
+            const uint32_t total_segs = (uint32_t)(rows * (cols >> 10));
+            const int64_t want = cdiv64(total_segs, 8);        // eight warps per block, one segment per warp and pass
+            const int grid = (int)(want < 148 * 8 ? (want < 1 ? 1 : want) : 148 * 8);
+            noise_bf16_seg_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<uint4 *>(out), total_segs, (uint32_t)(cols >> 10),
+                                                       (uint32_t)(ld >> 3), lin);
+            return launch_status();
+        }
         const uint32_t total = (uint32_t)(rows * (cols >> 3));
         const int64_t want = cdiv64(total, 256 * 4);           // about four groups (32 elements) per thread
         const int grid = (int)(want < 148 * 8 ? (want < 1 ? 1 : want) : 148 * 8);
