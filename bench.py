@@ -174,7 +174,7 @@ def run_reference(args, cfg):
         "impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.workload, cfg, args.gpus, args.replicate_grads),
+        "config": workload_config(args.workload, cfg, args.gpus, args.replicate_grads, args.gather_output),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -186,8 +186,9 @@ def metric_name(workload):
     return "fused PRNG-matmul fwd+bwd GB/s" if workload == "gemv" else "fused PRNG-matmul fwd+bwd TFLOP/s"
 
 
-def workload_config(name, cfg, gpus, replicate_grads=False):
-    sharded = (f"output rows split over {gpus} ranks (zero weight traffic); y stays row-sharded; z all-gather, " +
+def workload_config(name, cfg, gpus, replicate_grads=False, gather_output=False):
+    sharded = (f"output rows split over {gpus} ranks (zero weight traffic); " +
+               ("y all-gathered beside the backward products; " if gather_output else "y stays row-sharded; ") + "z all-gather, " +
                ("g reduce-scatter, dX all-gather, dC all-reduce (gradients replicated on every rank)" if replicate_grads else
                 "g all-reduce; dX stays token-sharded and dC input-feature-sharded (every gradient element on one rank)"))
     par = {"gemm": f"dp{gpus} (tokens per rank fixed, dC all-reduce behind the dX product)" if gpus > 1 else "single GPU",
@@ -232,12 +233,20 @@ def run_ours(args, cfg):
     x = x_host.to(dev)
     dy = torch.randn(T, n_local, generator=g).to(dt).to(dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.workload == "gemv" else None
+    y_all = (torch.empty((world * T, n_local), dtype=dt, device=dev)
+             if args.workload == "sharded" and args.gather_output and world > 1 else None)
 
     def step():
         if plan is not None and world > 1:
             # rows split over ranks: z all-gather, g all-reduce, dX all-gather, dC all-reduce
             y = rb.parallel.sharded_forward(x, C, seed, plan)
+            work = None
+            if args.gather_output:
+                # every rank receives all column blocks of y (rank-major [G, T, N/G]); runs beside the backward products
+                work = dist.all_gather_into_tensor(y_all, y, async_op=True)
             dx, dc = rb.parallel.sharded_backward(dy, x, C, seed, plan, replicate=args.replicate_grads)
+            if work is not None:
+                work.wait()
             return y, dx, dc
         y = K.linear_fwd(x, C, seed, n_local, row0)
         if world > 1:
@@ -283,13 +292,18 @@ def run_ours(args, cfg):
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall0 = time.time()
+    step_ms = None
     if flush is None:
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]   # one event per step boundary
         ev0.record()
-        for _ in range(args.steps):
+        marks[0].record()
+        for i in range(args.steps):
             step()
+            marks[i + 1].record()
         ev1.record()
         barrier()
         elapsed_ms = ev0.elapsed_time(ev1)
+        step_ms = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps))
     else:
         elapsed_ms = 0.0
         for _ in range(args.steps):
@@ -391,10 +405,14 @@ def run_ours(args, cfg):
             "metric": metric_name(args.workload), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if args.workload == "sharded" else "weak", "vs_baseline": None,
-            "dtype": cfg["dtype"], "data": "synthetic", "config": workload_config(args.workload, cfg, world, args.replicate_grads),
+            "dtype": cfg["dtype"], "data": "synthetic", "config": workload_config(args.workload, cfg, world, args.replicate_grads, args.gather_output),
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(args.workload, staged) * args.steps,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
+        if step_ms:
+            # this rank's per-step device times: median and the reference's 20 / 80 % quantiles (benchmark.py:50)
+            q = lambda f: step_ms[min(len(step_ms) - 1, int(f * len(step_ms)))]
+            line["ms_per_step_quantiles"] = {"p20": q(0.2), "median": q(0.5), "p80": q(0.8)}
         if eager_ms is not None:
             line["config"]["launch"] = "the step's four kernels replayed as one CUDA graph"
             line["eager_ms_per_step"] = eager_ms
@@ -515,6 +533,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather-output", action="store_true",
+                    help="sharded workload: all-gather y (537 MB at the full size) so that every rank holds all of it")
     ap.add_argument("--replicate-grads", action="store_true",
                     help="sharded workload: all-gather dX and all-reduce dC so that every rank holds both in full")
     ap.add_argument("--no-graph", action="store_true", help="gemv workload: launch the four kernels eagerly in the timed region")
