@@ -6,16 +6,16 @@ reference package ``rten_cpp``):
 
 * ``ops``      torch.library operators (``rten::rlinear_fwd`` ..., ``rten::materialize_fwd`` ...)
 * ``RandumbTensor`` / ``CreateRandumbTensor``   storage-less tensor subclass + differentiable constructor
-* ``RandumbLinear`` / ``SillyLinear`` / ``SillyEmbedding`` / ``stepgen`` / ``listgen``   modules
+* ``RandumbLinear`` / ``SillyLinear`` / ``SillyEmbedding`` / ``SillyConv2d`` / ``stepgen`` / ``listgen``   modules
 * ``parallel`` row sharding over GPUs and the dC all-reduce
 * ``kernels``  tensor-level wrappers over the C ABI (``include/randumb_b200.h``)
 
 Importing the package does not need a GPU; running any kernel does, and there is no CPU fallback.
 """
 from . import kernels, ops, parallel  # noqa: F401
-from .layers import RandumbLinear, SillyEmbedding, SillyLinear, listgen, stepgen  # noqa: F401
+from .layers import RandumbLinear, SillyConv2d, SillyEmbedding, SillyLinear, listgen, stepgen  # noqa: F401
 from .ops import rlinear  # noqa: F401
 from .tensor import CreateRandumbTensor, RandumbTensor  # noqa: F401
 
-__all__ = ["kernels", "ops", "parallel", "RandumbLinear", "SillyLinear", "SillyEmbedding", "listgen", "stepgen", "rlinear",
+__all__ = ["kernels", "ops", "parallel", "RandumbLinear", "SillyLinear", "SillyEmbedding", "SillyConv2d", "listgen", "stepgen", "rlinear",
            "CreateRandumbTensor", "RandumbTensor"]

@@ -1,6 +1,6 @@
 // bf16 tensor-core (tcgen05 / TMEM / TMA) kernels of the pseudorandom-weight layer.
 //
-// Two persistent, warp-specialised kernels, one CTA per SM:
+// Persistent, warp-specialised kernels, one CTA per SM:
 //
 //  noise_gemm_kernel   D[M,N] = A[M,Kc] * G^T  where the B operand G is never read from memory:
 //                      generator warps hash (seed, row, k) with 32-bit integer ALU ops in
@@ -9,11 +9,14 @@
 //                      expects, while a TMA warp stages the A tiles beside it.  One generated
 //                      [BN x 64] stage is consumed by MT token sub-tiles (MT*128 rows of A), so
 //                      every hash is amortised over MT*128 tokens.
-//                      Serves y = z S^T (forward) and g = dY S (backward, transposed walk).
+//  noise_pair_kernel   the same product on CTA pairs (cta_group::2 MMAs, 512 tokens x 256 generated rows).
+//                      Both serve y = z S^T and g = dY S (transposed walk) when S is regenerated per tile.
 //
-//  dense_gemm_kernel   D[M,N] = op(A) op(B)^T with both operands staged by TMA (K-major or
-//                      MN-major), double-buffered TMEM accumulators so the epilogue of one tile
-//                      overlaps the main loop of the next.  Serves z = x C^T, dX = g C, dC = g^T x.
+//  dense_pair_kernel   D[M,N] = op(A) op(B)^T with both operands staged by TMA (K-major or MN-major) on CTA
+//                      pairs: 512 x 256 tiles, each CTA stages its own rows of A and its own half of B.
+//  dense_gemm_kernel   the same on single CTAs: 128 x 256 tiles, double-buffered TMEM accumulators so the
+//                      epilogue of one tile overlaps the main loop of the next.
+//                      They serve z = x C^T, dX = g C, dC = g^T x, and y / g on a staged copy of S.
 //
 // The reference has no tensor-core path for any of this: its fused attempt runs tl.dot in IEEE
 // float32 (src/rten_cpp/RandumbTensor.py:539, 725) and the production path materialises W and

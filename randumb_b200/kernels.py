@@ -275,7 +275,14 @@ def materialize_fwd(coef: torch.Tensor, size, strides, seed: int, scale_bias: Op
     elif len(size) == 2:
         P, Q, sP, sQ = size[0], size[1], strides[0], strides[1]
     else:
-        raise RuntimeError("materialize_fwd handles 1-D and 2-D outputs")
+        # more dimensions: only the contiguous layout, which is the flat 1-D case (element n uses noise row n)
+        expect, acc = [], 1
+        for d in reversed(size):
+            expect.append(acc)
+            acc *= d
+        if strides != list(reversed(expect)):
+            raise RuntimeError("materialize_fwd handles 1-D and 2-D outputs, and contiguous outputs of more dimensions")
+        P, Q, sP, sQ = 1, acc, 0, 1
     out = torch.empty(size, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         rc = _lib.lib().rdb_materialize_fwd(_ptr(out), _ptr(coef), coef.numel(), P, Q, sP, sQ,

@@ -225,3 +225,52 @@ class SillyEmbedding(RandumbModuleMixin, nn.Module):
 
     def extra_repr(self) -> str:
         return f"{self.num_embeddings}, {self.embedding_dim}, int_dim={self.int_dim}, seeds={self.seed}"
+
+
+class SillyConv2d(RandumbModuleMixin, nn.Conv2d):
+    """``nn.Conv2d`` whose weight ``[out, in/groups, kh, kw]`` and bias are RandumbTensors in the 1-D coefficient
+    form (reference: SillyLayers.py:230-297); the convolution itself is PyTorch's, on the weight materialised for the
+    call by ``rten::materialize_fwd`` and dropped afterwards."""
+    num_seeds = 2
+
+    def __init__(self, in_channels: int, out_channels: int, int_dim: Union[list, Generator], seed: Union[list, Generator],
+                 kernel_size, stride=1, padding=0, dilation=1, groups: int = 1, bias: bool = True, rt_bias: bool = False,
+                 padding_mode: str = "zeros", device=None, dtype=None) -> None:
+        self.int_dim = [next(int_dim) for _ in range(self.num_seeds)] if isinstance(int_dim, GeneratorType) else list(int_dim)
+        self.seed = [next(seed) for _ in range(self.num_seeds)] if isinstance(seed, GeneratorType) else list(seed)
+        self.rt_bias = rt_bias
+        super().__init__(in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias, padding_mode,
+                         device=device, dtype=dtype)
+
+    def reset_parameters(self) -> None:
+        # nn.Conv2d.__init__ has created dense parameters: keep their shapes, replace them by coefficient vectors
+        w = self.weight
+        fan_in = w.shape[1] * w.shape[2] * w.shape[3]
+        self.weight_coef = nn.Parameter(torch.empty(self.int_dim[0], dtype=w.dtype, device=w.device))
+        wshape = tuple(w.shape)
+        del self.weight
+        self.register_buffer("weight", CreateRandumbTensor(self.weight_coef, self.seed[0], wshape, fused_bias=self.rt_bias),
+                             persistent=False)
+        if self.bias is not None:
+            b = self.bias
+            self.bias_coef = nn.Parameter(torch.empty(self.int_dim[1], dtype=b.dtype, device=b.device))
+            bshape = tuple(b.shape)
+            del self.bias
+            self.register_buffer("bias", CreateRandumbTensor(self.bias_coef, self.seed[1], bshape, fused_bias=self.rt_bias),
+                                 persistent=False)
+        out_std = kaiming_out_std(fan_in)
+        gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed[0] & 0x7FFFFFFFFFFFFFFF)
+        with torch.no_grad():
+            if self.rt_bias:
+                self.weight_coef.zero_()
+                if self.bias is not None:
+                    self.bias_coef.zero_()
+            else:
+                self.weight_coef.uniform_(-1, 1, generator=gen).mul_(math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[0]))
+                if self.bias is not None:
+                    self.bias_coef.uniform_(-1, 1, generator=gen).mul_(math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[1]))
+        if self.rt_bias:
+            self.init_rt_scale_bias(math.sqrt(3.0) * out_std)
+
+    def extra_repr(self) -> str:
+        return super().extra_repr() + f", int_dim={self.int_dim}, seeds={self.seed}"

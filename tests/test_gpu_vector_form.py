@@ -149,6 +149,27 @@ def test_rt_mm_against_reference_kernel_output(rb, golden):
     np.testing.assert_allclose(coef.grad.cpu().numpy(), O.materialize_bwd(dW.astype("float32"), 24, 9), rtol=1e-4, atol=1e-4)
 
 
+def test_silly_conv2d_step(rb):
+    """Convolution with a storage-less weight [out, in, kh, kw] and bias: forward and every gradient against the same
+    convolution with the oracle's dense weight."""
+    torch.manual_seed(0)
+    m = rb.SillyConv2d(3, 8, [16, 4], [5, 6], 3, padding=1).cuda()
+    x = torch.randn(2, 3, 10, 10, device="cuda", requires_grad=True)
+    y = m(x)
+    Wc = m.weight_coef.detach().double().cpu().requires_grad_(True)
+    bc = m.bias_coef.detach().double().cpu().requires_grad_(True)
+    S_w = torch.from_numpy(O.noise_f32(8 * 3 * 3 * 3, 16, 5)).double()
+    S_b = torch.from_numpy(O.noise_f32(8, 4, 6)).double()
+    xr = x.detach().double().cpu().requires_grad_(True)
+    ref = F.conv2d(xr, (S_w @ Wc).reshape(8, 3, 3, 3), S_b @ bc, padding=1)
+    assert O.close(y.reshape(2, -1), ref.reshape(2, -1), 1e-4)
+    dout = torch.randn(2, 8, 10, 10, generator=torch.Generator().manual_seed(3))
+    y.backward(dout.cuda())
+    ref.backward(dout.double())
+    assert O.close(m.weight_coef.grad, Wc.grad, 1e-4) and O.close(m.bias_coef.grad, bc.grad, 1e-4)
+    assert O.close(x.grad.reshape(2, -1), xr.grad.reshape(2, -1), 1e-4)
+
+
 def test_opcheck_vector_form_ops(rb):
     coef = torch.randn(12, device="cuda", requires_grad=True)
     idx = torch.randint(0, 30, (6,), device="cuda")
