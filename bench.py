@@ -525,13 +525,168 @@ def run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier):
                     "(dX and dC), loss.item() back to the host"}
 
 
+# --------------------------------------------------------------------------------------------------
+# GPT-2-small-shaped workload: only the pseudorandom-weight layers of the 12 blocks (c_fc 768 -> 3072, c_proj 3072 -> 768,
+# d_c = 128, seeds 13, 20, 27, ...), 8 x 1024 tokens per GPU, data parallel with one flat all-reduce of the 24 dC
+# --------------------------------------------------------------------------------------------------
+GPT2 = dict(T=8192, d=768, mlp=3072, R=128, blocks=12, seed0=13, seed_step=7, coef_std=(3 * 0.02 ** 2 / 128) ** 0.5)
+
+
+def run_gpt2mlp(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py measures the CUDA kernels; no GPU is visible (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
+        dist.init_process_group("nccl", device_id=dev)
+    from randumb_b200 import kernels as K
+    import randumb_b200 as rb
+    c = GPT2
+    T, d, mlp, R, nb = c["T"], c["d"], c["mlp"], c["R"], c["blocks"]
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(1004 + rank)
+    x1_host = torch.randn(T, d, generator=g).to(dt).pin_memory()
+    x1, x2 = x1_host.to(dev), torch.randn(T, mlp, generator=g).to(dt).to(dev)
+    dy1, dy2 = torch.randn(T, mlp, generator=g).to(dt).to(dev), torch.randn(T, d, generator=g).to(dt).to(dev)
+    gc = torch.Generator().manual_seed(7)
+    layers = []                                   # (x, dy, coef, seed, out_features)
+    for b in range(nb):
+        s_fc, s_proj = c["seed0"] + c["seed_step"] * (2 * b), c["seed0"] + c["seed_step"] * (2 * b + 1)
+        layers.append((x1, dy1, (torch.randn(R, d, generator=gc) * c["coef_std"]).to(dt).to(dev), s_fc, mlp))
+        layers.append((x2, dy2, (torch.randn(R, mlp, generator=gc) * c["coef_std"]).to(dt).to(dev), s_proj, d))
+    flops_step = sum(algorithmic_flops(T, L[0].shape[1], L[4], R) for L in layers)
+
+    def step():
+        dcs = []
+        for x, dy, C, seed, n_out in layers:
+            K.linear_fwd(x, C, seed, n_out)
+        for x, dy, C, seed, n_out in reversed(layers):
+            dx, dc = K.linear_bwd(dy, x, C, seed)
+            dcs.append(dc.reshape(-1))
+        flat = torch.cat(dcs)                     # 5.9 M coefficients, 11.8 MB bf16
+        if world > 1:
+            dist.all_reduce(flat)
+        return flat
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    t_wall1 = time.time()
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    K.check_status()
+    tmax = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(tmax.item())
+    value = world * flops_step * args.steps / (elapsed_ms * 1e-3) / 1e12
+
+    # end to end: the MLP halves of the 12 blocks as modules (residual stream, tanh-GELU), x from pinned host memory,
+    # autograd backward, the loss value read back
+    seeds = rb.stepgen(c["seed0"], c["seed_step"])
+    blocks = [(rb.RandumbLinear(d, mlp, R, next(seeds), device=dev, dtype=dt), rb.RandumbLinear(mlp, d, R, next(seeds), device=dev, dtype=dt))
+              for _ in range(nb)]
+    params = [m.weight_coef for pair in blocks for m in pair]
+    xin = torch.empty_like(x1)
+
+    def e2e_step():
+        xin.copy_(x1_host, non_blocking=True)
+        h = xin
+        for fc, proj in blocks:
+            h = h + proj(torch.nn.functional.gelu(fc(h), approximate="tanh"))
+        loss = _MeanSquare.apply(h)
+        loss.backward()
+        if world > 1:
+            rb.parallel.allreduce_coef_grads(params)
+        val = float(loss.item())
+        for p_ in params:
+            p_.grad = None
+        return val
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    n_e2e = max(3, min(args.steps, 10))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    barrier()
+    t2 = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t2.item()) / n_e2e
+    e2e = {"value": world * flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": x1_host.numel() * 2,
+           "d2h_bytes_per_step": 4, "steps": n_e2e, "ms_per_step": e2e_ms,
+           "what": "pinned-host x -> device, 12 x (RandumbLinear, tanh-GELU, RandumbLinear, residual), mean-square loss, autograd "
+                   "backward, flat dC all-reduce, loss.item(); TFLOP/s counts the pseudorandom-weight layers only"}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        dt_cpu, fl_cpu = 0.0, 0.0
+        for (Kin, n_out, seed) in ((d, mlp, c["seed0"]), (mlp, d, c["seed0"] + c["seed_step"])):
+            cc = dict(T=T, K=Kin, N=n_out, R=R, seed=seed, dtype="bf16", coef_std=c["coef_std"])
+            cpu_reference_step(cc, T)
+            t_, _ = cpu_reference_step(cc, T)
+            dt_cpu += t_
+            fl_cpu += algorithmic_flops(T, Kin, n_out, R)
+        cpu_baseline = {"value": fl_cpu / dt_cpu / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                        "sample": f"one block's two layers (of 12 blocks) at all {T} tokens in {dt_cpu:.2f} s: explicit S from the C "
+                                  "oracle, W = S @ C, F.linear, autograd; float32"}
+    if rank == 0:
+        peaks = measured_peaks()
+        per_gpu = value / world
+        line = {
+            "metric": metric_name("gpt2mlp"), "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"gpt2mlp: the 24 pseudorandom-weight layers of GPT-2 small's 12 MLPs (768 -> 3072 -> 768, d_c=128, "
+                                   f"seeds {c['seed0']}+{c['seed_step']}i), {T} tokens per GPU, fwd + dX + dC of every layer",
+                       "parallelism": f"dp{world} (one flat all-reduce of the 24 dC, 11.8 MB)" if world > 1 else "single GPU",
+                       "l2": "one step streams about 1.5 GB of activations, outputs and gradients (24 layers), far more than the 126 MB L2 "
+                             "(no explicit flush)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": 24 * 7 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "whole step (24 layers x 7 launches; contractions of 128 and 768-3072)",
+                         "achieved": per_gpu, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": per_gpu / peaks["tensor"],
+                         "peak_source": f"{peaks['src']} burst bf16", "traffic": None},
+            "cpu_baseline": cpu_baseline,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemm", choices=list(WORKLOADS))
+    ap.add_argument("--workload", default="gemm", choices=list(WORKLOADS) + ["gpt2mlp"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather-output", action="store_true",
                     help="sharded workload: all-gather y (537 MB at the full size) so that every rank holds all of it")
@@ -539,7 +694,10 @@ def main():
                     help="sharded workload: all-gather dX and all-reduce dC so that every rank holds both in full")
     ap.add_argument("--no-graph", action="store_true", help="gemv workload: launch the four kernels eagerly in the timed region")
     args = ap.parse_args()
-    cfg = WORKLOADS[args.workload]
+    if args.workload == "gpt2mlp" and args.impl == "ours":
+        run_gpt2mlp(args)
+        return
+    cfg = WORKLOADS["gemm" if args.workload == "gpt2mlp" else args.workload]
     if args.impl == "reference":
         run_reference(args, cfg)
     else:
