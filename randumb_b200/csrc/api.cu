@@ -48,7 +48,7 @@ struct WsLayout {
 
 // Workspace segments (each 1024-byte aligned):
 //   UMMA factored  fwd: z bf16[T,R], then S bf16[N,R] when the noise operand is staged
-//                  bwd: g bf16[T,R], then S bf16[N,R] when staged
+//                  bwd: g bf16[T,R], then S bf16[N,R] when staged, then float32 [split,R,K] when dC is computed split-K
 //   SIMT factored  fwd: z f32[T,R]           bwd: g f32[T,R]
 //   SIMT W path    fwd: W f32[N,K]           bwd: W f32[N,K], dW f32[N,K]
 static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, int path, int impl) {
@@ -58,6 +58,17 @@ static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, in
         if (impl == RDB_IMPL_UMMA) {
             seg[0] = (size_t)T * R * 2;
             if (stage_noise(T, N, R)) seg[1] = (size_t)N * R * 2;
+            // float32 partial products of the products with few output tiles and a long contraction, computed split-K:
+            // forward z = x C^T (contraction K); backward g = dY S (contraction N, staged S only) and dC = g^T x (contraction T)
+            if (op == 0) {
+                const int split = dense_split_k_slices(T, R, K);
+                if (split > 1) seg[2] = (size_t)split * T * R * 4;
+            } else {
+                const int sg = stage_noise(T, N, R) ? dense_split_k_slices(T, R, N) : 1;
+                const int sc = dense_split_k_slices(R, K, T);
+                const size_t a = sg > 1 ? (size_t)sg * T * R * 4 : 0, b = sc > 1 ? (size_t)sc * R * K * 4 : 0;
+                seg[2] = a > b ? a : b;        // used one after the other
+            }
         } else {
             seg[0] = (size_t)T * R * 4;
         }
@@ -227,7 +238,12 @@ extern "C" int rdb_linear_fwd(void *y, const void *x, const void *coef, void *wo
     if (p == RDB_PATH_FACTORED) {
         if (im == RDB_IMPL_UMMA) {
             void *z = ws + w.off[0];
-            rc = umma_gemm_dense(z, x, coef, T, R, K, K, K, R, RDB_BF16, 1, 1, status, st);
+            const int sz = dense_split_k_slices(T, R, K);
+            if (sz > 1)
+                rc = umma_gemm_dense_split_k(z, x, coef, reinterpret_cast<float *>(ws + w.off[2]), sz, T, R, K, K, K, RDB_BF16, 1, 1,
+                                             status, st);
+            else
+                rc = umma_gemm_dense(z, x, coef, T, R, K, K, K, R, RDB_BF16, 1, 1, status, st);
             if (rc) return rc;
             if (stage_noise(T, N, R)) {
                 void *S = ws + w.off[1];
@@ -285,7 +301,12 @@ extern "C" int rdb_linear_bwd(void *dx, void *dc, const void *dy, const void *x,
                 void *S = ws + w.off[1];
                 rc = rdb_noise(S, RDB_BF16, N, R, R, row0, 0, seed, stream);
                 if (rc) return rc;
-                rc = umma_gemm_dense(g, dy, S, T, R, N, N, R, R, RDB_BF16, 1, 0, status, st);    // S read as an MN-major operand
+                const int sg = dense_split_k_slices(T, R, N);
+                if (sg > 1)
+                    rc = umma_gemm_dense_split_k(g, dy, S, reinterpret_cast<float *>(ws + w.off[2]), sg, T, R, N, N, R, RDB_BF16, 1, 0,
+                                                 status, st);
+                else
+                    rc = umma_gemm_dense(g, dy, S, T, R, N, N, R, R, RDB_BF16, 1, 0, status, st);    // S read as an MN-major operand
             } else {
                 rc = umma_gemm_noise(g, dy, T, R, N, N, R, cols, status, st);
             }
@@ -295,7 +316,12 @@ extern "C" int rdb_linear_bwd(void *dx, void *dc, const void *dy, const void *x,
                 if (rc) return rc;
             }
             if (dc) {
-                rc = umma_gemm_dense(dc, g, x, R, K, T, R, K, K, RDB_BF16, 0, 0, status, st);
+                const int split = dense_split_k_slices(R, K, T);
+                if (split > 1)
+                    rc = umma_gemm_dense_split_k(dc, g, x, reinterpret_cast<float *>(ws + w.off[2]), split, R, K, T, R, K, RDB_BF16, 0,
+                                                 0, status, st);
+                else
+                    rc = umma_gemm_dense(dc, g, x, R, K, T, R, K, K, RDB_BF16, 0, 0, status, st);
                 if (rc) return rc;
             }
             return RDB_OK;

@@ -46,6 +46,10 @@ int umma_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, in
                     int32_t *status, cudaStream_t stream);
 bool umma_shape_ok_dense(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int d_dtype,
                          int a_kmajor, int b_kmajor, const void *a, const void *b, const void *d);
+int dense_split_k_slices(int64_t M, int64_t N, int64_t Kc);
+int umma_gemm_dense_split_k(void *d, const void *a, const void *b, float *partials, int split, int64_t M, int64_t N,
+                            int64_t Kc, int64_t lda, int64_t ldb, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status,
+                            cudaStream_t stream);
 int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda,
                     int64_t ldb, int64_t ldd, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status,
                     cudaStream_t stream);

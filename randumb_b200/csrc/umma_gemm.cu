@@ -784,8 +784,11 @@ struct DenseCfg {
     static constexpr int A_STAGE = SUB_BYTES;
     static constexpr int B_STAGE = BN * BK * 2;
     static constexpr int STAGE = A_STAGE + B_STAGE;
-    static constexpr int THREADS = 6 * 32;
-    static constexpr int SMEM_DYN = STAGES * STAGE + 1024;
+    static constexpr int EPI_WARPS = 8;                               // two per TMEM lane quarter, half of the columns each
+    static constexpr int THREADS = (2 + EPI_WARPS) * 32;
+    static constexpr int OUT_STAGING = EPI_WARPS * 4096;              // per epilogue warp: one [32 rows x 64 columns] bf16 box
+    static constexpr int SMEM_DYN = STAGES * STAGE + OUT_STAGING + 1024;
+    static_assert(SMEM_DYN <= 232448 - 512, "shared memory");
     static_assert(2 * BN <= TMEM_COLS, "two accumulator stages must fit TMEM");
     static_assert(BN % 64 == 0 && BN <= 256, "BN");
 };
@@ -793,7 +796,10 @@ struct DenseCfg {
 template <int BN, int STAGES, int A_MN, int B_MN, typename OutT>
 __global__ void __launch_bounds__(DenseCfg<BN, STAGES>::THREADS, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  OutT *__restrict__ d, int64_t ldd, int64_t M, int64_t N, int64_t Kc, int m_fast, int32_t *status) {
+                  const __grid_constant__ CUtensorMap tmap_d, OutT *__restrict__ d, int64_t ldd, int64_t M, int64_t N, int64_t Kc, int m_fast, int split, int64_t slice_stride,
+                  int32_t *status) {
+    // split > 1: the contraction is cut into `split` slices of whole k-blocks; work item = (slice, tile) and slice s
+    // writes its partial product at d + s * slice_stride (the caller sums the slices in order)
     using Cfg = DenseCfg<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tmem_full[2], bar_tmem_empty[2];
@@ -807,7 +813,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tmem_full[s]), 1); mbar_init(smem_u32(&bar_tmem_empty[s]), 128); }
+        for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tmem_full[s]), 1); mbar_init(smem_u32(&bar_tmem_empty[s]), Cfg::EPI_WARPS); }
         abort_flag = 0;
         fence_mbar_init();
     }
@@ -823,8 +829,13 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
     const int64_t tiles_n = (N + BN - 1) / BN;
     const int64_t tiles_m = (M + BM - 1) / BM;
-    const int64_t total_tiles = tiles_m * tiles_n;
-    const int num_kb = (int)((Kc + BK - 1) / BK);
+    const int64_t tiles_mn = tiles_m * tiles_n;
+    const int64_t total_tiles = tiles_mn * split;
+    const int all_kb = (int)((Kc + BK - 1) / BK);
+    const int kb_per = (all_kb + split - 1) / split;
+    // k-block range of a work item
+    auto kb_lo = [&](int64_t w) { return (int)(w / tiles_mn) * kb_per; };
+    auto kb_hi = [&](int64_t w) { const int hi = ((int)(w / tiles_mn) + 1) * kb_per; return hi < all_kb ? hi : all_kb; };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -832,10 +843,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             prefetch_tmap(&tmap_b);
             PipeState st;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int64_t w = blockIdx.x; w < total_tiles && ok; w += gridDim.x) {
+                const int64_t tile = w % tiles_mn;
                 const int32_t m0 = (int32_t)((m_fast ? tile % tiles_m : tile / tiles_n) * BM);
                 const int32_t n0 = (int32_t)((m_fast ? tile / tiles_m : tile % tiles_n) * BN);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb_lo(w); kb < kb_hi(w); ++kb) {
                     if (!mbar_wait(smem_u32(&bar_empty[st.idx]), st.phase ^ 1, abortp)) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
                         ok = false;
@@ -881,14 +893,15 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             PipeState st;
             uint32_t acc = 0, acc_phase = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int64_t w = blockIdx.x; w < total_tiles && ok; w += gridDim.x) {
+                const int kb0 = kb_lo(w), kb1 = kb_hi(w);
                 if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1, abortp)) {
                     raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
                     break;
                 }
                 tc_fence_after_sync();
                 const uint32_t tacc = tmem_base + acc * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&bar_full[st.idx]), st.phase, abortp)) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
                         ok = false;
@@ -903,7 +916,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t adesc = pack_desc(a_lo + ((k * A_KSTEP) >> 4), desc_hi);
                         const uint64_t bdesc = pack_desc(b_lo + ((k * B_KSTEP) >> 4), desc_hi);
-                        umma_bf16(tacc, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_bf16(tacc, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&bar_empty[st.idx]));
                     st.advance<STAGES>();
@@ -913,9 +926,15 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
         }
     } else {
-        const int q = warp & 3;
+        const int q = warp & 3;                       // TMEM lane quarter this warp may read
+        constexpr int CPW = BN / (Cfg::EPI_WARPS / 4);  // accumulator columns per warp
+        const int cbase = ((warp - 2) >> 2) * CPW;
+        constexpr bool TMA_OUT = (sizeof(OutT) == 2);   // bf16: swizzled staging + TMA tile stores; float32: direct stores
+        const uint32_t stag = smem_base + STAGES * Cfg::STAGE + (uint32_t)(warp - 2) * 4096u;
         uint32_t acc = 0, acc_phase = 0;
-        for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        for (int64_t w = blockIdx.x; w < total_tiles; w += gridDim.x) {
+            const int64_t tile = w % tiles_mn;
+            OutT *dw = d + (w / tiles_mn) * slice_stride;
             const int64_t m0 = (m_fast ? tile % tiles_m : tile / tiles_n) * BM;
             const int64_t n0 = (m_fast ? tile / tiles_m : tile % tiles_n) * BN;
             if (!mbar_wait_warp<false>(smem_u32(&bar_tmem_full[acc]), acc_phase, abortp)) {
@@ -923,20 +942,59 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 break;
             }
             tc_fence_after_sync();
-            const int64_t row = m0 + q * 32 + lane;
+            const int64_t row_w = m0 + q * 32;
+            if (TMA_OUT) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
-                tmem_ld_wait();
-                const int64_t col = n0 + c0;
-                const int ncols = (int)((N - col) < 32 ? (N - col) : 32);
-                if (row < M && ncols > 0) store_row32<OutT>(d + row * ldd + col, r, ncols);
+                for (int c0 = cbase; c0 < cbase + CPW; c0 += 64) {
+                    uint32_t r0[32], r1[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0);
+                    tmem_ld_32x32(taddr, r0);
+                    tmem_ld_32x32(taddr + 32, r1);
+                    // the previous store of this warp must have finished reading the staging box
+                    if (lane == 0) bulk_wait_group_read0();
+                    __syncwarp();
+                    tmem_ld_wait();
+                    const uint32_t rowaddr = stag + (uint32_t)lane * 128u;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t pk[4], pl[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 2 * e]), __uint_as_float(r0[j * 8 + 2 * e + 1]));
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r1[j * 8 + 2 * e]), __uint_as_float(r1[j * 8 + 2 * e + 1]));
+                            pk[e] = *reinterpret_cast<uint32_t *>(&h0);
+                            pl[e] = *reinterpret_cast<uint32_t *>(&h1);
+                        }
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)((j ^ (lane & 7)) << 4)),
+                                     "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)(((4 + j) ^ (lane & 7)) << 4)),
+                                     "r"(pl[0]), "r"(pl[1]), "r"(pl[2]), "r"(pl[3]) : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row_w < M && n0 + c0 < N) {
+                        tma_store_2d(&tmap_d, stag, (int32_t)(n0 + c0), (int32_t)row_w);
+                        bulk_commit_group();
+                    }
+                }
+            } else {
+                const int64_t row = row_w + lane;
+#pragma unroll 1
+                for (int c0 = cbase; c0 < cbase + CPW; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                    tmem_ld_wait();
+                    const int64_t col = n0 + c0;
+                    const int ncols = (int)((N - col) < 32 ? (N - col) : 32);
+                    if (row < M && ncols > 0) store_row32<OutT>(dw + row * ldd + col, r, ncols);
+                }
             }
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        if (TMA_OUT && lane == 0) bulk_wait_group0();   // all output tiles written before the CTA retires
     }
 
     tc_fence_before_sync();
@@ -1420,23 +1478,29 @@ bool umma_shape_ok_dense(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t 
 
 template <int BN, int STAGES, int A_MN, int B_MN, typename OutT>
 static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
-                        int64_t ldd, int32_t *status, cudaStream_t st) {
+                        int64_t ldd, int32_t *status, cudaStream_t st, int split = 1, int64_t slice_stride = 0) {
     using Cfg = DenseCfg<BN, STAGES>;
     CUtensorMap ta, tb;
     int rc = A_MN ? make_tmap(&ta, a, M, Kc, lda, 64, BK) : make_tmap(&ta, a, Kc, M, lda, BK, BM);
     if (rc) return rc;
     rc = B_MN ? make_tmap(&tb, b, N, Kc, ldb, 64, BK) : make_tmap(&tb, b, Kc, N, ldb, BK, BN);
     if (rc) return rc;
+    CUtensorMap td = ta;                       // float32 outputs are stored directly: the map is not used
+    if (sizeof(OutT) == 2) {
+        rc = make_tmap(&td, d, N, M, ldd, 64, 32);   // output tiles of 32 rows x 64 columns
+        if (rc) return rc;
+    }
     auto kern = dense_gemm_kernel<BN, STAGES, A_MN, B_MN, OutT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
     if (e != cudaSuccess) return (int)e;
-    const int64_t tiles = cdiv64(M, BM) * cdiv64(N, BN);
+    const int64_t tiles = cdiv64(M, BM) * cdiv64(N, BN) * split;
     int ctas = sm_count() - g_reserve_sms;
     if (ctas < 1) ctas = 1;
     const int grid = (int)(tiles < ctas ? tiles : ctas);
     // tiles that run at the same time share the panel of the larger operand, which is then streamed from memory once
     const int m_fast = (M <= N) ? 1 : 0;
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, tb, reinterpret_cast<OutT *>(d), ldd, M, N, Kc, m_fast, status);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, tb, td, reinterpret_cast<OutT *>(d), ldd, M, N, Kc, m_fast, split, slice_stride,
+                                                    status);
     return launch_status();
 }
 
@@ -1530,10 +1594,76 @@ static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_
             return launch_dense_pair<2, 4, A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, cdiv64(M, 4 * BM) * cdiv64(N, 256), P,
                                                        status, st);
     }
+    // at most 128 output columns (a coefficient dimension of 128 or less): 128-column tiles, half the MMA and B traffic
+    if (d_dtype == RDB_BF16 && N <= 128)
+        return launch_dense<128, 6, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
     if (d_dtype == RDB_BF16)
         return launch_dense<256, 4, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
     if (d_dtype == RDB_F32) return launch_dense<256, 4, A_MN, B_MN, float>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
     return RDB_ERR_DTYPE;
+}
+
+// ---- split-K: few output tiles, long contraction (dC = g^T x of a layer with a small coefficient matrix) ---------------
+// Slices the contraction into `split` pieces that run as independent work items writing float32 partial products
+// [split, M, N] into `partials`; split_k_reduce_kernel then sums the slices in a fixed order.
+int dense_split_k_slices(int64_t M, int64_t N, int64_t Kc) {
+    const int64_t tiles = cdiv64(M, BM) * cdiv64(N, N <= 128 ? 128 : 256);
+    const int64_t kbs = cdiv64(Kc, BK);
+    const int sms = sm_count();
+    if (tiles * 2 > sms || kbs < 16) return 1;
+    int64_t s = sms / tiles;                 // one wave of work items
+    if (s > kbs / 4) s = kbs / 4;            // at least four k-blocks per slice
+    if (s > 16) s = 16;                      // every slice writes and re-reads a float32 copy of the output
+    if (s < 2) return 1;
+    const int64_t kb_per = cdiv64(kbs, s);   // the kernel gives every slice this many k-blocks ...
+    return (int)cdiv64(kbs, kb_per);         // ... so this many slices are non-empty
+}
+
+template <typename OutT>
+__global__ void split_k_reduce_kernel(OutT *__restrict__ out, const float *__restrict__ partials, int64_t n4, int split,
+                                      int64_t slice_stride4) {
+    const float4 *p = reinterpret_cast<const float4 *>(partials);
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        float4 acc = p[i];
+        for (int s = 1; s < split; ++s) {
+            const float4 v = p[i + s * slice_stride4];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (sizeof(OutT) == 4) {
+            reinterpret_cast<float4 *>(out)[i] = acc;
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+            uint2 v;
+            v.x = *reinterpret_cast<uint32_t *>(&lo);
+            v.y = *reinterpret_cast<uint32_t *>(&hi);
+            reinterpret_cast<uint2 *>(out)[i] = v;
+        }
+    }
+}
+
+// d must be densely packed (ldd == N) and N a multiple of 8; partials: split * M * N floats
+int umma_gemm_dense_split_k(void *d, const void *a, const void *b, float *partials, int split, int64_t M, int64_t N, int64_t Kc,
+                            int64_t lda, int64_t ldb, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status, cudaStream_t st) {
+    if (M == 0 || N == 0) return RDB_OK;
+    const int64_t stride = M * N;
+    int rc;
+    if (N <= 128) {
+        if (a_kmajor && b_kmajor) rc = launch_dense<128, 6, 0, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
+        else if (a_kmajor) rc = launch_dense<128, 6, 0, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
+        else if (b_kmajor) rc = launch_dense<128, 6, 1, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
+        else rc = launch_dense<128, 6, 1, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
+    } else if (a_kmajor && b_kmajor) rc = launch_dense<256, 4, 0, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
+    else if (a_kmajor) rc = launch_dense<256, 4, 0, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
+    else if (b_kmajor) rc = launch_dense<256, 4, 1, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
+    else rc = launch_dense<256, 4, 1, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
+    if (rc) return rc;
+    const int64_t n4 = stride / 4;
+    const int grid = (int)(cdiv64(n4, 256) < 148 * 8 ? cdiv64(n4, 256) : 148 * 8);
+    if (d_dtype == RDB_BF16)
+        split_k_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16 *>(d), partials, n4, split, stride / 4);
+    else
+        split_k_reduce_kernel<float><<<grid, 256, 0, st>>>(reinterpret_cast<float *>(d), partials, n4, split, stride / 4);
+    return launch_status();
 }
 
 int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
