@@ -797,7 +797,7 @@ template <int BN, int STAGES, int A_MN, int B_MN, typename OutT>
 __global__ void __launch_bounds__(DenseCfg<BN, STAGES>::THREADS, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_d, OutT *__restrict__ d, int64_t ldd, int64_t M, int64_t N, int64_t Kc, int m_fast, int split, int64_t slice_stride,
-                  int32_t *status) {
+                  int f32_tma, int32_t *status) {
     // split > 1: the contraction is cut into `split` slices of whole k-blocks; work item = (slice, tile) and slice s
     // writes its partial product at d + s * slice_stride (the caller sums the slices in order)
     using Cfg = DenseCfg<BN, STAGES>;
@@ -977,6 +977,29 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         bulk_commit_group();
                     }
                 }
+            } else if (f32_tma) {
+                // float32 partial products, M a multiple of 128: [32 rows x 32 columns] boxes (128-byte rows) through the same
+                // staging; the output is addressed as one [split * M, N] matrix
+                const int64_t row_g = (w / tiles_mn) * M + row_w;
+#pragma unroll 1
+                for (int c0 = cbase; c0 < cbase + CPW; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                    if (lane == 0) bulk_wait_group_read0();
+                    __syncwarp();
+                    tmem_ld_wait();
+                    const uint32_t rowaddr = stag + (uint32_t)lane * 128u;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)((j ^ (lane & 7)) << 4)),
+                                     "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && n0 + c0 < N) {
+                        tma_store_2d(&tmap_d, stag, (int32_t)(n0 + c0), (int32_t)row_g);
+                        bulk_commit_group();
+                    }
+                }
             } else {
                 const int64_t row = row_w + lane;
 #pragma unroll 1
@@ -994,7 +1017,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
-        if (TMA_OUT && lane == 0) bulk_wait_group0();   // all output tiles written before the CTA retires
+        if ((TMA_OUT || f32_tma) && lane == 0) bulk_wait_group0();   // all output tiles written before the CTA retires
     }
 
     tc_fence_before_sync();
@@ -1319,15 +1342,15 @@ static void ensure_context() {
 
 // bf16 matrix with `inner` contiguous elements per row, `outer` rows, row pitch ld elements.
 static int make_tmap(CUtensorMap *m, const void *base, int64_t inner, int64_t outer, int64_t ld, uint32_t box_inner,
-                     uint32_t box_outer) {
+                     uint32_t box_outer, bool f32 = false) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return RDB_ERR_DRIVER;
     ensure_context();
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+    CUresult r = fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -1485,10 +1508,15 @@ static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_
     if (rc) return rc;
     rc = B_MN ? make_tmap(&tb, b, N, Kc, ldb, 64, BK) : make_tmap(&tb, b, Kc, N, ldb, BK, BN);
     if (rc) return rc;
-    CUtensorMap td = ta;                       // float32 outputs are stored directly: the map is not used
+    CUtensorMap td = ta;                       // float32 outputs with ragged row tiles are stored directly: the map is not used
+    int f32_tma = 0;
     if (sizeof(OutT) == 2) {
         rc = make_tmap(&td, d, N, M, ldd, 64, 32);   // output tiles of 32 rows x 64 columns
         if (rc) return rc;
+    } else if ((M % BM) == 0 && (ldd % 4) == 0 && slice_stride == (split > 1 ? M * ldd : slice_stride)) {
+        rc = make_tmap(&td, d, N, (int64_t)split * M, ldd, 32, 32, true);   // float32: 32 x 32 boxes over [split * M, N]
+        if (rc) return rc;
+        f32_tma = 1;
     }
     auto kern = dense_gemm_kernel<BN, STAGES, A_MN, B_MN, OutT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
@@ -1500,7 +1528,7 @@ static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_
     // tiles that run at the same time share the panel of the larger operand, which is then streamed from memory once
     const int m_fast = (M <= N) ? 1 : 0;
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, tb, td, reinterpret_cast<OutT *>(d), ldd, M, N, Kc, m_fast, split, slice_stride,
-                                                    status);
+                                                    f32_tma, status);
     return launch_status();
 }
 

@@ -176,6 +176,22 @@ def test_dense_products_all_operand_layouts(K, akm, bkm, out):
     assert O.close(d2, ref, 1e-2 if out == torch.bfloat16 else 1e-5)
 
 
+@pytest.mark.parametrize("M,N,Kc,out", [(1024, 520, 328, torch.float32), (256, 72, 200, torch.float32), (1000, 72, 200, torch.bfloat16),
+                                         (128, 128, 4096, torch.bfloat16)])
+def test_dense_products_whole_row_tiles_and_narrow_outputs(K, M, N, Kc, out):
+    """float32 outputs with whole 128-row tiles (TMA-stored), outputs of at most 128 columns (128-column tiles)."""
+    g = torch.Generator().manual_seed(6)
+    A = torch.randn(M, Kc, generator=g).bfloat16()
+    B = torch.randn(N, Kc, generator=g).bfloat16()
+    ref = A.float() @ B.float().t()
+    for akm, bkm in ((True, True), (False, False)):
+        a = (A if akm else A.t().contiguous()).cuda()
+        b = (B if bkm else B.t().contiguous()).cuda()
+        d = K.gemm_dense(a, b, akm, bkm, out_dtype=out, impl=K.IMPL_UMMA)
+        K.check_status()
+        assert O.close(d, ref, 1e-2 if out == torch.bfloat16 else 1e-5)
+
+
 @pytest.mark.parametrize("akm,bkm", [(True, True), (True, False), (False, True), (False, False)])
 @pytest.mark.parametrize("M,N,Kc", [(1000, 520, 328), (2048, 264, 72), (136, 136, 8), (304, 1032, 4096)])
 def test_dense_products_on_cta_pairs(K, akm, bkm, M, N, Kc):
