@@ -571,7 +571,7 @@ def run_gpt2mlp(args):
             dcs.append(dc.reshape(-1))
         return torch.cat(dcs)                     # 5.9 M coefficients, 11.8 MB bf16
 
-    # 168 short launches per step: replayed as one CUDA graph so that the host's launch rate is not what is measured
+    # 216 short launches per step: replayed as one CUDA graph so that the host's launch rate is not what is measured
     # (the all-reduce stays outside the graph, on the graph's output buffer)
     graph, flat_static = None, None
     if not args.no_graph:
@@ -685,11 +685,11 @@ def run_gpt2mlp(args):
             "config": {"workload": f"gpt2mlp: the 24 pseudorandom-weight layers of GPT-2 small's 12 MLPs (768 -> 3072 -> 768, d_c=128, "
                                    f"seeds {c['seed0']}+{c['seed_step']}i), {T} tokens per GPU, fwd + dX + dC of every layer",
                        "parallelism": f"dp{world} (one flat all-reduce of the 24 dC, 11.8 MB)" if world > 1 else "single GPU",
-                       "launch": "eager launches" if graph is None else "the step's 168 kernels replayed as one CUDA graph",
+                       "launch": "eager launches" if graph is None else "the step's 216 kernels replayed as one CUDA graph",
                        "l2": "one step streams about 1.5 GB of activations, outputs and gradients (24 layers), far more than the 126 MB L2 "
                              "(no explicit flush)"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": 24 * 7 * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "whole step (24 layers x 7 launches; contractions of 128 and 768-3072)",
+            "clocks": clocks, "e2e": e2e, "gpu_launches": 12 * 18 * args.steps,   # per block: c_fc fwd 3, c_proj fwd 4 (z split-K), c_proj bwd 5, c_fc bwd 6
+            "roofline": {"bound": "tensor", "kernel": "whole step (24 layers, 216 launches; contractions of 128 and 768-8192)",
                          "achieved": per_gpu, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": per_gpu / peaks["tensor"],
                          "peak_source": f"{peaks['src']} burst bf16", "traffic": None},
             "cpu_baseline": cpu_baseline,
