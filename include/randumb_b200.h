@@ -244,6 +244,17 @@ int rdb_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, 
                    int b_kmajor, int impl, int32_t *status, void *stream);
 
 /*
+ * The same product with scratch for split-K: when the output has few tiles and the contraction is long
+ * (rdb_gemm_dense_workspace_bytes > 0), the contraction is cut into slices that run as independent work items writing
+ * float32 partial products into `workspace`, summed afterwards in a fixed order.  Needs a densely packed output
+ * (ldd == N) and a 256-byte aligned workspace; falls back to rdb_gemm_dense otherwise.  No reference counterpart.
+ */
+size_t rdb_gemm_dense_workspace_bytes(int64_t M, int64_t N, int64_t Kc);
+int rdb_gemm_dense_ws(void *d, const void *a, const void *b, void *workspace, size_t workspace_bytes, int64_t M, int64_t N,
+                      int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int a_dtype, int b_dtype, int d_dtype,
+                      int a_kmajor, int b_kmajor, int impl, int32_t *status, void *stream);
+
+/*
  * Reference 1-D-coefficient form (every existing randumb model):
  *   out[n] = sum_m S[sq(n), m] * coef[m],  sq(n) = (n % Q)*stride_Q + (n / Q)*stride_P,  float32 [P,Q].
  * Stands in for rten::materialize_fwd (src/rten_cpp/RandumbTensor.py:235-290, 371-381) and

@@ -46,6 +46,9 @@ PROTOTYPES = {
     "rdb_gemm_noise": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i64, _i64, _u32, _i32, _vp, _vp]),
     "rdb_gemm_dense": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp,
                               _vp]),
+    "rdb_gemm_dense_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "rdb_gemm_dense_ws": (_i32, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp,
+                          _vp]),
     "rdb_materialize_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _u32, _vp]),
     "rdb_materialize_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "rdb_materialize_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _u32, _vp]),

@@ -179,6 +179,26 @@ extern "C" int rdb_gemm_dense(void *d, const void *a, const void *b, int64_t M, 
                      b_kmajor ? ldb : 1, b_kmajor ? 1 : ldb, none, M, N, Kc, st);
 }
 
+extern "C" size_t rdb_gemm_dense_workspace_bytes(int64_t M, int64_t N, int64_t Kc) {
+    if (M <= 0 || N <= 0 || Kc <= 0) return 0;
+    const int split = dense_split_k_slices(M, N, Kc);
+    return split > 1 ? (size_t)split * (size_t)M * (size_t)N * sizeof(float) : 0;
+}
+
+extern "C" int rdb_gemm_dense_ws(void *d, const void *a, const void *b, void *workspace, size_t workspace_bytes, int64_t M,
+                                 int64_t N, int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int a_dtype, int b_dtype,
+                                 int d_dtype, int a_kmajor, int b_kmajor, int impl, int32_t *status, void *stream) {
+    const size_t need = rdb_gemm_dense_workspace_bytes(M, N, Kc);
+    const bool split_ok = need > 0 && g_dense_pair != 2 && workspace && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
+                          ldd == N && impl != RDB_IMPL_SIMT && a_dtype == RDB_BF16 && b_dtype == RDB_BF16 && d && a && b &&
+                          lda >= (a_kmajor ? Kc : M) && ldb >= (b_kmajor ? Kc : N) &&
+                          umma_shape_ok_dense(M, N, Kc, lda, ldb, ldd, d_dtype, a_kmajor, b_kmajor, a, b, d);
+    if (!split_ok)
+        return rdb_gemm_dense(d, a, b, M, N, Kc, lda, ldb, ldd, a_dtype, b_dtype, d_dtype, a_kmajor, b_kmajor, impl, status, stream);
+    return umma_gemm_dense_split_k(d, a, b, reinterpret_cast<float *>(workspace), dense_split_k_slices(M, N, Kc), M, N, Kc, lda, ldb,
+                                   d_dtype, a_kmajor, b_kmajor, status, (cudaStream_t)stream);
+}
+
 extern "C" size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path,
                                              int impl) {
     if (T <= 0 || K <= 0 || N <= 0 || R <= 0) return 0;

@@ -253,11 +253,15 @@ def gemm_dense(a: torch.Tensor, b: torch.Tensor, a_kmajor: bool = True, b_kmajor
         raise RuntimeError("gemm_dense: contraction extents differ")
     out_dtype = out_dtype or a.dtype
     d = torch.empty((M, N), dtype=out_dtype, device=dev)
+    L = _lib.lib()
     with torch.cuda.device(dev):
-        rc = _lib.lib().rdb_gemm_dense(_ptr(d), _ptr(a), _ptr(b), M, N, Kc, a.shape[1], b.shape[1], N, _dt(a.dtype),
-                                       _dt(b.dtype), _dt(out_dtype), 1 if a_kmajor else 0, 1 if b_kmajor else 0, impl,
-                                       _ptr(status_buffer(dev)), _stream(dev))
-    _lib.check(rc, "rdb_gemm_dense")
+        # few output tiles and a long contraction: scratch for split-K (float32 partial products, ordered sum)
+        nbytes = L.rdb_gemm_dense_workspace_bytes(M, N, Kc) if impl != IMPL_SIMT and a.dtype == torch.bfloat16 else 0
+        ws = _workspace(nbytes, dev) if nbytes else None
+        rc = L.rdb_gemm_dense_ws(_ptr(d), _ptr(a), _ptr(b), _ptr(ws), nbytes, M, N, Kc, a.shape[1], b.shape[1], N, _dt(a.dtype),
+                                 _dt(b.dtype), _dt(out_dtype), 1 if a_kmajor else 0, 1 if b_kmajor else 0, impl,
+                                 _ptr(status_buffer(dev)), _stream(dev))
+    _lib.check(rc, "rdb_gemm_dense_ws")
     return d
 
 
