@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the fused pseudorandom-weight matmul (forward + dX + dC) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemm|sharded|gemv]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemm|sharded|gemv|gpt2mlp]
+                    [--gather-output] [--replicate-grads] [--no-graph] [--no-cpu-baseline]
 
 One step = one forward + backward pass of the layer over one batch of seeded synthetic input.
 Default workload ("gemm"): x bf16 [8192 x 4096], virtual W [16384 x 4096], d_c = 1024, seed 42, float32
@@ -10,7 +11,10 @@ torchrun, one rank per GPU) every rank runs that step on its own tokens and the 
 are summed with one NCCL all-reduce per step (data parallel, weak scaling).
 
 `--workload sharded` runs the 65536 x 16384 virtual layer (d_c = 2048, seed 7) with its output rows split
-over the ranks (strong scaling); `--workload gemv` the batch-1 float32 4096 x 4096 layer.
+over the ranks (strong scaling; by default y, dX and dC stay sharded, `--gather-output` all-gathers y and
+`--replicate-grads` gives every rank the full dX and dC); `--workload gemv` the batch-1 float32 4096 x 4096 layer
+(the step replayed as a CUDA graph unless `--no-graph`); `--workload gpt2mlp` the 24 pseudorandom-weight layers of
+GPT-2 small's MLPs (768 <-> 3072, d_c = 128), data parallel with one flat all-reduce of their dC.
 
 Prints ONE JSON line (rank 0).  `--impl reference` times the reference's CPU PyTorch path (explicit noise
 matrix, W = S @ C, F.linear, autograd) on the host cores instead; it never touches the GPU kernels.

@@ -275,6 +275,30 @@ def test_run_to_run_reproducible(K):
     assert torch.equal(d1[0], d2[0]) and torch.equal(d1[1], d2[1])
 
 
+@pytest.mark.parametrize("T,Kin,N,R", [(2048, 264, 520, 72), (300, 64, 136, 200)])
+def test_partial_backward_and_graph_replay(K, T, Kin, N, R):
+    """Asking for only dX or only dC gives the same tensors as asking for both; a forward + backward captured into a
+    CUDA graph (no allocation, no synchronisation inside the entry points) replays to the eager results."""
+    x, C, dy = _inputs(T, Kin, N, R, torch.bfloat16, 4)
+    xg, Cg, dyg = x.cuda(), C.cuda(), dy.cuda()
+    y = K.linear_fwd(xg, Cg, 3, N, 16)
+    dx, dc = K.linear_bwd(dyg, xg, Cg, 3, 16)
+    dx_only, none1 = K.linear_bwd(dyg, xg, Cg, 3, 16, need_dc=False)
+    none2, dc_only = K.linear_bwd(dyg, xg, Cg, 3, 16, need_dx=False)
+    assert none1 is None and none2 is None and torch.equal(dx_only, dx) and torch.equal(dc_only, dc)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_g = K.linear_fwd(xg, Cg, 3, N, 16)
+        dx_g, dc_g = K.linear_bwd(dyg, xg, Cg, 3, 16)
+    for _ in range(2):
+        y_g.zero_(); dx_g.zero_(); dc_g.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y_g, y) and torch.equal(dx_g, dx) and torch.equal(dc_g, dc)
+    K.check_status()
+
+
 # ---- full benchmark size: properties that do not need the oracle at that size ---------------------------
 def test_full_size_properties(K):
     """8192 x 4096 -> 16384, d_c = 1024 (the headline configuration)."""
