@@ -112,7 +112,8 @@ int rdb_set_option(int key, int value);
  * counters per CTA into it: [0] MMA thread waiting for the streamed operand, [1] waiting for the generated
  * operand, [2] waiting for the epilogue to drain TMEM, [3] MMA thread total, [4] TMA thread waiting for a
  * free stage, [5] generator waiting for a free stage, [6] generator hashing and storing, [7] epilogue busy,
- * [8] MMA thread in fences, [9] issuing MMAs, [10] issuing commits; the rest unused.
+ * [8] MMA thread in fences, [9] issuing MMAs, [10] issuing commits; the rest unused.  The CTA-pair plain-product kernel
+ * writes [0] (operands), [2], [3] and [4] the same way.
  * Pass NULL to switch it off (the default; the counters then cost nothing).
  */
 int rdb_set_profile_buffer(void *device_buffer, size_t bytes);
