@@ -193,6 +193,30 @@ def test_dense_products_whole_row_tiles_and_narrow_outputs(K, M, N, Kc, out):
         assert O.close(d, ref, 1e-2 if out == torch.bfloat16 else 1e-5)
 
 
+def test_dense_products_random_shapes(K):
+    """Seeded random extents (multiples of 8, ragged against every tile size), operand layouts and kernel choices."""
+    import random
+    rnd = random.Random(1234)
+    g = torch.Generator().manual_seed(9)
+    for case in range(16):
+        M = 8 * rnd.randint(1, 160)
+        N = 8 * rnd.randint(1, 160)
+        Kc = 8 * rnd.randint(1, 300)
+        akm, bkm = rnd.random() < 0.5, rnd.random() < 0.5
+        pair = rnd.choice((0, 1, 2))
+        A = torch.randn(M, Kc, generator=g).bfloat16()
+        B = torch.randn(N, Kc, generator=g).bfloat16()
+        a = (A if akm else A.t().contiguous()).cuda()
+        b = (B if bkm else B.t().contiguous()).cuda()
+        prev = K.set_option(2, pair)
+        try:
+            d = K.gemm_dense(a, b, akm, bkm, impl=K.IMPL_UMMA)
+        finally:
+            K.set_option(2, prev)
+        K.check_status()
+        assert O.close(d, A.float() @ B.float().t(), 1e-2), (case, M, N, Kc, akm, bkm, pair)
+
+
 @pytest.mark.parametrize("M,N,Kc", [(512, 2048, 16384), (128, 768, 8192), (72, 264, 1504), (256, 128, 3072)])
 def test_dense_products_split_k(K, M, N, Kc):
     """Few output tiles and a long contraction: slices of the contraction as independent work items, float32 partial
