@@ -124,7 +124,9 @@ def ref_rt_mm(rt, mat1, coef, P, Q, sP, sQ, seed):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: TRITON_INTERPRET=1 AUTOTUNE=0 python tests/golden/make_golden.py /path/to/reference")
+    root = sys.argv[1]
     rt = load_reference(root)
     out = {}
 
