@@ -111,3 +111,42 @@ def test_shard_ranges_partition(total, world):
         assert (lo % 8 == 0 or lo == total) and (hi % 8 == 0 or hi == total)
     sizes = [hi - lo for lo, hi in rs]
     assert max(sizes) - min(sizes) <= 8
+
+
+def test_vector_form_operator_schemas_and_cpu_stubs():
+    assert str(torch.ops.rten.scale_bias_bwd.default._schema) == "rten::scale_bias_bwd(Tensor dout, SymInt seed) -> Tensor"
+    assert str(torch.ops.rten.embed_fwd.default._schema) == \
+        "rten::embed_fwd(Tensor idx, Tensor coefs, SymInt rowsize, SymInt seed) -> Tensor"
+    assert str(torch.ops.rten.embed_bwd.default._schema) == \
+        "rten::embed_bwd(Tensor idx, Tensor dout, SymInt dcoefs_size, SymInt rowsize, SymInt seed) -> Tensor"
+    for call in (lambda: rb.ops.scale_bias_bwd(torch.ones(4), 0),
+                 lambda: rb.ops.embed_fwd(torch.zeros(3, dtype=torch.int64), torch.ones(4), 5, 0),
+                 lambda: rb.ops.rt_mm(torch.ones(2, 3), torch.ones(4), [3, 5], [5, 1], 0)):
+        with pytest.raises(NotImplementedError, match="Unsupported CPU implementation"):
+            call()
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        idx = torch.empty(2, 7, dtype=torch.int64, device="cuda")
+        assert rb.ops.embed_fwd(idx, torch.empty(9, device="cuda"), 16, 1).shape == (2, 7, 16)
+        assert rb.ops.scale_bias_bwd(torch.empty(50, device="cuda"), 1).shape == (1,)
+
+
+def test_reference_convention_modules_on_cpu():
+    """Parameters, buffers and the random-bias scales of the reference-style layers (construction only)."""
+    m = rb.SillyLinear(12, 20, rb.listgen([6, 4]), rb.stepgen(3, 2), rt_bias=True, coef_form="vector")
+    assert m.seed == [3, 5] and m.int_dim == [6, 4]
+    assert {n for n, _ in m.named_parameters()} == {"weight_coef", "bias_coef", "weight_scale_bias", "bias_scale_bias"}
+    assert m.weight.fused_bias and m.weight.scale_bias is m.weight_scale_bias and not m.weight.is_matrix_form
+    assert abs(float(m.bias_scale_bias.detach()) - 1.0 / math.sqrt(12)) < 1e-6 and float(m.weight_coef.detach().abs().sum()) == 0.0
+    assert list(m.state_dict()) == ["weight_coef", "bias_coef", "weight_scale_bias", "bias_scale_bias"]   # virtual tensors are not stored
+    mm = rb.SillyLinear(12, 20, [6, 4], [3, 5], rt_bias=True)           # matrix-form weight: only the bias has a scale
+    assert mm.weight.is_matrix_form and {n for n, _ in mm.named_parameters()} == {"weight_coef", "bias_coef", "bias_scale_bias"}
+    with pytest.raises(ValueError):
+        rb.SillyLinear(4, 4, [2, 2], [0, 1], coef_form="dense")
+    e = rb.SillyEmbedding(100, 16, [8], rb.stepgen(9, 1), device="cpu")
+    assert e.weight.shape == (100, 16) and e.weight_coef.shape == (8,) and e.seed == [9]
+    with pytest.raises(AssertionError):
+        rb.SillyEmbedding(10, 4, [2], [0], padding_idx=0, device="cpu")
+    c = rb.SillyConv2d(3, 8, [16, 4], [5, 6], 3, padding=1)
+    assert tuple(c.weight.shape) == (8, 3, 3, 3) and c.weight.noise_matrix_shape == (216, 16) and c.bias.shape == (8,)
+    assert {n for n, _ in c.named_parameters()} == {"weight_coef", "bias_coef"}
