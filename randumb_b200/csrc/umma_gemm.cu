@@ -1190,37 +1190,56 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     tc_fence_after_sync();
                     const uint32_t sa = smem_base + st.idx * Cfg::STAGE;
                     const uint32_t b_lo = smem_desc_lo(sa + Cfg::A_PART, B_LBO);
-                    if (kb == 0) {
+                    auto issue = [&](int s, int k) {
+                        const uint32_t a_lo = smem_desc_lo(sa + s * SUB_BYTES, A_LBO);
+                        const uint64_t adesc = pack_desc(a_lo + ((k * A_KSTEP) >> 4), desc_hi);
+                        const uint64_t bdesc = pack_desc(b_lo + ((k * B_KSTEP) >> 4), desc_hi);
+                        umma_bf16_pair(tmem_base + acc_of(it, s) * BN, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                    };
+                    const bool first = (kb == 0), last = (kb == num_kb - 1);
+                    if (MT == 2 && (first || last)) {
+                        // tile boundaries, one accumulator after the other: the first k-block of accumulator 0 starts as soon
+                        // as the epilogue has drained it (accumulator 1 is still being stored), and the last k-block hands
+                        // accumulator 0 to the epilogue while accumulator 1's MMAs still run
 #pragma unroll
                         for (int s = 0; s < MT; ++s) {
-                            // the accumulator is reusable once both CTAs' epilogues have drained it
+                            if (first) {
+                                const long long te = prof ? clock64() : 0;
+                                if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[acc_of(it, s)]), par_of(it) ^ 1, abortp)) {
+                                    raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
+                                    ok = false;
+                                    break;
+                                }
+                                tc_fence_after_sync();
+                                if (prof) pc2 += clock64() - te;
+                            }
+#pragma unroll
+                            for (int k = 0; k < BK / UMMA_K; ++k) issue(s, k);
+                            if (last) {
+                                umma_commit_pair(smem_u32(&bar_tmem_full[acc_of(it, s)]));
+                                umma_commit_pair(mapa(smem_u32(&bar_tmem_full[acc_of(it, s)]), peer));
+                            }
+                        }
+                    } else {
+                        if (first) {
                             const long long te = prof ? clock64() : 0;
-                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[acc_of(it, s)]), par_of(it) ^ 1, abortp)) {
+                            if (!mbar_wait_cluster(smem_u32(&bar_tmem_empty[acc_of(it, 0)]), par_of(it) ^ 1, abortp)) {
                                 raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
                                 ok = false;
                                 break;
                             }
+                            tc_fence_after_sync();
                             if (prof) pc2 += clock64() - te;
                         }
-                        tc_fence_after_sync();
-                    }
-                    if (!ok) break;
-                    // consecutive MMAs alternate between the accumulators and share the B slice
+                        // consecutive MMAs alternate between the accumulators and share the B slice
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t bdesc = pack_desc(b_lo + ((k * B_KSTEP) >> 4), desc_hi);
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
 #pragma unroll
-                        for (int s = 0; s < MT; ++s) {
-                            const uint32_t a_lo = smem_desc_lo(sa + s * SUB_BYTES, A_LBO);
-                            const uint64_t adesc = pack_desc(a_lo + ((k * A_KSTEP) >> 4), desc_hi);
-                            umma_bf16_pair(tmem_base + acc_of(it, s) * BN, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                            for (int s = 0; s < MT; ++s) issue(s, k);
                         }
-                    }
-                    if (kb == num_kb - 1) {
-#pragma unroll
-                        for (int s = 0; s < MT; ++s) {
-                            umma_commit_pair(smem_u32(&bar_tmem_full[acc_of(it, s)]));
-                            umma_commit_pair(mapa(smem_u32(&bar_tmem_full[acc_of(it, s)]), peer));
+                        if (last) {
+                            umma_commit_pair(smem_u32(&bar_tmem_full[acc_of(it, 0)]));
+                            umma_commit_pair(mapa(smem_u32(&bar_tmem_full[acc_of(it, 0)]), peer));
                         }
                     }
                     if (!ok) break;
