@@ -365,11 +365,34 @@ def run_ours(args, cfg):
         else:
             avg_ms, fill_ms, kernel = fused_ms, None, fused["kernel"]
         achieved = flops_launch / (avg_ms * 1e-3) / 1e12
+        # SM clock the dominant kernel actually ran at: cycles its MMA thread counted from first to last k-block, over the
+        # launch's CUDA-event time (a lower bound: prologue and the last epilogue are outside the counted span); nvidia-smi
+        # samples every 50 ms and mostly sees the idle clock
+        sm_mhz_in_kernel = None
+        if staged:
+            try:
+                from randumb_b200 import _lib
+                prof = torch.zeros(148 * 16, dtype=torch.int64, device=dev)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                for _ in range(5):
+                    K.gemm_dense(dy, S, True, False)
+                _lib.lib().rdb_set_profile_buffer(prof.data_ptr(), prof.numel() * 8)
+                e0.record()
+                K.gemm_dense(dy, S, True, False)
+                e1.record()
+                torch.cuda.synchronize()
+                _lib.lib().rdb_set_profile_buffer(None, 0)
+                cyc = int(prof.view(148, 16)[:, 3].max().item())
+                if cyc > 0:
+                    sm_mhz_in_kernel = cyc / (e0.elapsed_time(e1) * 1e3)
+            except Exception:
+                sm_mhz_in_kernel = None
         roofline = {"bound": "tensor", "kernel": kernel, "achieved": achieved,
                     "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"],
                     "peak_source": f"{peaks['src']} burst bf16", "avg_launch_ms": avg_ms,
                     "traffic": (DENSE_ON_NOISE_DRAM_BYTES if staged else NOISE_GEMM_DRAM_BYTES).get(args.workload),
-                    "noise_fill_ms": fill_ms, "regenerate_in_kernel": fused if staged else None}
+                    "noise_fill_ms": fill_ms, "regenerate_in_kernel": fused if staged else None,
+                    "sm_mhz_in_kernel": sm_mhz_in_kernel}
     else:
         # matrix-vector: bytes of C read twice and dC written once (+ the small vectors)
         bytes_step = 3 * R * Kin * 4 + 4 * (3 * Kin + 2 * N + 2 * R)
