@@ -51,6 +51,18 @@ def algorithmic_flops(T, K, N, R):
     return min(fact, wpath)
 
 
+def cpu_model():
+    """Name of the host CPU the CPU legs ran on (first 'model name' of /proc/cpuinfo)."""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.lower().startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -179,7 +191,7 @@ def run_reference(args, cfg):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args.workload, cfg, args.gpus, args.replicate_grads, args.gather_output),
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "cpu": cpu_model(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -423,7 +435,7 @@ def run_ours(args, cfg):
             v = (3 * R * Kin * 4 + 4 * (3 * Kin + 2 * N + 2 * R)) / dt_cpu / 1e9
         else:
             v = algorithmic_flops(T_s, Kin, N, R) / dt_cpu / 1e12
-        cpu_baseline = {"value": v, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
+        cpu_baseline = {"value": v, "unit": unit, "cores": torch.get_num_threads(), "cpu": cpu_model(), "kind": "port",
                         "sample": f"one step at {T_s} of {T} tokens (full K/N/d_c) in {dt_cpu:.2f} s: explicit S from the C oracle, "
                                   "W = S @ C, F.linear, autograd; float32"}
 
@@ -699,7 +711,7 @@ def run_gpt2mlp(args):
             t_, _ = cpu_reference_step(cc, T)
             dt_cpu += t_
             fl_cpu += algorithmic_flops(T, Kin, n_out, R)
-        cpu_baseline = {"value": fl_cpu / dt_cpu / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+        cpu_baseline = {"value": fl_cpu / dt_cpu / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "cpu": cpu_model(), "kind": "port",
                         "sample": f"one block's two layers (of 12 blocks) at all {T} tokens in {dt_cpu:.2f} s: explicit S from the C "
                                   "oracle, W = S @ C, F.linear, autograd; float32"}
     if rank == 0:
