@@ -5,7 +5,8 @@
  *   S[o,k] = squirrel5(uint32(198491317*o + k), seed)  in [-1,1]   (N x R, regenerated on the fly)
  *   C      = trainable coefficient matrix                          (R x K, row-major)
  * and   y = x W^T,   dX = dY W,   dC = S^T (dY^T X).
- * W is never formed on the tensor-core path.  S is regenerated from the seed in every call: tile by tile in shared
+ * W is never formed on the factored path (every BASELINE layer but a 256 -> 10 head); the W path, chosen when it costs
+ * fewer FLOPs, keeps W in the caller's workspace for the length of one call.  S is regenerated from the seed in every call: tile by tile in shared
  * memory, or (1024 tokens or more) once per call as a transient bf16 copy in the caller's workspace -- see
  * RDB_OPT_STAGE_NOISE.  Nothing of it survives the call.
  *
@@ -46,7 +47,7 @@ extern "C" {
 /* association of W = S*C with the activation (rdb_linear_*): */
 #define RDB_PATH_AUTO 0     /* pick by FLOP count */
 #define RDB_PATH_FACTORED 1 /* y = (x C^T) S^T ;  g = dY S, dX = g C, dC = g^T X  */
-#define RDB_PATH_WPATH 2    /* materialise W = S C in workspace, then dense products */
+#define RDB_PATH_WPATH 2    /* W = S C in workspace (bf16 on the tensor-core kernels, float32 on CUDA cores), then dense products */
 
 /* which kernels may run (rdb_linear_*): */
 #define RDB_IMPL_AUTO 0   /* tcgen05 tensor-core kernels when dtype/shape allow, else SIMT */
@@ -63,6 +64,7 @@ extern "C" {
 #define RDB_ERR_UNSUPPORTED -6
 #define RDB_ERR_DRIVER -7
 #define RDB_ERR_TOO_LARGE -8
+#define RDB_ERR_PEER -9
 /* tensor-map encoding rejected by the driver: the code is RDB_ERR_DRIVER_BASE - CUresult */
 #define RDB_ERR_DRIVER_BASE -1000
 
@@ -71,12 +73,16 @@ extern "C" {
 #define RDB_STATUS_TIMEOUT_MMA 2
 #define RDB_STATUS_TIMEOUT_EPILOGUE 3
 #define RDB_STATUS_TIMEOUT_GENERATOR 4
+#define RDB_STATUS_TIMEOUT_PEER 5      /* a rank of a peer exchange did not arrive in time */
 
 int rdb_version(void);
 const char *rdb_strerror(int code);
 
 /*
- * Process-wide tuning switches (not part of the reference surface; defaults are the tuned ones).
+ * Tuning switches (not part of the reference surface; defaults are the tuned ones).  rdb_set_option sets the PROCESS
+ * DEFAULT of one switch; the *_ex entry points take a `const rdb_call_options *` whose fields override the defaults for
+ * that one call (a field < 0, or a NULL pointer, keeps the default), so concurrent callers -- autograd worker threads,
+ * several streams -- never have to change process state around a launch.
  *   RDB_OPT_NOISE_TILE   kernel variant / work unit of the generated-operand product:
  *                        0: automatic (7 for more than 512 tokens with a contraction of at most 4096, else 1)
  *                        single-CTA MMAs (cta_group::1), (cluster size, token sub-tiles, generated rows):
@@ -94,27 +100,44 @@ const char *rdb_strerror(int code);
  *                           hashes every noise element once instead of once per 512-token tile; below that, and
  *                           whenever S would exceed 1 GiB, the kernels regenerate S tile by tile in shared memory
  *                        1: always regenerate tile by tile (no S in memory)   2: always stage when it fits
- *   RDB_OPT_RESERVE_SMS  0 (default) .. 64: SMs the persistent plain-product kernels leave without a CTA.  Their CTAs
- *                        take a whole SM each for the length of the launch, so a collective enqueued beside them
- *                        (an NCCL all-reduce of the previous product's result) only runs at the same time if some SMs
- *                        are left free; set around the launch that should overlap, then restore.
- * Returns the previous value, or RDB_ERR_UNSUPPORTED for an unknown key.
+ *   RDB_OPT_RESERVE_SMS  0 (default) .. RDB_MAX_RESERVE_SMS: SMs the persistent plain-product kernels leave without a
+ *                        CTA.  Their CTAs take a whole SM each for the length of the launch, so a collective enqueued
+ *                        beside them (an NCCL all-reduce of the previous product's result) only runs at the same time
+ *                        if some SMs are left free.  Meant to be given per call, for the launch that should overlap.
+ *   RDB_OPT_FILL_OVERLAP 1 (default): rdb_linear_fwd hashes the staged S on a stream of the library's own, forked from
+ *                        and joined back into the caller's stream with events, so the integer-ALU fill runs beside the
+ *                        tensor-core product z = x C^T it does not depend on.  The stream and its two events are created
+ *                        once per device by the first such call (make it before any stream capture; a call that finds
+ *                        its stream capturing before they exist keeps the fill on the caller's stream).  0: always on
+ *                        the caller's stream.
+ * rdb_set_option returns the previous default, or RDB_ERR_UNSUPPORTED for an unknown key or a value outside the
+ * range above (nothing changes then); a call whose rdb_call_options holds such a value returns the same error.
  */
 #define RDB_OPT_NOISE_TILE 1
 #define RDB_OPT_DENSE_PAIR 2
 #define RDB_OPT_STAGE_NOISE 3
 #define RDB_OPT_RESERVE_SMS 4
+#define RDB_OPT_FILL_OVERLAP 5
+#define RDB_MAX_RESERVE_SMS 64
 int rdb_set_option(int key, int value);
 
+typedef struct rdb_call_options {
+    int32_t noise_tile;   /* RDB_OPT_NOISE_TILE, or < 0 for the process default */
+    int32_t dense_pair;   /* RDB_OPT_DENSE_PAIR   ... */
+    int32_t stage_noise;  /* RDB_OPT_STAGE_NOISE  ... */
+    int32_t reserve_sms;  /* RDB_OPT_RESERVE_SMS  ... */
+    int32_t fill_overlap; /* RDB_OPT_FILL_OVERLAP ... */
+} rdb_call_options;
+
 /*
- * Tuning aid.  While a device buffer of at least 128 bytes per CTA (148 * 128 covers any launch) is
- * registered, every launch of the generated-operand tensor-core kernel writes sixteen int64 SM-cycle
- * counters per CTA into it: [0] MMA thread waiting for the streamed operand, [1] waiting for the generated
- * operand, [2] waiting for the epilogue to drain TMEM, [3] MMA thread total, [4] TMA thread waiting for a
- * free stage, [5] generator waiting for a free stage, [6] generator hashing and storing, [7] epilogue busy,
+ * Cycle counters of the tensor-core kernels (diagnostics; no reference counterpart).  While a device buffer of at
+ * least 128 bytes per CTA (148 * 128 covers any launch) is registered, every launch of the generated-operand kernels
+ * writes sixteen int64 SM-cycle counters per CTA into it: [0] MMA thread waiting for the streamed operand, [1] waiting
+ * for the generated operand, [2] waiting for the epilogue to drain TMEM, [3] MMA thread total, [4] TMA thread waiting
+ * for a free stage, [5] generator waiting for a free stage, [6] generator hashing and storing, [7] epilogue busy,
  * [8] MMA thread in fences, [9] issuing MMAs, [10] issuing commits; the rest unused.  The CTA-pair plain-product kernel
- * writes [0] (operands), [2], [3] and [4] the same way.
- * Pass NULL to switch it off (the default; the counters then cost nothing).
+ * writes [0] (operands), [2], [3] and [4] the same way; the benchmark divides [3] by the launch's event time to report
+ * the SM clock the kernel really ran at.  Pass NULL to switch it off (the default; the counters then cost nothing).
  */
 int rdb_set_profile_buffer(void *device_buffer, size_t bytes);
 
@@ -145,10 +168,14 @@ int rdb_noise_1d(float *out, int64_t n, int64_t idx0, uint32_t seed, void *strea
  * Bytes of scratch the linear entry points need for the given problem (op: 0 = forward,
  * 1 = backward).  The workspace must be 256-byte aligned.  bf16 tensor-core path: T*R*2 bytes for z or g, plus
  * N*R*2 bytes when the noise operand is staged (rdb_linear_stages_noise); the size depends on the option values
- * in force, so query it after setting them.
+ * in force, so query it after setting them (or pass the call's options to the _ex form).  The query assumes 16-byte
+ * aligned operands; a call with RDB_IMPL_AUTO whose x, coef, y, dy, dx or dc is not 16-byte aligned runs on the CUDA-core
+ * kernels instead (RDB_IMPL_UMMA returns RDB_ERR_ALIGN) and needs the size this query returns for RDB_IMPL_SIMT.
  */
 size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path,
                                   int impl);
+size_t rdb_linear_workspace_bytes_ex(int op, int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path,
+                                     int impl, const rdb_call_options *options);
 
 /*
  * 1 when the linear entry points would, for this problem, write S (bf16, N x R) into the workspace once per call
@@ -156,6 +183,17 @@ size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64_t N, int64
  * float32 kernels); negative: error.  See RDB_OPT_STAGE_NOISE.  No reference counterpart (a planning query).
  */
 int rdb_linear_stages_noise(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl);
+int rdb_linear_stages_noise_ex(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl,
+                               const rdb_call_options *options);
+
+/*
+ * Planning query: which association and which kernels the linear entry points would use for this problem (operands
+ * assumed 16-byte aligned): returns RDB_PATH_* | (RDB_IMPL_* << 8) with both resolved (never AUTO), or a negative error.
+ * RDB_PATH_AUTO picks by FLOP count -- factored 2TR(K+N) per result against 2NRK + 2TNK through W; RDB_IMPL_AUTO picks
+ * the tcgen05 kernels for bf16 problems whose extents are multiples of 8 (both associations run on them), else the
+ * CUDA-core kernels.  No reference counterpart.
+ */
+int rdb_linear_path(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl);
 
 /*
  * Forward  y[T,N] = x[T,K] * W^T  with W regenerated from (seed, row0) and coef[R,K].
@@ -166,6 +204,9 @@ int rdb_linear_stages_noise(int64_t T, int64_t K, int64_t N, int64_t R, int dtyp
 int rdb_linear_fwd(void *y, const void *x, const void *coef, void *workspace, size_t workspace_bytes,
                    int64_t T, int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed, int dtype,
                    int path, int impl, int32_t *status, void *stream);
+int rdb_linear_fwd_ex(void *y, const void *x, const void *coef, void *workspace, size_t workspace_bytes,
+                      int64_t T, int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed, int dtype,
+                      int path, int impl, const rdb_call_options *options, int32_t *status, void *stream);
 
 /*
  * Backward: dx[T,K] = dy W (skipped when dx == NULL) and dc[R,K] = S^T (dy^T x) (skipped when
@@ -176,6 +217,10 @@ int rdb_linear_fwd(void *y, const void *x, const void *coef, void *workspace, si
 int rdb_linear_bwd(void *dx, void *dc, const void *dy, const void *x, const void *coef, void *workspace,
                    size_t workspace_bytes, int64_t T, int64_t K, int64_t N, int64_t R, int64_t row0,
                    uint32_t seed, int dtype, int path, int impl, int32_t *status, void *stream);
+int rdb_linear_bwd_ex(void *dx, void *dc, const void *dy, const void *x, const void *coef, void *workspace,
+                      size_t workspace_bytes, int64_t T, int64_t K, int64_t N, int64_t R, int64_t row0,
+                      uint32_t seed, int dtype, int path, int impl, const rdb_call_options *options,
+                      int32_t *status, void *stream);
 
 /*
  * Dense weight w[N,K] = S[row0:row0+N, 0:R] * coef[R,K] written out in `dtype` (debugging and ops
@@ -254,6 +299,11 @@ size_t rdb_gemm_dense_workspace_bytes(int64_t M, int64_t N, int64_t Kc);
 int rdb_gemm_dense_ws(void *d, const void *a, const void *b, void *workspace, size_t workspace_bytes, int64_t M, int64_t N,
                       int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int a_dtype, int b_dtype, int d_dtype,
                       int a_kmajor, int b_kmajor, int impl, int32_t *status, void *stream);
+/* ... and with per-call options (workspace may be NULL: no split-K then) */
+int rdb_gemm_dense_ex(void *d, const void *a, const void *b, void *workspace, size_t workspace_bytes, int64_t M, int64_t N,
+                      int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int a_dtype, int b_dtype, int d_dtype,
+                      int a_kmajor, int b_kmajor, int impl, const rdb_call_options *options, int32_t *status,
+                      void *stream);
 
 /*
  * Reference 1-D-coefficient form (every existing randumb model):

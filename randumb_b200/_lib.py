@@ -20,10 +20,25 @@ OPT_NOISE_TILE = 1
 OPT_DENSE_PAIR = 2
 OPT_STAGE_NOISE = 3
 OPT_RESERVE_SMS = 4
+OPT_FILL_OVERLAP = 5
+MAX_RESERVE_SMS = 64
 STATUS_NAMES = {0: "ok", 1: "producer wait expired", 2: "mma wait expired", 3: "epilogue wait expired",
-                4: "generator wait expired"}
+                4: "generator wait expired", 5: "peer wait expired"}
 
 _i64, _u32, _i32, _vp, _sz = ctypes.c_int64, ctypes.c_uint32, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
+
+
+class CallOptions(ctypes.Structure):
+    """``rdb_call_options``: per-call values of the tuning switches; a field < 0 keeps the process default."""
+    _fields_ = [("noise_tile", ctypes.c_int32), ("dense_pair", ctypes.c_int32), ("stage_noise", ctypes.c_int32),
+                ("reserve_sms", ctypes.c_int32), ("fill_overlap", ctypes.c_int32)]
+
+    def __init__(self, noise_tile: int = -1, dense_pair: int = -1, stage_noise: int = -1, reserve_sms: int = -1,
+                 fill_overlap: int = -1):
+        super().__init__(noise_tile, dense_pair, stage_noise, reserve_sms, fill_overlap)
+
+
+_op = ctypes.POINTER(CallOptions)
 
 # name -> (restype, argtypes); one entry per declaration in the header
 PROTOTYPES = {
@@ -35,7 +50,15 @@ PROTOTYPES = {
     "rdb_noise": (_i32, [_vp, _i32, _i64, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_noise_1d": (_i32, [_vp, _i64, _i64, _u32, _vp]),
     "rdb_linear_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64, _i64, _i32, _i32, _i32]),
+    "rdb_linear_workspace_bytes_ex": (_sz, [_i32, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _op]),
     "rdb_linear_stages_noise": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32]),
+    "rdb_linear_stages_noise_ex": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32, _op]),
+    "rdb_linear_path": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32]),
+    "rdb_linear_fwd_ex": (_i32, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32, _op, _vp, _vp]),
+    "rdb_linear_bwd_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32,
+                                 _op, _vp, _vp]),
+    "rdb_gemm_dense_ex": (_i32, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _op,
+                                 _vp, _vp]),
     "rdb_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32, _vp, _vp]),
     "rdb_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32,
                               _vp, _vp]),

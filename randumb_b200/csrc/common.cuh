@@ -36,22 +36,29 @@ int simt_gemm(void *d, int d_dtype, int64_t d_rs, int64_t d_cs, const void *a, i
               int64_t a_cs, const void *b, int b_dtype, int64_t b_rs, int64_t b_cs, Sq5Lin lin, int64_t M,
               int64_t N, int64_t Kc, cudaStream_t stream);
 
+// Tuning switches of one call, resolved from the caller's rdb_call_options (fields < 0 take the process default
+// that rdb_set_option holds).  Passed by value down to the launch: no launch reads process state.
+struct CallOpts {
+    int noise_tile;    // RDB_OPT_NOISE_TILE
+    int dense_pair;    // RDB_OPT_DENSE_PAIR
+    int stage_noise;   // RDB_OPT_STAGE_NOISE
+    int reserve_sms;   // RDB_OPT_RESERVE_SMS
+    int fill_overlap;  // RDB_OPT_FILL_OVERLAP
+};
+
 // ---- implemented in umma_gemm.cu -------------------------------------------------------------
-void set_noise_cfg(int v);
-void set_dense_pair(int v);
-void set_reserve_sms(int v);
 void set_profile_buffer(void *p, size_t bytes);
 bool umma_shape_ok_noise(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, const void *a, const void *d);
 int umma_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, Sq5Lin lin,
-                    int32_t *status, cudaStream_t stream);
+                    int32_t *status, cudaStream_t stream, const CallOpts &o);
 bool umma_shape_ok_dense(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb, int64_t ldd, int d_dtype,
                          int a_kmajor, int b_kmajor, const void *a, const void *b, const void *d);
 int dense_split_k_slices(int64_t M, int64_t N, int64_t Kc);
 int umma_gemm_dense_split_k(void *d, const void *a, const void *b, float *partials, int split, int64_t M, int64_t N,
                             int64_t Kc, int64_t lda, int64_t ldb, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status,
-                            cudaStream_t stream);
+                            cudaStream_t stream, const CallOpts &o);
 int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda,
                     int64_t ldb, int64_t ldd, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status,
-                    cudaStream_t stream);
+                    cudaStream_t stream, const CallOpts &o);
 
 }  // namespace rdb

@@ -1256,6 +1256,11 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
     } else {
         // ------------------------------------------------------------------ epilogue (8 warps, this CTA's 128 rows)
+        // Two phases per tile.  (1) Drain: as soon as an accumulator is complete, every warp copies its 32 rows x 128
+        // columns into registers (already rounded to bf16) and hands the accumulator back to the MMA thread -- TMEM is
+        // held only for the tcgen05.ld round trips, so the next tile's MMAs start while (2) the registers go through the
+        // swizzled staging box and out as TMA tile stores.  One 512 x 256 tile fills all of TMEM, so everything that
+        // happens before the hand-back is time the tensor pipe idles; after it, the stores hide under ~16 k-blocks of MMAs.
         const int ew = warp - Cfg::FIRST_EPI_WARP;
         const int q = warp & 3;                      // TMEM lane quarter this warp may read
         const int cg = ew >> 2;                      // which 128 of the 256 accumulator columns
@@ -1266,43 +1271,53 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
             const int64_t m0 = tile_m(t) * MT * 2 * BM + half * BM;
             const int64_t n0 = tile_n(t) * BN;
-#pragma unroll 1
+            uint32_t packed[MT][64];                 // [sub-tile][16-byte chunk * 4 + word]: 128 bf16 columns of this lane's row
+#pragma unroll
             for (int s = 0; s < MT; ++s) {
                 const int a = acc_of(it, s);
-                if (!mbar_wait_warp<true>(smem_u32(&bar_tmem_full[a]), par_of(it), abortp)) {
+                if (ok && !mbar_wait_warp<true>(smem_u32(&bar_tmem_full[a]), par_of(it), abortp)) {
                     raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
                     ok = false;
-                    break;
                 }
-                tc_fence_after_sync();
+                if (ok) {
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int hb = 0; hb < 2; ++hb) {
+                        uint32_t r0[32], r1[32];
+                        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + cg * 128 + hb * 64);
+                        tmem_ld_32x32(taddr, r0);
+                        tmem_ld_32x32(taddr + 32, r1);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+                            packed[s][hb * 32 + j] = *reinterpret_cast<uint32_t *>(&h0);
+                            packed[s][hb * 32 + 16 + j] = *reinterpret_cast<uint32_t *>(&h1);
+                        }
+                    }
+                    // this warp's part of the accumulator is in registers: hand it back to the MMA thread of the pair
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
+                }
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int s = 0; s < MT; ++s) {
                 const int64_t row_w = m0 + s * 2 * BM + q * 32;    // first row of this warp's 32-row slab
-#pragma unroll 1
+#pragma unroll
                 for (int hb = 0; hb < 2; ++hb) {
                     const int c0 = cg * 128 + hb * 64;
-                    uint32_t r0[32], r1[32];
-                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c0);
-                    tmem_ld_32x32(taddr, r0);
-                    tmem_ld_32x32(taddr + 32, r1);
                     // the previous store of this warp must have finished reading the staging box
                     if (lane == 0) bulk_wait_group_read0();
                     __syncwarp();
-                    tmem_ld_wait();
                     const uint32_t rowaddr = stag + (uint32_t)lane * 128u;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t pk[4], pl[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 2 * e]), __uint_as_float(r0[j * 8 + 2 * e + 1]));
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r1[j * 8 + 2 * e]), __uint_as_float(r1[j * 8 + 2 * e + 1]));
-                            pk[e] = *reinterpret_cast<uint32_t *>(&h0);
-                            pl[e] = *reinterpret_cast<uint32_t *>(&h1);
-                        }
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)((j ^ (lane & 7)) << 4)),
-                                     "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)(((4 + j) ^ (lane & 7)) << 4)),
-                                     "r"(pl[0]), "r"(pl[1]), "r"(pl[2]), "r"(pl[3]) : "memory");
-                    }
+                    for (int ch = 0; ch < 8; ++ch)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)((ch ^ (lane & 7)) << 4)),
+                                     "r"(packed[s][hb * 32 + ch * 4]), "r"(packed[s][hb * 32 + ch * 4 + 1]),
+                                     "r"(packed[s][hb * 32 + ch * 4 + 2]), "r"(packed[s][hb * 32 + ch * 4 + 3]) : "memory");
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0 && row_w < M && n0 + c0 < N) {
@@ -1310,10 +1325,6 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         bulk_commit_group();
                     }
                 }
-                // this warp's part of the accumulator has been read out: tell the MMA thread of the pair
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
             }
         }
         if (lane == 0) bulk_wait_group0();   // all output tiles written before the CTA retires
@@ -1380,10 +1391,6 @@ static int make_tmap(CUtensorMap *m, const void *base, int64_t inner, int64_t ou
     }
     return RDB_OK;
 }
-
-// RDB_OPT_RESERVE_SMS: SMs the persistent plain-product kernels leave idle, for a collective that should run beside them
-static int g_reserve_sms = 0;
-void set_reserve_sms(int v) { g_reserve_sms = v < 0 ? 0 : v; }
 
 static int sm_count() {
     int dev = 0, n = 0;
@@ -1483,14 +1490,11 @@ static int launch_noise_pair(void *d, const void *a, int64_t M, int64_t N, int64
     return launch_status();
 }
 
-// RDB_OPT_NOISE_TILE: (cluster size, token sub-tiles, generated rows) per work unit
-static int g_noise_cfg = 0;
-void set_noise_cfg(int v) { g_noise_cfg = v; }
-
+// o.noise_tile (RDB_OPT_NOISE_TILE): (cluster size, token sub-tiles, generated rows) per work unit
 int umma_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, Sq5Lin lin,
-                    int32_t *status, cudaStream_t st) {
+                    int32_t *status, cudaStream_t st, const CallOpts &o) {
     if (M == 0 || N == 0) return RDB_OK;
-    int cfg = g_noise_cfg;
+    int cfg = o.noise_tile;
     // more than one 512-token tile and a short contraction (many tiles, epilogue matters): CTA pairs (cta_group::2);
     // otherwise one CTA per 512-token tile
     if (cfg == 0) cfg = (M > 4 * BM && Kc <= 4096) ? 7 : 1;
@@ -1520,7 +1524,7 @@ bool umma_shape_ok_dense(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t 
 
 template <int BN, int STAGES, int A_MN, int B_MN, typename OutT>
 static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
-                        int64_t ldd, int32_t *status, cudaStream_t st, int split = 1, int64_t slice_stride = 0) {
+                        int64_t ldd, int32_t *status, cudaStream_t st, int reserve_sms, int split = 1, int64_t slice_stride = 0) {
     using Cfg = DenseCfg<BN, STAGES>;
     CUtensorMap ta, tb;
     int rc = A_MN ? make_tmap(&ta, a, M, Kc, lda, 64, BK) : make_tmap(&ta, a, Kc, M, lda, BK, BM);
@@ -1541,7 +1545,7 @@ static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
     if (e != cudaSuccess) return (int)e;
     const int64_t tiles = cdiv64(M, BM) * cdiv64(N, BN) * split;
-    int ctas = sm_count() - g_reserve_sms;
+    int ctas = sm_count() - reserve_sms;   // SMs left without a CTA for a collective that should run beside this launch
     if (ctas < 1) ctas = 1;
     const int grid = (int)(tiles < ctas ? tiles : ctas);
     // tiles that run at the same time share the panel of the larger operand, which is then streamed from memory once
@@ -1553,7 +1557,7 @@ static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_
 
 template <int MT, int D, int A_MN, int B_MN>
 static int launch_dense_pair(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
-                             int64_t ldd, int64_t tiles, int max_pairs, int32_t *status, cudaStream_t st) {
+                             int64_t ldd, int64_t tiles, int max_pairs, int32_t *status, cudaStream_t st, int reserve_sms) {
     using Cfg = DensePairCfg<MT, D>;
     CUtensorMap ta, tb, td;
     int rc = A_MN ? make_tmap(&ta, a, M, Kc, lda, 64, BK) : make_tmap(&ta, a, Kc, M, lda, BK, BM);
@@ -1576,7 +1580,7 @@ static int launch_dense_pair(void *d, const void *a, const void *b, int64_t M, i
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    int pairs = max_pairs - (g_reserve_sms + 1) / 2;
+    int pairs = max_pairs - (reserve_sms + 1) / 2;
     if (pairs < 1) pairs = 1;
     const int64_t npairs = tiles < pairs ? tiles : pairs;
     cfg.gridDim = dim3((unsigned)(npairs * 2));
@@ -1629,24 +1633,22 @@ static bool prefer_dense_pair(int64_t M, int64_t N, int64_t Kc, int P) {
     return eff >= 0.95 || (Kc >= 4096 && eff >= 0.85);
 }
 
-static int g_dense_pair = 1;   // RDB_OPT_DENSE_PAIR
-void set_dense_pair(int v) { g_dense_pair = v; }
-
 template <int A_MN, int B_MN>
 static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
-                        int64_t ldd, int d_dtype, int32_t *status, cudaStream_t st) {
-    if (d_dtype == RDB_BF16 && g_dense_pair && M > BM && N > BM) {
+                        int64_t ldd, int d_dtype, int32_t *status, cudaStream_t st, const CallOpts &o) {
+    const int rs = o.reserve_sms;
+    if (d_dtype == RDB_BF16 && o.dense_pair && M > BM && N > BM) {
         const int P = max_resident_pairs();
-        if (g_dense_pair == 2 || prefer_dense_pair(M, N, Kc, P))
+        if (o.dense_pair == 2 || prefer_dense_pair(M, N, Kc, P))
             return launch_dense_pair<2, 4, A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, cdiv64(M, 4 * BM) * cdiv64(N, 256), P,
-                                                       status, st);
+                                                       status, st, rs);
     }
     // at most 128 output columns (a coefficient dimension of 128 or less): 128-column tiles, half the MMA and B traffic
     if (d_dtype == RDB_BF16 && N <= 128)
-        return launch_dense<128, 6, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
+        return launch_dense<128, 6, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st, rs);
     if (d_dtype == RDB_BF16)
-        return launch_dense<256, 4, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
-    if (d_dtype == RDB_F32) return launch_dense<256, 4, A_MN, B_MN, float>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st);
+        return launch_dense<256, 4, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st, rs);
+    if (d_dtype == RDB_F32) return launch_dense<256, 4, A_MN, B_MN, float>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st, rs);
     return RDB_ERR_DTYPE;
 }
 
@@ -1690,19 +1692,21 @@ __global__ void split_k_reduce_kernel(OutT *__restrict__ out, const float *__res
 
 // d must be densely packed (ldd == N) and N a multiple of 8; partials: split * M * N floats
 int umma_gemm_dense_split_k(void *d, const void *a, const void *b, float *partials, int split, int64_t M, int64_t N, int64_t Kc,
-                            int64_t lda, int64_t ldb, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status, cudaStream_t st) {
+                            int64_t lda, int64_t ldb, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status, cudaStream_t st,
+                            const CallOpts &o) {
     if (M == 0 || N == 0) return RDB_OK;
     const int64_t stride = M * N;
+    const int rs = o.reserve_sms;
     int rc;
     if (N <= 128) {
-        if (a_kmajor && b_kmajor) rc = launch_dense<128, 6, 0, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
-        else if (a_kmajor) rc = launch_dense<128, 6, 0, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
-        else if (b_kmajor) rc = launch_dense<128, 6, 1, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
-        else rc = launch_dense<128, 6, 1, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
-    } else if (a_kmajor && b_kmajor) rc = launch_dense<256, 4, 0, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
-    else if (a_kmajor) rc = launch_dense<256, 4, 0, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
-    else if (b_kmajor) rc = launch_dense<256, 4, 1, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
-    else rc = launch_dense<256, 4, 1, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, split, stride);
+        if (a_kmajor && b_kmajor) rc = launch_dense<128, 6, 0, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
+        else if (a_kmajor) rc = launch_dense<128, 6, 0, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
+        else if (b_kmajor) rc = launch_dense<128, 6, 1, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
+        else rc = launch_dense<128, 6, 1, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
+    } else if (a_kmajor && b_kmajor) rc = launch_dense<256, 4, 0, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
+    else if (a_kmajor) rc = launch_dense<256, 4, 0, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
+    else if (b_kmajor) rc = launch_dense<256, 4, 1, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
+    else rc = launch_dense<256, 4, 1, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
     if (rc) return rc;
     const int64_t n4 = stride / 4;
     const int grid = (int)(cdiv64(n4, 256) < 148 * 8 ? cdiv64(n4, 256) : 148 * 8);
@@ -1714,12 +1718,12 @@ int umma_gemm_dense_split_k(void *d, const void *a, const void *b, float *partia
 }
 
 int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
-                    int64_t ldd, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status, cudaStream_t st) {
+                    int64_t ldd, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status, cudaStream_t st, const CallOpts &o) {
     if (M == 0 || N == 0) return RDB_OK;
-    if (a_kmajor && b_kmajor) return dense_by_out<0, 0>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st);
-    if (a_kmajor && !b_kmajor) return dense_by_out<0, 1>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st);
-    if (!a_kmajor && b_kmajor) return dense_by_out<1, 0>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st);
-    return dense_by_out<1, 1>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st);
+    if (a_kmajor && b_kmajor) return dense_by_out<0, 0>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st, o);
+    if (a_kmajor && !b_kmajor) return dense_by_out<0, 1>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st, o);
+    if (!a_kmajor && b_kmajor) return dense_by_out<1, 0>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st, o);
+    return dense_by_out<1, 1>(d, a, b, M, N, Kc, lda, ldb, ldd, d_dtype, status, st, o);
 }
 
 }  // namespace rdb

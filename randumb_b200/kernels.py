@@ -74,7 +74,23 @@ def check_status(dev: Optional[torch.device] = None) -> None:
 
 
 def set_option(key: int, value: int) -> int:
-    return _lib.lib().rdb_set_option(key, value)
+    """Set the PROCESS DEFAULT of a tuning switch; returns the previous one.  Raises on an unknown key or a value out of
+    range (nothing changes then).  Per-call values go through the ``options`` argument of the wrappers below."""
+    prev = _lib.lib().rdb_set_option(key, value)
+    _lib.check(min(prev, 0), f"rdb_set_option({key}, {value})")
+    return prev
+
+
+def _auto_impl(impl: int, *ts: Optional[torch.Tensor]) -> int:
+    """IMPL_AUTO with an operand that does not start on a 16-byte boundary (a view at an odd storage offset) means the
+    CUDA-core kernels: say so up front, so the workspace is sized for them."""
+    if impl == IMPL_AUTO and any(t is not None and t.data_ptr() % 16 for t in ts):
+        return IMPL_SIMT
+    return impl
+
+
+def _opts(options: Optional[_lib.CallOptions]):
+    return ctypes.byref(options) if options is not None else None
 
 
 # ------------------------------------------------------------------------------------------ noise
@@ -112,7 +128,7 @@ def _workspace(nbytes: int, dev: torch.device) -> torch.Tensor:
 
 
 def linear_fwd(x: torch.Tensor, coef: torch.Tensor, seed: int, out_features: int, row0: int = 0,
-               path: int = PATH_AUTO, impl: int = IMPL_AUTO) -> torch.Tensor:
+               path: int = PATH_AUTO, impl: int = IMPL_AUTO, options: Optional[_lib.CallOptions] = None) -> torch.Tensor:
     """y[T, N] = x[T, K] @ (S[row0:row0+N] @ coef[R, K]).T  -- x, coef contiguous, same dtype."""
     dev = _need_cuda(x, coef)
     if x.dim() != 2 or coef.dim() != 2 or x.shape[1] != coef.shape[1]:
@@ -126,17 +142,18 @@ def linear_fwd(x: torch.Tensor, coef: torch.Tensor, seed: int, out_features: int
     dt = _dt(x.dtype)
     L = _lib.lib()
     y = torch.empty((T, N), dtype=x.dtype, device=dev)
+    impl = _auto_impl(impl, x, coef, y)
     with torch.cuda.device(dev):
-        nbytes = L.rdb_linear_workspace_bytes(0, T, K, N, R, dt, path, impl)
+        nbytes = L.rdb_linear_workspace_bytes_ex(0, T, K, N, R, dt, path, impl, _opts(options))
         ws = _workspace(nbytes, dev)
-        rc = L.rdb_linear_fwd(_ptr(y), _ptr(x), _ptr(coef), _ptr(ws), ws.numel(), T, K, N, R, row0, _seed(seed), dt, path,
-                              impl, _ptr(status_buffer(dev)), _stream(dev))
+        rc = L.rdb_linear_fwd_ex(_ptr(y), _ptr(x), _ptr(coef), _ptr(ws), ws.numel(), T, K, N, R, row0, _seed(seed), dt, path,
+                                 impl, _opts(options), _ptr(status_buffer(dev)), _stream(dev))
     _lib.check(rc, "rdb_linear_fwd")
     return y
 
 
 def linear_bwd(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, row0: int = 0, need_dx: bool = True,
-               need_dc: bool = True, path: int = PATH_AUTO, impl: int = IMPL_AUTO
+               need_dc: bool = True, path: int = PATH_AUTO, impl: int = IMPL_AUTO, options: Optional[_lib.CallOptions] = None
                ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
     """(dx[T,K], dc[R,K]) for dy[T,N]; either may be skipped."""
     dev = _need_cuda(dy, x, coef)
@@ -152,11 +169,12 @@ def linear_bwd(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int,
     L = _lib.lib()
     dx = torch.empty((T, K), dtype=x.dtype, device=dev) if need_dx else None
     dc = torch.empty((R, K), dtype=x.dtype, device=dev) if need_dc else None
+    impl = _auto_impl(impl, dy, x, coef, dx, dc)
     with torch.cuda.device(dev):
-        nbytes = L.rdb_linear_workspace_bytes(1, T, K, N, R, dt, path, impl)
+        nbytes = L.rdb_linear_workspace_bytes_ex(1, T, K, N, R, dt, path, impl, _opts(options))
         ws = _workspace(nbytes, dev)
-        rc = L.rdb_linear_bwd(_ptr(dx), _ptr(dc), _ptr(dy), _ptr(x), _ptr(coef), _ptr(ws), ws.numel(), T, K, N, R, row0,
-                              _seed(seed), dt, path, impl, _ptr(status_buffer(dev)), _stream(dev))
+        rc = L.rdb_linear_bwd_ex(_ptr(dx), _ptr(dc), _ptr(dy), _ptr(x), _ptr(coef), _ptr(ws), ws.numel(), T, K, N, R, row0,
+                                 _seed(seed), dt, path, impl, _opts(options), _ptr(status_buffer(dev)), _stream(dev))
     _lib.check(rc, "rdb_linear_bwd")
     return dx, dc
 
@@ -222,46 +240,63 @@ def gemm_noise(a: torch.Tensor, n: int, seed: int, transposed: bool = False, row
     return d
 
 
-def linear_stages_noise(T: int, K: int, N: int, R: int, dtype: torch.dtype, path: int = PATH_AUTO, impl: int = IMPL_AUTO) -> bool:
+def linear_stages_noise(T: int, K: int, N: int, R: int, dtype: torch.dtype, path: int = PATH_AUTO, impl: int = IMPL_AUTO,
+                        options: Optional[_lib.CallOptions] = None) -> bool:
     """Whether linear_fwd / linear_bwd would write S once into the workspace for this problem (see rdb_linear_stages_noise)."""
-    rc = _lib.lib().rdb_linear_stages_noise(int(T), int(K), int(N), int(R), _dt(dtype), path, impl)
+    rc = _lib.lib().rdb_linear_stages_noise_ex(int(T), int(K), int(N), int(R), _dt(dtype), path, impl, _opts(options))
     _lib.check(min(rc, 0), "rdb_linear_stages_noise")
     return rc == 1
 
 
-def noise_product(a: torch.Tensor, n: int, seed: int, transposed: bool = False, row0: int = 0) -> torch.Tensor:
+def linear_plan(T: int, K: int, N: int, R: int, dtype: torch.dtype, path: int = PATH_AUTO, impl: int = IMPL_AUTO) -> Tuple[int, int]:
+    """(association, kernels) the linear entry points would use: (PATH_FACTORED | PATH_WPATH, IMPL_SIMT | IMPL_UMMA)."""
+    rc = _lib.lib().rdb_linear_path(int(T), int(K), int(N), int(R), _dt(dtype), path, impl)
+    _lib.check(min(rc, 0), "rdb_linear_path")
+    return rc & 0xFF, rc >> 8
+
+
+def noise_product(a: torch.Tensor, n: int, seed: int, transposed: bool = False, row0: int = 0,
+                  options: Optional[_lib.CallOptions] = None) -> torch.Tensor:
     """``a @ S[row0:row0+n].T`` (``transposed=False``, a is [M, R]) or ``a @ S[row0:row0+Kc]`` (``transposed=True``, a is
     [M, Kc], result [M, n]) with the same rule as the linear entry points: bf16 problems with 1024 rows or more hash S
     once into a temporary and run the plain tensor-core product; everything else regenerates S inside the kernel."""
     M, Kc = a.shape
     rows, cols = (Kc, n) if transposed else (n, Kc)          # extent of the noise block S[rows, cols]
     ok8 = rows % 8 == 0 and cols % 8 == 0
-    if a.dtype == torch.bfloat16 and ok8 and linear_stages_noise(M, 8, rows, cols, a.dtype, PATH_FACTORED):
+    if a.dtype == torch.bfloat16 and ok8 and linear_stages_noise(M, 8, rows, cols, a.dtype, PATH_FACTORED, options=options):
         S = noise(rows, cols, seed, row0, 0, torch.bfloat16, a.device)
-        return gemm_dense(a, S, True, not transposed)
+        return gemm_dense(a, S, True, not transposed, options=options)
     return gemm_noise(a, n, seed, transposed, row0)
 
 
 def gemm_dense(a: torch.Tensor, b: torch.Tensor, a_kmajor: bool = True, b_kmajor: bool = True,
-               out_dtype: Optional[torch.dtype] = None, impl: int = IMPL_AUTO) -> torch.Tensor:
-    """D[M, N] = op(a) @ op(b).T; a is [M,Kc] (a_kmajor) or [Kc,M]; b is [N,Kc] (b_kmajor) or [Kc,N]."""
+               out_dtype: Optional[torch.dtype] = None, impl: int = IMPL_AUTO, options: Optional[_lib.CallOptions] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """D[M, N] = op(a) @ op(b).T; a is [M,Kc] (a_kmajor) or [Kc,M]; b is [N,Kc] (b_kmajor) or [Kc,N].
+    ``options``: per-call tuning switches (e.g. ``CallOptions(reserve_sms=32)`` for a launch that should leave SMs to a
+    collective); ``out``: a contiguous [M, N] tensor to write into instead of a fresh one."""
     dev = _need_cuda(a, b)
     assert a.dim() == 2 and b.dim() == 2 and a.is_contiguous() and b.is_contiguous()
     M, Kc = (a.shape[0], a.shape[1]) if a_kmajor else (a.shape[1], a.shape[0])
     N, Kb = (b.shape[0], b.shape[1]) if b_kmajor else (b.shape[1], b.shape[0])
     if Kc != Kb:
         raise RuntimeError("gemm_dense: contraction extents differ")
-    out_dtype = out_dtype or a.dtype
-    d = torch.empty((M, N), dtype=out_dtype, device=dev)
+    if out is not None:
+        if tuple(out.shape) != (M, N) or not out.is_contiguous() or out.device != dev:
+            raise RuntimeError(f"gemm_dense: out must be a contiguous [{M}, {N}] tensor on {dev}")
+        d, out_dtype = out, out.dtype
+    else:
+        out_dtype = out_dtype or a.dtype
+        d = torch.empty((M, N), dtype=out_dtype, device=dev)
     L = _lib.lib()
     with torch.cuda.device(dev):
         # few output tiles and a long contraction: scratch for split-K (float32 partial products, ordered sum)
         nbytes = L.rdb_gemm_dense_workspace_bytes(M, N, Kc) if impl != IMPL_SIMT and a.dtype == torch.bfloat16 else 0
         ws = _workspace(nbytes, dev) if nbytes else None
-        rc = L.rdb_gemm_dense_ws(_ptr(d), _ptr(a), _ptr(b), _ptr(ws), nbytes, M, N, Kc, a.shape[1], b.shape[1], N, _dt(a.dtype),
-                                 _dt(b.dtype), _dt(out_dtype), 1 if a_kmajor else 0, 1 if b_kmajor else 0, impl,
+        rc = L.rdb_gemm_dense_ex(_ptr(d), _ptr(a), _ptr(b), _ptr(ws), nbytes, M, N, Kc, a.shape[1], b.shape[1], N, _dt(a.dtype),
+                                 _dt(b.dtype), _dt(out_dtype), 1 if a_kmajor else 0, 1 if b_kmajor else 0, impl, _opts(options),
                                  _ptr(status_buffer(dev)), _stream(dev))
-    _lib.check(rc, "rdb_gemm_dense_ws")
+    _lib.check(rc, "rdb_gemm_dense_ex")
     return d
 
 

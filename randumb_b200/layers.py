@@ -62,7 +62,7 @@ class RandumbModuleMixin(nn.Module):
                 self._buffers[name] = CreateRandumbTensor(coef, buf.seed, buf.shape, scale_bias, buf.fused_bias, buf.row0)
 
     def init_rt_scale_bias(self, val: float = 0.0) -> None:
-        """One trainable scale per virtual buffer for the fused random bias, registered as
+        """One trainable scale per 1-D-form virtual buffer for the fused random bias, registered as
         ``<buffer>_scale_bias`` (reference: SillyLayers.py:116-120)."""
         for name, buf in list(self._buffers.items()):
             if isinstance(buf, RandumbTensor) and not buf.is_matrix_form:
@@ -70,6 +70,46 @@ class RandumbModuleMixin(nn.Module):
                 p = nn.Parameter(torch.tensor([val], dtype=coef.dtype, device=coef.device))
                 self.register_parameter(f"{name}_scale_bias", p)
                 self._buffers[name] = CreateRandumbTensor(coef, buf.seed, buf.shape, p, buf.fused_bias, buf.row0)
+
+    def _fan_in_std(self) -> float:
+        w = self._buffers["weight"]
+        fan_in = w.shape[1] if w.dim() == 2 else int(w.shape[1:].numel())
+        return kaiming_out_std(fan_in)
+
+    def init_zero_coef_uniform_bias(self) -> None:
+        """The reference layers' default start (SillyLayers.py:122-133): coefficient vectors zero, every
+        ``<buffer>_scale_bias`` equal to nn.Linear's uniform bound ``sqrt(3) * gain / sqrt(fan_in)``."""
+        self.init_rt_scale_bias(math.sqrt(3.0) * self._fan_in_std())
+        with torch.no_grad():
+            for name, buf in self._buffers.items():
+                if isinstance(buf, RandumbTensor) and not buf.is_matrix_form:
+                    getattr(self, f"{name}_coef").zero_()
+
+    def init_uniform_coef_zero_bias(self) -> None:
+        """The reference's alternative start (SillyLayers.py:135-138, 37-79): uniform coefficients whose variance
+        gives the virtual weight nn.Linear's default std, random-bias scales zero.  One generator seeded with the
+        layer's first seed draws the weight coefficients, then the bias coefficients."""
+        self.init_rt_scale_bias(0.0)
+        out_std = self._fan_in_std()
+        seed0 = self.seed[0] if isinstance(self.seed, (list, tuple)) else self.seed
+        coef_w = getattr(self, "weight_coef")
+        gen = torch.Generator(device=coef_w.device).manual_seed(int(seed0))
+        with torch.no_grad():
+            for name in ("weight", "bias"):
+                buf = self._buffers.get(name)
+                if isinstance(buf, RandumbTensor) and not buf.is_matrix_form:
+                    coef = getattr(self, f"{name}_coef")
+                    bound = math.sqrt(3.0) * coef_std_for(out_std, coef.shape[0])
+                    coef.uniform_(-bound, bound, generator=gen)
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        # The reference registers its virtual tensors as persistent buffers, so its checkpoints carry a dense copy of
+        # every weight and bias beside the coefficients (SillyLayers.py:207, 212).  Those copies are redundant here
+        # (the buffers are regenerated from seed + coefficients): drop them instead of failing on unexpected keys.
+        for name, buf in self._buffers.items():
+            if isinstance(buf, RandumbTensor):
+                state_dict.pop(prefix + name, None)
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
 
 
 class RandumbLinear(RandumbModuleMixin, nn.Module):
@@ -130,23 +170,25 @@ class RandumbLinear(RandumbModuleMixin, nn.Module):
 
 
 class SillyLinear(RandumbModuleMixin, nn.Module):
-    """Reference-convention linear layer: weight and bias are both RandumbTensors.
+    """The reference's linear layer (src/rten_cpp/SillyLayers.py:142-227): weight and bias are both RandumbTensors.
 
-    ``int_dim`` / ``seed``: list of two values or a generator (first for the weight, second for the
-    bias).  ``coef_form="matrix"`` (default) gives the weight the matrix-coefficient form (``weight_coef`` is
-    ``[int_dim[0], in_features]``, fused tensor-core operator); ``coef_form="vector"`` is the reference's own
-    layer: ``weight_coef`` is ``[int_dim[0]]`` and the weight is materialised by ``rten::materialize_fwd``
-    before a dense product.  The bias always has the 1-D coefficient form (``bias_coef`` is ``[int_dim[1]]``).
+    ``int_dim`` / ``seed``: list of two values or a generator (first for the weight, second for the bias).
+    With the default ``coef_form="vector"`` an unchanged reference call site gets the reference's layer: ``weight_coef``
+    is ``[int_dim[0]]``, ``bias_coef`` ``[int_dim[1]]``, one ``<name>_scale_bias`` parameter per virtual tensor, all
+    coefficients zero at the start and the scales equal to nn.Linear's uniform bound (``init_zero_coef_uniform_bias``,
+    SillyLayers.py:122-133, 218-221); ``rt_bias`` decides whether the fused random bias ``scale_bias * noise1d`` is
+    added when the tensors are materialised.  The forward is ``mat1 @ RT`` on the library's own kernels (``ops.rt_mm``).
+    A reference checkpoint loads into it (its dense ``weight`` / ``bias`` entries are ignored).
 
-    ``rt_bias`` adds the reference's fused random bias ``scale_bias * noise1d`` to every 1-D-form tensor of the
-    layer, with one trainable ``<name>_scale_bias`` each; the layer then starts from zero coefficients and a
-    uniform random weight of nn.Linear's default bound (reference ``init_zero_coef_uniform_bias``:
-    SillyLayers.py:122-133).
+    ``coef_form="matrix"`` is this library's extension: the weight takes the matrix-coefficient form
+    (``weight_coef`` is ``[int_dim[0], in_features]``, fused tensor-core operator, uniform start with the variance of
+    ``init_kaiming_uniform``, SillyLayers.py:37-79); the bias keeps the 1-D form.  ``RandumbLinear`` is the plain
+    module for that form.
     """
     num_seeds = 2
 
     def __init__(self, in_features: int, out_features: int, int_dim: Union[list, Generator], seed: Union[list, Generator],
-                 bias: bool = True, rt_bias: bool = False, device=None, dtype=None, coef_form: str = "matrix") -> None:
+                 bias: bool = True, rt_bias: bool = False, device=None, dtype=None, coef_form: str = "vector") -> None:
         super().__init__()
         if coef_form not in ("matrix", "vector"):
             raise ValueError(f"coef_form must be 'matrix' or 'vector', got {coef_form!r}")
@@ -167,28 +209,25 @@ class SillyLinear(RandumbModuleMixin, nn.Module):
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
-        """Uniform coefficients with the variance that gives the virtual weight nn.Linear's default std
-        (reference ``init_kaiming_uniform``: SillyLayers.py:37-79); with ``rt_bias`` the 1-D-form tensors start
-        from zero coefficients and a random-bias scale equal to nn.Linear's uniform bound instead."""
-        out_std = kaiming_out_std(self.in_features)
-        gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed[0] & 0x7FFFFFFFFFFFFFFF)
-        with torch.no_grad():
-            if self.rt_bias and self.coef_form == "vector":
-                self.weight_coef.zero_()
-            else:
-                bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[0])
+        self.init_zero_coef_uniform_bias()           # every 1-D-form tensor: zero coefficients, scale = uniform bound
+        if self.coef_form == "matrix":
+            out_std = kaiming_out_std(self.in_features)
+            gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed[0] & 0x7FFFFFFFFFFFFFFF)
+            bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[0])
+            with torch.no_grad():
                 self.weight_coef.uniform_(-bound, bound, generator=gen)
-            if self.bias is not None:
-                if self.rt_bias:
-                    self.bias_coef.zero_()
-                else:
-                    bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[1])
-                    self.bias_coef.uniform_(-bound, bound, generator=gen)
-        if self.rt_bias:
-            self.init_rt_scale_bias(math.sqrt(3.0) * out_std)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        return F.linear(input, self.weight, self.bias)
+        w = self.weight
+        if self.coef_form == "vector" and input.is_cuda:
+            # x @ W^T with W materialised by the library's kernel and multiplied by the library's own product kernels
+            # (the reference ends in a library GEMM here: RandumbTensor.py:942-946, 771-791)
+            lead = input.shape[:-1]
+            x2 = input.reshape(-1, self.in_features)
+            y = ops.rt_mm(x2, w._coef, [self.in_features, self.out_features], [1, self.in_features], w.seed, w.scale_bias,
+                          w.fused_bias).reshape(*lead, self.out_features)
+            return y if self.bias is None else y + self.bias.to(y.dtype)
+        return F.linear(input, w, self.bias)
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, int_dim={self.int_dim}, "
@@ -197,31 +236,47 @@ class SillyLinear(RandumbModuleMixin, nn.Module):
 
 class SillyEmbedding(RandumbModuleMixin, nn.Module):
     """Embedding table that is a RandumbTensor in the 1-D coefficient form (reference:
-    SillyLayers.py:301-366): ``forward(idx)`` regenerates only the looked-up rows, ``rten::embed_fwd``.
-    ``padding_idx`` is not supported, as in the reference."""
+    SillyLayers.py:301-366; same constructor arguments in the same order): ``forward(idx)`` regenerates only the
+    looked-up rows, ``rten::embed_fwd``.  ``padding_idx``, ``max_norm``, ``scale_grad_by_freq`` and ``sparse`` are
+    accepted and, as in the reference, not applied; ``rt_bias`` only registers the (zero) ``weight_scale_bias``
+    parameter -- the reference's lookup kernel does not add the random bias either (RandumbTensor.py:998-1057)."""
     num_seeds = 1
 
     def __init__(self, num_embeddings: int, embedding_dim: int, int_dim: Union[list, Generator], seed: Union[list, Generator],
-                 padding_idx: Optional[int] = None, _freeze: bool = False, device="cuda", dtype=None) -> None:
+                 rt_bias: bool = False, padding_idx: Optional[int] = None, max_norm: Optional[float] = None,
+                 norm_type: float = 2.0, scale_grad_by_freq: bool = False, sparse: bool = False,
+                 _weight: Optional[RandumbTensor] = None, _freeze: bool = False, device="cuda", dtype=None) -> None:
         super().__init__()
         assert padding_idx is None, "padding_idx not supported"
-        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        self.num_embeddings, self.embedding_dim, self.rt_bias = num_embeddings, embedding_dim, rt_bias
+        self.padding_idx, self.max_norm, self.norm_type = padding_idx, max_norm, norm_type
+        self.scale_grad_by_freq, self.sparse = scale_grad_by_freq, sparse
         self.int_dim = [next(int_dim) for _ in range(self.num_seeds)] if isinstance(int_dim, GeneratorType) else list(int_dim)
         self.seed = [next(seed) for _ in range(self.num_seeds)] if isinstance(seed, GeneratorType) else list(seed)
-        self.weight_coef = nn.Parameter(torch.empty(self.int_dim[0], dtype=dtype, device=device), requires_grad=not _freeze)
-        self.register_buffer("weight", CreateRandumbTensor(self.weight_coef, self.seed[0], (num_embeddings, embedding_dim)),
-                             persistent=False)
-        self.reset_parameters()
+        if _weight is None:
+            self.weight_coef = nn.Parameter(torch.empty(self.int_dim[0], dtype=dtype, device=device), requires_grad=not _freeze)
+            self.register_buffer("weight", CreateRandumbTensor(self.weight_coef, self.seed[0], (num_embeddings, embedding_dim)),
+                                 persistent=False)
+            self.reset_parameters()
+        else:
+            assert list(_weight.shape) == [num_embeddings, embedding_dim], \
+                f"Shape of weight {_weight.shape} does not match num_embeddings and embedding_dim"
+            self.register_buffer("weight", _weight, persistent=False)
+            self.weight_coef = _weight._coef
 
     def reset_parameters(self) -> None:
+        # reference: init_kaiming_uniform on the coefficient vector, generator seeded with the layer's seed
+        # (SillyLayers.py:362-365, 37-79); the (unused) scale starts at zero
+        if self.rt_bias:
+            self.init_rt_scale_bias(0.0)
         out_std = kaiming_out_std(self.embedding_dim)
-        gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed[0] & 0x7FFFFFFFFFFFFFFF)
+        gen = torch.Generator(device=self.weight_coef.device).manual_seed(int(self.seed[0]))
         with torch.no_grad():
             bound = math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[0])
             self.weight_coef.uniform_(-bound, bound, generator=gen)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        return ops.embed_fwd(input, self.weight_coef, self.embedding_dim, self.seed[0]).to(self.weight_coef.dtype)
+        return ops.embed_fwd(input, self.weight_coef, self.embedding_dim, self.weight.seed).to(self.weight_coef.dtype)
 
     def extra_repr(self) -> str:
         return f"{self.num_embeddings}, {self.embedding_dim}, int_dim={self.int_dim}, seeds={self.seed}"
@@ -230,7 +285,8 @@ class SillyEmbedding(RandumbModuleMixin, nn.Module):
 class SillyConv2d(RandumbModuleMixin, nn.Conv2d):
     """``nn.Conv2d`` whose weight ``[out, in/groups, kh, kw]`` and bias are RandumbTensors in the 1-D coefficient
     form (reference: SillyLayers.py:230-297); the convolution itself is PyTorch's, on the weight materialised for the
-    call by ``rten::materialize_fwd`` and dropped afterwards."""
+    call by ``rten::materialize_fwd`` and dropped afterwards.  Starts like the reference: zero coefficients, one
+    ``<name>_scale_bias`` per virtual tensor equal to the uniform bound; ``rt_bias`` switches the fused random bias on."""
     num_seeds = 2
 
     def __init__(self, in_channels: int, out_channels: int, int_dim: Union[list, Generator], seed: Union[list, Generator],
@@ -245,7 +301,6 @@ class SillyConv2d(RandumbModuleMixin, nn.Conv2d):
     def reset_parameters(self) -> None:
         # nn.Conv2d.__init__ has created dense parameters: keep their shapes, replace them by coefficient vectors
         w = self.weight
-        fan_in = w.shape[1] * w.shape[2] * w.shape[3]
         self.weight_coef = nn.Parameter(torch.empty(self.int_dim[0], dtype=w.dtype, device=w.device))
         wshape = tuple(w.shape)
         del self.weight
@@ -258,19 +313,7 @@ class SillyConv2d(RandumbModuleMixin, nn.Conv2d):
             del self.bias
             self.register_buffer("bias", CreateRandumbTensor(self.bias_coef, self.seed[1], bshape, fused_bias=self.rt_bias),
                                  persistent=False)
-        out_std = kaiming_out_std(fan_in)
-        gen = torch.Generator(device=self.weight_coef.device).manual_seed(self.seed[0] & 0x7FFFFFFFFFFFFFFF)
-        with torch.no_grad():
-            if self.rt_bias:
-                self.weight_coef.zero_()
-                if self.bias is not None:
-                    self.bias_coef.zero_()
-            else:
-                self.weight_coef.uniform_(-1, 1, generator=gen).mul_(math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[0]))
-                if self.bias is not None:
-                    self.bias_coef.uniform_(-1, 1, generator=gen).mul_(math.sqrt(3.0) * coef_std_for(out_std, self.int_dim[1]))
-        if self.rt_bias:
-            self.init_rt_scale_bias(math.sqrt(3.0) * out_std)
+        self.init_zero_coef_uniform_bias()
 
     def extra_repr(self) -> str:
         return super().extra_repr() + f", int_dim={self.int_dim}, seeds={self.seed}"

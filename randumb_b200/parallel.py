@@ -25,9 +25,16 @@ import torch.distributed as dist
 
 from . import _lib
 
-# SMs left without a CTA of the persistent product kernels while a collective runs beside them
-# (two GPUs, headline layer: 0 -> 0.640 ms per step, 16 -> 0.635, 32 -> 0.628)
-OVERLAP_SMS = int(os.environ.get("RANDUMB_B200_OVERLAP_SMS", "32"))
+def _overlap_sms() -> int:
+    """SMs left without a CTA of the persistent product kernels while a collective runs beside them; given to that one
+    launch as a per-call option.  ``RANDUMB_B200_OVERLAP_SMS`` overrides the default and must lie in the library's range."""
+    v = int(os.environ.get("RANDUMB_B200_OVERLAP_SMS", "32"))
+    if not 0 <= v <= _lib.MAX_RESERVE_SMS:
+        raise ValueError(f"RANDUMB_B200_OVERLAP_SMS={v} is outside 0..{_lib.MAX_RESERVE_SMS}")
+    return v
+
+
+OVERLAP_SMS = _overlap_sms()
 
 
 # ------------------------------------------------------------------------------------------------
@@ -230,11 +237,7 @@ def sharded_backward(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor
     if equal:
         dx = dx_loc.new_empty((sum(plan.tok_sizes), dx_loc.shape[1]))
         work_dx = dist.all_gather_into_tensor(dx, dx_loc, group=group, async_op=True)
-        prev = K.set_option(_lib.OPT_RESERVE_SMS, OVERLAP_SMS)
-        try:
-            dc = K.gemm_dense(g_loc, x_loc, False, False)                                     # partial [R, K]
-        finally:
-            K.set_option(_lib.OPT_RESERVE_SMS, prev)
+        dc = K.gemm_dense(g_loc, x_loc, False, False, options=_lib.CallOptions(reserve_sms=OVERLAP_SMS))   # partial [R, K]
         dist.all_reduce(dc, group=group)
         work_dx.wait()
     else:
@@ -263,12 +266,9 @@ def data_parallel_backward(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         work = dist.all_reduce(dc, op=dist.ReduceOp.SUM, group=group, async_op=True)
     # the product kernels are persistent, one CTA per SM: leave a few SMs to the collective or it waits for them to retire
-    prev = K.set_option(_lib.OPT_RESERVE_SMS, OVERLAP_SMS) if work is not None else None
-    try:
-        dx = K.gemm_dense(g, coef, True, False)                                               # [T, K]
-    finally:
-        if prev is not None:
-            K.set_option(_lib.OPT_RESERVE_SMS, prev)
+    # (an option of this one launch: no process state changes, other threads' launches are not affected)
+    dx = K.gemm_dense(g, coef, True, False,
+                      options=_lib.CallOptions(reserve_sms=OVERLAP_SMS) if work is not None else None)   # [T, K]
     if work is not None:
         work.wait()                       # makes the current stream wait for the reduction; the host does not block
         if average:

@@ -175,6 +175,55 @@ def main():
     np.savez_compressed(dst, **out)
     print("wrote", dst, {k: v.shape for k, v in out.items()})
 
+    write_module_fixture(root)
+
+
+# constructor cases of the reference's modules; "args" are passed positionally after the generators are built
+MODULE_CASES = [
+    ("SillyLinear", dict(args=[12, 20], int_dim=("listgen", [6, 4]), seed=("stepgen", 3, 2), kwargs={})),
+    ("SillyLinear", dict(args=[12, 20], int_dim=("list", [6, 4]), seed=("list", [3, 5]), kwargs={"bias": False, "rt_bias": True})),
+    ("SillyLinear", dict(args=[768, 3072], int_dim=("stepgen", 256, 0), seed=("stepgen", 13, 7), kwargs={"bias": False})),
+    ("SillyConv2d", dict(args=[3, 8], int_dim=("list", [16, 4]), seed=("list", [5, 6]), kwargs={"kernel_size": 3, "padding": 1})),
+    ("SillyConv2d", dict(args=[1, 32], int_dim=("stepgen", 128, 0), seed=("stepgen", 5, 4), kwargs={"kernel_size": 3, "stride": 1, "rt_bias": True})),
+    ("SillyEmbedding", dict(args=[100, 16], int_dim=("list", [8]), seed=("stepgen", 9, 1), kwargs={"device": "cpu"})),
+    ("SillyEmbedding", dict(args=[100, 16], int_dim=("list", [8]), seed=("stepgen", 9, 1), kwargs={"rt_bias": True, "device": "cpu"})),
+]
+
+
+def build_module(layers, cls_name, case):
+    """Construct ``cls_name`` from a MODULE_CASES entry with the generators of ``layers`` (the reference's module
+    file, or the library under test: both export stepgen / listgen and the three classes)."""
+    def gen(spec):
+        kind = spec[0]
+        if kind == "list":
+            return list(spec[1])
+        if kind == "listgen":
+            return layers.listgen(list(spec[1]))
+        return layers.stepgen(spec[1], spec[2])
+    return getattr(layers, cls_name)(*case["args"], gen(case["int_dim"]), gen(case["seed"]), **case["kwargs"])
+
+
+def write_module_fixture(root):
+    """Parameter names, shapes and initial values of the reference's modules for MODULE_CASES, constructed on CPU
+    (src/rten_cpp/SillyLayers.py); virtual tensors are listed by buffer name."""
+    import json
+    pkg_dir = os.path.join(root, "src", "rten_cpp")
+    spec = importlib.util.spec_from_file_location("rten_ref.SillyLayers", os.path.join(pkg_dir, "SillyLayers.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["rten_ref.SillyLayers"] = mod
+    spec.loader.exec_module(mod)
+    records = []
+    for cls_name, case in MODULE_CASES:
+        m = build_module(mod, cls_name, case)
+        params = {n: {"shape": list(p.shape), "head": [float(v) for v in p.detach().flatten()[:8]],
+                      "abs_sum": float(p.detach().abs().sum())} for n, p in m.named_parameters()}
+        records.append({"cls": cls_name, "case": case, "params": params, "buffers": [n for n, _ in m.named_buffers()],
+                        "seed": list(m.seed), "int_dim": list(m.int_dim)})
+    dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_modules.json")
+    with open(dst, "w") as f:
+        json.dump(records, f, indent=1)
+    print("wrote", dst, len(records), "module cases")
+
 
 if __name__ == "__main__":
     main()

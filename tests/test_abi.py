@@ -53,6 +53,68 @@ def test_argument_errors_are_caught_on_host(built_lib):
     assert L.rdb_set_option(99, 1) == -6
 
 
+def test_options_are_validated_and_per_call(built_lib):
+    L = _lib.lib()
+    # process defaults: a value out of range is refused and nothing changes
+    assert L.rdb_set_option(_lib.OPT_RESERVE_SMS, 16) == 0
+    assert L.rdb_set_option(_lib.OPT_RESERVE_SMS, _lib.MAX_RESERVE_SMS + 1) == -6
+    assert L.rdb_set_option(_lib.OPT_RESERVE_SMS, 0) == 16
+    assert L.rdb_set_option(_lib.OPT_FILL_OVERLAP, 2) == -6 and L.rdb_set_option(_lib.OPT_FILL_OVERLAP, 1) == 1
+    # per-call options override the default for that call only, and are validated the same way
+    stage_off = _lib.CallOptions(stage_noise=1)
+    zg, S = 8192 * 1024 * 2, 16384 * 1024 * 2
+    assert L.rdb_linear_workspace_bytes_ex(0, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0, ctypes.byref(stage_off)) == zg
+    assert L.rdb_linear_workspace_bytes(0, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == zg + S
+    assert L.rdb_linear_stages_noise_ex(8192, 4096, 16384, 1024, _lib.BF16, 0, 0, ctypes.byref(stage_off)) == 0
+    bad = _lib.CallOptions(reserve_sms=1000)
+    assert L.rdb_linear_stages_noise_ex(8192, 4096, 16384, 1024, _lib.BF16, 0, 0, ctypes.byref(bad)) == -6
+    assert L.rdb_linear_fwd_ex(None, None, None, None, 0, 4, 4, 4, 4, 0, 0, 0, 0, 0, ctypes.byref(bad), None, None) == -6
+    assert L.rdb_gemm_dense_ex(None, None, None, None, 0, 4, 4, 4, 4, 4, 4, 0, 0, 0, 1, 1, 0, ctypes.byref(bad), None, None) == -6
+
+
+def test_unaligned_operands_are_caught_on_host(built_lib):
+    """The tensor-core kernels address their operands through TMA, which needs 16-byte aligned bases.  With RDB_IMPL_UMMA an
+    operand at an odd offset is an alignment error; with RDB_IMPL_AUTO the call goes to the CUDA-core kernels, which then ask
+    for their own (larger) workspace.  Both answers come from the host checks: the pointers are never dereferenced."""
+    L = _lib.lib()
+    T, K, N, R = 64, 128, 256, 64
+    ok, odd, ws = 0x7F0000001000, 0x7F0000001000 + 8, 0x7F0000100000
+    big = 1 << 30
+    args = (ws, big, T, K, N, R, 0, 0, _lib.BF16, _lib.PATH_FACTORED)
+    assert L.rdb_linear_fwd(ok, odd, ok, *args, _lib.IMPL_UMMA, None, None) == -4
+    assert L.rdb_linear_fwd(odd, ok, ok, *args, _lib.IMPL_UMMA, None, None) == -4
+    assert L.rdb_linear_fwd(ok, ok, odd, *args, _lib.IMPL_UMMA, None, None) == -4
+    assert L.rdb_linear_bwd(ok, ok, odd, ok, ok, *args, _lib.IMPL_UMMA, None, None) == -4
+    assert L.rdb_linear_bwd(odd, None, ok, ok, ok, *args, _lib.IMPL_UMMA, None, None) == -4
+    assert "16-byte" in _lib.strerror(-4)
+    # AUTO: falls back to the CUDA-core layout (float32 z: T*R*4 bytes), so a workspace sized for the bf16 kernels is refused
+    umma_ws = L.rdb_linear_workspace_bytes(0, T, K, N, R, _lib.BF16, _lib.PATH_FACTORED, _lib.IMPL_AUTO)
+    simt_ws = L.rdb_linear_workspace_bytes(0, T, K, N, R, _lib.BF16, _lib.PATH_FACTORED, _lib.IMPL_SIMT)
+    assert umma_ws == T * R * 2 and simt_ws == T * R * 4
+    assert L.rdb_linear_fwd(ok, odd, ok, ws, umma_ws, T, K, N, R, 0, 0, _lib.BF16, _lib.PATH_FACTORED, _lib.IMPL_AUTO, None, None) == -5
+
+
+def test_association_and_kernel_decision_table(built_lib):
+    """rdb_linear_path: FLOP rule for the association, tcgen05 kernels for every bf16 problem with extents in multiples of 8
+    -- both associations run on them, so a large-d_c problem that prefers the W path keeps the tensor cores."""
+    L = _lib.lib()
+    F, W, SIMT, UMMA = _lib.PATH_FACTORED, _lib.PATH_WPATH, _lib.IMPL_SIMT, _lib.IMPL_UMMA
+    plan = lambda T, K, N, R, dt, path=0, impl=0: (lambda rc: (rc & 0xFF, rc >> 8) if rc >= 0 else rc)(L.rdb_linear_path(T, K, N, R, dt, path, impl))
+    assert plan(8192, 4096, 16384, 1024, _lib.BF16) == (F, UMMA)          # headline layer
+    assert plan(4096, 16384, 65536, 2048, _lib.BF16) == (F, UMMA)         # row-sharded layer
+    assert plan(8192, 768, 3072, 128, _lib.BF16) == (F, UMMA)             # GPT-2-small MLP
+    assert plan(64, 784, 256, 64, _lib.F32) == (F, SIMT) and plan(64, 256, 10, 64, _lib.F32) == (W, SIMT)   # MNIST-shaped
+    assert plan(8192, 4096, 4096, 4096, _lib.BF16) == (W, UMMA)           # large d_c: fewer FLOPs through W, still tensor cores
+    assert plan(4096, 1024, 1024, 1024, _lib.BF16) == (W, UMMA)
+    assert plan(4096, 1024, 1024, 1024, _lib.BF16, F) == (F, UMMA) and plan(4096, 1024, 1024, 1024, _lib.BF16, 0, SIMT) == (W, SIMT)
+    assert plan(64, 250, 10, 64, _lib.BF16) == (W, SIMT)                  # extents not in multiples of 8
+    assert plan(64, 250, 10, 64, _lib.BF16, 0, UMMA) == -6
+    # W-path workspace on the tensor cores: S and W (and dW in backward), bf16
+    n, k, r = 4096, 4096, 4096
+    assert L.rdb_linear_workspace_bytes(0, 8192, k, n, r, _lib.BF16, 0, 0) == n * r * 2 + n * k * 2
+    assert L.rdb_linear_workspace_bytes(1, 8192, k, n, r, _lib.BF16, 0, 0) == n * r * 2 + 2 * n * k * 2
+
+
 def test_workspace_sizes(built_lib):
     L = _lib.lib()
     # bf16 factored on tensor cores: z or g, bf16 [T, R], plus S bf16 [N, R] when the noise operand is staged

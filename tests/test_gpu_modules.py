@@ -90,7 +90,10 @@ def test_reference_form_tensor(rb, golden):
 
 def test_silly_linear_with_pseudorandom_bias(rb):
     torch.manual_seed(0)
-    m = rb.SillyLinear(32, 48, rb.stepgen(8, 0), rb.stepgen(13, 7)).cuda()
+    m = rb.SillyLinear(32, 48, rb.stepgen(8, 0), rb.stepgen(13, 7), coef_form="matrix")
+    with torch.no_grad():
+        m.bias_coef.uniform_(-0.3, 0.3)        # 1-D-form tensors start from zero coefficients
+    m = m.cuda()
     assert m.weight.device.type == "cuda" and m.weight._coef is m.weight_coef
     x = torch.randn(5, 32, device="cuda")
     y = m(x)

@@ -69,7 +69,7 @@ def test_constructor_backward_returns_scale_gradient(rb, golden):
 def test_silly_linear_vector_form_with_rt_bias(rb):
     """The reference's own layer: 1-D coefficients for weight and bias, zero coefficients and a random-bias
     scale at initialisation, so the layer starts as a fixed random projection."""
-    m = rb.SillyLinear(32, 48, [16, 8], [13, 20], rt_bias=True, coef_form="vector").cuda()
+    m = rb.SillyLinear(32, 48, [16, 8], [13, 20], rt_bias=True).cuda()           # the default form is the reference's
     names = dict(m.named_parameters())
     assert set(names) == {"weight_coef", "bias_coef", "weight_scale_bias", "bias_scale_bias"}
     assert m.weight_coef.shape == (16,) and float(m.weight_coef.abs().sum()) == 0.0
@@ -153,7 +153,10 @@ def test_silly_conv2d_step(rb):
     """Convolution with a storage-less weight [out, in, kh, kw] and bias: forward and every gradient against the same
     convolution with the oracle's dense weight."""
     torch.manual_seed(0)
-    m = rb.SillyConv2d(3, 8, [16, 4], [5, 6], 3, padding=1).cuda()
+    m = rb.SillyConv2d(3, 8, [16, 4], [5, 6], 3, padding=1)
+    m.init_uniform_coef_zero_bias()            # the default start is all-zero coefficients; use the reference's other scheme
+    m = m.cuda()
+    assert float(m.weight_coef.abs().sum()) > 0 and not m.weight.fused_bias
     x = torch.randn(2, 3, 10, 10, device="cuda", requires_grad=True)
     y = m(x)
     Wc = m.weight_coef.detach().double().cpu().requires_grad_(True)

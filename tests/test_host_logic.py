@@ -1,6 +1,7 @@
 """Host-side mirror of the reference interface: operator schemas, the tensor subclass's metadata
 handling, module conventions, sharding arithmetic.  CPU only -- no kernel runs here."""
 import math
+import os
 
 import pytest
 import torch
@@ -8,6 +9,8 @@ import torch
 import randumb_b200 as rb
 from randumb_b200 import parallel
 from randumb_b200.tensor import RandumbTensor
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_operator_schemas_match_reference_names():
@@ -92,13 +95,58 @@ def test_randumb_linear_init_and_state():
 
 
 def test_silly_linear_conventions():
+    # an unchanged reference call site: generators for int_dim and seed, 1-D coefficient vectors
     s = rb.SillyLinear(16, 24, rb.stepgen(8, 0), rb.stepgen(13, 7))
-    assert s.int_dim == [8, 8] and s.seed == [13, 20]
-    assert s.weight_coef.shape == (8, 16) and s.bias_coef.shape == (8,)
-    assert s.weight.seed == 13 and s.bias.seed == 20 and not s.bias.is_matrix_form
-    assert {n for n, _ in s.named_parameters()} == {"weight_coef", "bias_coef"}
+    assert s.int_dim == [8, 8] and s.seed == [13, 20] and s.coef_form == "vector"
+    assert s.weight_coef.shape == (8,) and s.bias_coef.shape == (8,)
+    assert s.weight.seed == 13 and s.bias.seed == 20 and not s.weight.is_matrix_form and not s.bias.is_matrix_form
+    assert {n for n, _ in s.named_parameters()} == {"weight_coef", "bias_coef", "weight_scale_bias", "bias_scale_bias"}
+    assert not s.weight.fused_bias and s.weight.scale_bias is s.weight_scale_bias
     s2 = rb.SillyLinear(16, 24, [4, 2], [1, 2], bias=False)
     assert s2.bias is None
+    # the matrix-coefficient form is opt-in
+    s3 = rb.SillyLinear(16, 24, [4, 2], [1, 2], coef_form="matrix")
+    assert s3.weight_coef.shape == (4, 16) and s3.weight.is_matrix_form and float(s3.weight_coef.detach().abs().sum()) > 0
+    assert {n for n, _ in s3.named_parameters()} == {"weight_coef", "bias_coef", "bias_scale_bias"}
+
+
+def _build_from_case(cls_name, case):
+    def gen(spec):
+        if spec[0] == "list":
+            return list(spec[1])
+        if spec[0] == "listgen":
+            return rb.listgen(list(spec[1]))
+        return rb.stepgen(spec[1], spec[2])
+    return getattr(rb, cls_name)(*case["args"], gen(case["int_dim"]), gen(case["seed"]), **case["kwargs"])
+
+
+def test_modules_match_the_reference_classes_parameter_for_parameter():
+    """tests/golden/ref_modules.json holds, for a list of constructor calls, what the reference's own classes create on
+    CPU (written by tests/golden/make_golden.py): parameter names, shapes, initial values, buffer names, seeds.  The
+    same calls on this library's classes must give the same state_dict keys and shapes, so a reference checkpoint
+    loads, and the same initial values."""
+    import json
+    with open(os.path.join(ROOT, "tests", "golden", "ref_modules.json")) as f:
+        records = json.load(f)
+    assert len(records) >= 7
+    for rec in records:
+        m = _build_from_case(rec["cls"], rec["case"])
+        ours = dict(m.named_parameters())
+        assert set(ours) == set(rec["params"]), (rec["cls"], rec["case"], sorted(ours))
+        assert list(m.seed) == rec["seed"] and list(m.int_dim) == rec["int_dim"]
+        assert sorted(n for n, _ in m.named_buffers()) == sorted(rec["buffers"])
+        for name, want in rec["params"].items():
+            p = ours[name].detach()
+            assert list(p.shape) == want["shape"], (rec["cls"], name)
+            assert [float(v) for v in p.flatten()[:8]] == want["head"], (rec["cls"], name)
+            assert abs(float(p.abs().sum()) - want["abs_sum"]) <= 1e-6 * max(1.0, want["abs_sum"])
+        # a checkpoint written by the reference: the parameters plus a dense copy of every virtual tensor
+        sd = {n: torch.full(want["shape"], 0.5) for n, want in rec["params"].items()}
+        for b in rec["buffers"]:
+            sd[b] = torch.zeros(tuple(getattr(m, b).shape))
+        m.load_state_dict(sd)
+        assert all(float(p.detach().flatten()[0]) == 0.5 for p in m.parameters())
+        assert set(m.state_dict()) == set(rec["params"])            # virtual tensors are regenerated, never stored
 
 
 @pytest.mark.parametrize("total,world", [(65536, 8), (16384, 4), (1000, 3), (8, 8), (10, 4), (0, 2)])
@@ -133,13 +181,16 @@ def test_vector_form_operator_schemas_and_cpu_stubs():
 
 def test_reference_convention_modules_on_cpu():
     """Parameters, buffers and the random-bias scales of the reference-style layers (construction only)."""
-    m = rb.SillyLinear(12, 20, rb.listgen([6, 4]), rb.stepgen(3, 2), rt_bias=True, coef_form="vector")
+    m = rb.SillyLinear(12, 20, rb.listgen([6, 4]), rb.stepgen(3, 2), rt_bias=True)
     assert m.seed == [3, 5] and m.int_dim == [6, 4]
     assert {n for n, _ in m.named_parameters()} == {"weight_coef", "bias_coef", "weight_scale_bias", "bias_scale_bias"}
     assert m.weight.fused_bias and m.weight.scale_bias is m.weight_scale_bias and not m.weight.is_matrix_form
     assert abs(float(m.bias_scale_bias.detach()) - 1.0 / math.sqrt(12)) < 1e-6 and float(m.weight_coef.detach().abs().sum()) == 0.0
     assert list(m.state_dict()) == ["weight_coef", "bias_coef", "weight_scale_bias", "bias_scale_bias"]   # virtual tensors are not stored
-    mm = rb.SillyLinear(12, 20, [6, 4], [3, 5], rt_bias=True)           # matrix-form weight: only the bias has a scale
+    m.init_uniform_coef_zero_bias()                                     # the reference's other start
+    assert float(m.weight_coef.detach().abs().sum()) > 0 and float(m.weight_scale_bias.detach()) == 0.0
+    assert m.weight.scale_bias is m.weight_scale_bias
+    mm = rb.SillyLinear(12, 20, [6, 4], [3, 5], rt_bias=True, coef_form="matrix")   # matrix-form weight: only the bias has a scale
     assert mm.weight.is_matrix_form and {n for n, _ in mm.named_parameters()} == {"weight_coef", "bias_coef", "bias_scale_bias"}
     with pytest.raises(ValueError):
         rb.SillyLinear(4, 4, [2, 2], [0, 1], coef_form="dense")
@@ -149,4 +200,24 @@ def test_reference_convention_modules_on_cpu():
         rb.SillyEmbedding(10, 4, [2], [0], padding_idx=0, device="cpu")
     c = rb.SillyConv2d(3, 8, [16, 4], [5, 6], 3, padding=1)
     assert tuple(c.weight.shape) == (8, 3, 3, 3) and c.weight.noise_matrix_shape == (216, 16) and c.bias.shape == (8,)
-    assert {n for n, _ in c.named_parameters()} == {"weight_coef", "bias_coef"}
+    assert {n for n, _ in c.named_parameters()} == {"weight_coef", "bias_coef", "weight_scale_bias", "bias_scale_bias"}
+
+
+def test_a_status_word_set_by_a_kernel_raises_and_is_cleared():
+    """The host half of the bounded waits: a kernel whose wait expires writes a code into the per-device status words;
+    ``kernels.check_status`` turns it into an exception and clears the words.  The code is injected here on the host (a CPU
+    tensor stands in for the device words) -- no device wait is made to expire."""
+    from randumb_b200 import kernels as K, _lib
+    saved = dict(K._status_bufs)
+    try:
+        for code, text in ((2, "mma wait expired"), (4, "generator wait expired"), (5, "peer wait expired")):
+            K._status_bufs.clear()
+            K._status_bufs[0] = torch.tensor([code, 0, 0, 0], dtype=torch.int32)
+            with pytest.raises(RuntimeError, match=text):
+                K.check_status()
+            assert K._status_bufs[0].tolist() == [0, 0, 0, 0]
+            K.check_status()                          # clean again
+        assert set(_lib.STATUS_NAMES) >= {0, 1, 2, 3, 4, 5}
+    finally:
+        K._status_bufs.clear()
+        K._status_bufs.update(saved)
