@@ -323,9 +323,9 @@ def test_partial_backward_and_graph_replay(K, T, Kin, N, R):
     K.check_status()
 
 
-# ---- full benchmark size: properties that do not need the oracle at that size ---------------------------
+# ---- full benchmark sizes ------------------------------------------------------------------------------------------
 def test_full_size_properties(K):
-    """8192 x 4096 -> 16384, d_c = 1024 (the headline configuration)."""
+    """8192 x 4096 -> 16384, d_c = 1024 (the headline configuration): size-independent properties."""
     T, Kin, N, R, seed = 8192, 4096, 16384, 1024, 42
     g = torch.Generator(device="cuda").manual_seed(3)
     x = torch.randn(T, Kin, device="cuda", generator=g).bfloat16()
@@ -348,6 +348,112 @@ def test_full_size_properties(K):
     # (3) token shards reproduce the full result exactly (tiles do not interact across tokens)
     y_half = K.linear_fwd(x[:4096].contiguous(), C, seed, N)
     assert torch.equal(y_half, y[:4096])
+
+
+def _close_big(got, want, tol):
+    """The two tests of O.close on tensors too large to hold several float64 copies of: rel-Frobenius <= tol and
+    |a - b| <= tol * |b| + tol * rms(b) everywhere, evaluated in row chunks in float32 with float64 sums."""
+    want = want.detach()
+    got = got.detach().cpu()
+    assert got.shape == want.shape
+    num = den = 0.0
+    for lo in range(0, want.shape[0], 1024):
+        b = want[lo:lo + 1024].double()
+        num += float(((got[lo:lo + 1024].double() - b) ** 2).sum())
+        den += float((b ** 2).sum())
+    rms = (den / want.numel()) ** 0.5
+    worst = 0.0
+    for lo in range(0, want.shape[0], 1024):
+        b = want[lo:lo + 1024].float()
+        excess = (got[lo:lo + 1024].float() - b).abs() - (tol * b.abs() + tol * rms)
+        worst = max(worst, float(excess.max()))
+    rel = (num / max(den, 1e-300)) ** 0.5
+    return rel <= tol and worst <= 0.0, rel, worst
+
+
+def test_headline_size_elementwise_against_the_oracle(K):
+    """The headline configuration at full size (x[8192 x 4096] bf16, W[16384 x 4096], d_c = 1024, seed 42): every element of
+    y, dX and dC against the float32 oracle on the same bf16-rounded inputs (both 2e-2 tests)."""
+    T, Kin, N, R, seed = 8192, 4096, 16384, 1024, 42
+    g = torch.Generator().manual_seed(1003)
+    x = torch.randn(T, Kin, generator=g).bfloat16()
+    C = (torch.randn(R, Kin, generator=g) * (3 * 0.02 ** 2 / R) ** 0.5).bfloat16()
+    dy = torch.randn(T, N, generator=g).bfloat16()
+    torch.set_num_threads(max(torch.get_num_threads(), 8))
+    S = torch.from_numpy(O.c_noise_f32(N, R, seed))
+    W = S @ C.float()                                            # [N, K]
+    xg, Cg, dyg = x.cuda(), C.cuda(), dy.cuda()
+    y = K.linear_fwd(xg, Cg, seed, N)
+    dx, dc = K.linear_bwd(dyg, xg, Cg, seed)
+    torch.cuda.synchronize()
+    K.check_status()
+    ok, rel, worst = _close_big(y, x.float() @ W.t(), BF16_TOL)
+    assert ok, f"y rel {rel:.3e} worst excess {worst:.3e}"
+    ok, rel, worst = _close_big(dx, dy.float() @ W, BF16_TOL)
+    assert ok, f"dx rel {rel:.3e} worst excess {worst:.3e}"
+    dW = dy.float().t() @ x.float()                              # [N, K]
+    ok, rel, worst = _close_big(dc, S.t() @ dW, BF16_TOL)
+    assert ok, f"dc rel {rel:.3e} worst excess {worst:.3e}"
+
+
+@pytest.mark.parametrize("stage", [2, 1])
+def test_one_shard_of_the_row_sharded_layer_against_the_oracle(K, stage):
+    """One rank's part of the 65536 x 16384 virtual layer split over 8 ranks (x[4096 x 16384] bf16, d_c = 2048, seed 7):
+    rows [57344, 65536).  y, and this rank's contributions to dX and dC, element by element against the float32 oracle;
+    once with S hashed into the workspace (2) and once regenerated inside the product kernels (1)."""
+    from randumb_b200 import _lib
+    T, Kin, N, R, seed, n_loc, row0 = 4096, 16384, 65536, 2048, 7, 8192, 57344
+    g = torch.Generator().manual_seed(1005)
+    x = torch.randn(T, Kin, generator=g).bfloat16()
+    C = (torch.randn(R, Kin, generator=g) * (3 * 0.02 ** 2 / R) ** 0.5).bfloat16()
+    dy = torch.randn(T, n_loc, generator=g).bfloat16()
+    torch.set_num_threads(max(torch.get_num_threads(), 8))
+    S = torch.from_numpy(O.c_noise_f32(n_loc, R, seed, row0=row0))
+    W = S @ C.float()                                            # [n_loc, K]
+    opts = _lib.CallOptions(stage_noise=stage)
+    assert K.linear_stages_noise(T, Kin, n_loc, R, torch.bfloat16, options=opts) == (stage == 2)
+    xg, Cg, dyg = x.cuda(), C.cuda(), dy.cuda()
+    y = K.linear_fwd(xg, Cg, seed, n_loc, row0, options=opts)
+    dx, dc = K.linear_bwd(dyg, xg, Cg, seed, row0, options=opts)
+    torch.cuda.synchronize()
+    K.check_status()
+    ok, rel, worst = _close_big(y, x.float() @ W.t(), BF16_TOL)
+    assert ok, f"y rel {rel:.3e} worst excess {worst:.3e}"
+    ok, rel, worst = _close_big(dx, dy.float() @ W, BF16_TOL)
+    assert ok, f"dx rel {rel:.3e} worst excess {worst:.3e}"
+    dW = dy.float().t() @ x.float()                              # [n_loc, K]
+    ok, rel, worst = _close_big(dc, S.t() @ dW, BF16_TOL)
+    assert ok, f"dc rel {rel:.3e} worst excess {worst:.3e}"
+
+
+# ---- the W path on the tensor-core kernels ---------------------------------------------------------------------------
+@pytest.mark.parametrize("T,Kin,N,R,seed,row0", [(4096, 1024, 1024, 1024, 3, 0), (1000, 264, 136, 520, 11, 40)])
+def test_bf16_w_path_on_tensor_cores(K, T, Kin, N, R, seed, row0):
+    """Large d_c: fewer FLOPs through W = S C.  AUTO picks that association and the tcgen05 kernels for it (S hashed once,
+    W bf16 in the workspace, plain tensor-core products); the forced call and the CUDA-core W path agree."""
+    from randumb_b200 import _lib
+    assert K.linear_plan(T, Kin, N, R, torch.bfloat16) == (_lib.PATH_WPATH, _lib.IMPL_UMMA)
+    _check(K, T, Kin, N, R, torch.bfloat16, seed, row0, K.PATH_AUTO, K.IMPL_AUTO, BF16_TOL)
+    _check(K, T, Kin, N, R, torch.bfloat16, seed, row0, K.PATH_WPATH, K.IMPL_UMMA, BF16_TOL)
+    _check(K, T, Kin, N, R, torch.bfloat16, seed, row0, K.PATH_WPATH, K.IMPL_SIMT, BF16_TOL)
+
+
+def test_unaligned_views_fall_back_to_cuda_cores(K):
+    """bf16 operands that start 8 bytes into an allocation cannot be addressed by TMA: AUTO runs the CUDA-core kernels
+    (same results within tolerance), a forced tensor-core call is an alignment error."""
+    T, Kin, N, R, seed = 96, 128, 256, 64, 5
+    x, C, dy = _inputs(T, Kin, N, R, torch.bfloat16, seed)
+    buf = torch.empty(T * Kin + 4, dtype=torch.bfloat16, device="cuda")
+    xv = buf[4:].view(T, Kin)
+    xv.copy_(x)
+    assert xv.data_ptr() % 16 == 8 and xv.is_contiguous()
+    y_ref, dx_ref, dc_ref = O.linear_reference(x, C, seed, N, 0, dy, dtype=torch.float32)
+    y = K.linear_fwd(xv, C.cuda(), seed, N)
+    dx, dc = K.linear_bwd(dy.cuda(), xv, C.cuda(), seed)
+    torch.cuda.synchronize()
+    assert O.close(y, y_ref, BF16_TOL) and O.close(dx, dx_ref, BF16_TOL) and O.close(dc, dc_ref, BF16_TOL)
+    with pytest.raises(RuntimeError, match="16-byte"):
+        K.linear_fwd(xv, C.cuda(), seed, N, impl=K.IMPL_UMMA)
 
 
 # ---- the reference's 1-D coefficient form -------------------------------------------------------------------
