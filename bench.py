@@ -2,7 +2,8 @@
 """Benchmark of the fused pseudorandom-weight matmul (forward + dX + dC) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemm|sharded|gemv|gpt2mlp]
-                    [--gather-output] [--replicate-grads] [--no-graph] [--no-cpu-baseline]
+                    [--gather-output] [--replicate-grads] [--no-graph] [--no-cpu-baseline] [--no-sharded-record]
+                    [--exchange peer|nccl] [--profile-case noise|staged|roles|products|gemv ...]
 
 One step = one forward + backward pass of the layer over one batch of seeded synthetic input.
 Default workload ("gemm"): x bf16 [8192 x 4096], virtual W [16384 x 4096], d_c = 1024, seed 42, float32
@@ -15,6 +16,12 @@ over the ranks (strong scaling; by default y, dX and dC stay sharded, `--gather-
 `--replicate-grads` gives every rank the full dX and dC); `--workload gemv` the batch-1 float32 4096 x 4096 layer
 (the step replayed as a CUDA graph unless `--no-graph`); `--workload gpt2mlp` the 24 pseudorandom-weight layers of
 GPT-2 small's MLPs (768 <-> 3072, d_c = 128), data parallel with one flat all-reduce of their dC.
+
+The default line also carries a `sharded` sub-record: the row-sharded 65536 x 16384 layer measured right after the headline
+in the same process on the same N GPUs (value, ms per step, speed-up over one GPU measured in the same run, device time of
+each phase, and the figure with y all-gathered), so one `bench.py --gpus N` run per N gives both scaling curves.
+
+`--profile-case X` runs a small, self-terminating case for a profiler instead of the benchmark (see profile_case()).
 
 Prints ONE JSON line (rank 0).  `--impl reference` times the reference's CPU PyTorch path (explicit noise
 matrix, W = S @ C, F.linear, autograd) on the host cores instead; it never touches the GPU kernels.
@@ -190,7 +197,9 @@ def run_reference(args, cfg):
         "impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.workload, cfg, args.gpus, args.replicate_grads, args.gather_output),
+        "config": dict(workload_config(args.workload, cfg, args.gpus, args.replicate_grads, args.gather_output),
+                       parallelism=f"ONE host process on {cores} threads at any --gpus value (the reference's CPU path does not shard); "
+                                   "a ratio against an N-GPU line compares N GPUs with this one host"),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "cpu": cpu_model(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -217,6 +226,138 @@ def workload_config(name, cfg, gpus, replicate_grads=False, gather_output=False)
 
 
 # --------------------------------------------------------------------------------------------------
+# the row-sharded 65536 x 16384 layer (strong scaling): used by `--workload sharded` and by the `sharded` sub-record
+# --------------------------------------------------------------------------------------------------
+class ShardedLayerBench:
+    """Inputs and step function of the row-sharded layer on this rank.  `exchange`: "peer" = the library's own kernels over
+    peer memory when the ranks can map each other's buffers (else NCCL), "nccl" = NCCL collectives between the products."""
+
+    def __init__(self, cfg, dev, world, rank, rb, K, exchange="peer"):
+        import torch.distributed as dist
+        self.cfg, self.dev, self.world, self.rank, self.rb, self.K, self.dist = cfg, dev, world, rank, rb, K, dist
+        T, Kin, N, R = cfg["T"], cfg["K"], cfg["N"], cfg["R"]
+        self.plan = rb.parallel.ShardedLayerPlan(T, N, world, rank)
+        self.row0, self.n_local = self.plan.row_lo, self.plan.row_hi - self.plan.row_lo
+        g = torch.Generator().manual_seed(1005)
+        self.x = torch.randn(T, Kin, generator=g).bfloat16().to(dev)
+        self.C = (torch.randn(R, Kin, generator=torch.Generator().manual_seed(7)) * cfg["coef_std"]).bfloat16().to(dev)
+        gd = torch.Generator(device=dev).manual_seed(2000 + rank)
+        self.dy = torch.randn(T, self.n_local, device=dev, generator=gd).bfloat16()
+        self.ex = None
+        if world > 1 and exchange == "peer":
+            self.ex = rb.parallel.PeerExchange.create(self.plan, R, dev)
+        self.exchange = "single GPU" if world == 1 else (f"library kernels over peer memory ({self.ex.how})" if self.ex is not None
+                                                         else "NCCL collectives between the products")
+        self.y_all = None
+
+    def step(self, gather_output=False, replicate=False, timer=None):
+        rb, K, plan, seed = self.rb, self.K, self.plan, self.cfg["seed"]
+        if self.world == 1:
+            y = K.linear_fwd(self.x, self.C, seed, self.n_local, self.row0)
+            if timer is not None:
+                timer.mark("forward (z, noise fill, y)")
+            dx, dc = K.linear_bwd(self.dy, self.x, self.C, seed, self.row0)
+            if timer is not None:
+                timer.mark("backward (noise fill, g, dX, dC)")
+            return y, dx, dc
+        if self.ex is not None and not replicate:
+            y = rb.parallel.sharded_forward_peer(self.x, self.C, seed, plan, self.ex, timer)
+        else:
+            y = rb.parallel.sharded_forward(self.x, self.C, seed, plan)
+            if timer is not None:
+                timer.mark("forward (z, z all-gather, y)")
+        work = None
+        if gather_output:
+            if self.y_all is None:
+                self.y_all = torch.empty((self.world * self.cfg["T"], self.n_local), dtype=torch.bfloat16, device=self.dev)
+            # every rank receives all column blocks of y (rank-major [G, T, N/G]); runs beside the backward products
+            work = self.dist.all_gather_into_tensor(self.y_all, y, async_op=True)
+        if self.ex is not None and not replicate:
+            dx, dc = rb.parallel.sharded_backward_peer(self.dy, self.x, self.C, seed, plan, self.ex, timer)
+        else:
+            dx, dc = rb.parallel.sharded_backward(self.dy, self.x, self.C, seed, plan, replicate=replicate)
+            if timer is not None:
+                timer.mark("backward (g, g exchange, dX, dC)")
+        if work is not None:
+            work.wait()
+            if timer is not None:
+                timer.mark("y all-gather tail")
+        return y, dx, dc
+
+    def timed(self, steps, warmup, **kw):
+        """ms per step, maximum over the ranks (barrier and synchronise on both sides of the timed region)."""
+        dist, dev = self.dist, self.dev
+        for _ in range(max(warmup, 3)):
+            self.step(**kw)
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            self.step(**kw)
+        e1.record()
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        self.K.check_status()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def phases(self, reps=5, **kw):
+        """Device time of every phase as this rank's launching stream sees it, averaged over `reps` steps (exchanges that
+        run on a side stream show up only as the time the main stream waits for them)."""
+        acc = {}
+        for _ in range(reps):
+            timer = self.rb.parallel.PhaseTimer()
+            self.step(timer=timer, **kw)
+            torch.cuda.synchronize()
+            for k, v in timer.durations().items():
+                acc[k] = acc.get(k, 0.0) + v / reps
+        return {k: round(v, 4) for k, v in acc.items()}
+
+
+def sharded_record(args, dev, world, rank, rb, K):
+    """The `sharded` sub-record of the default line (also the body of `--workload sharded`)."""
+    cfg = WORKLOADS["sharded"]
+    T, Kin, N, R = cfg["T"], cfg["K"], cfg["N"], cfg["R"]
+    flops = algorithmic_flops(T, Kin, N, R)
+    peaks = measured_peaks()
+    b = ShardedLayerBench(cfg, dev, world, rank, rb, K, exchange=args.exchange)
+    ms = b.timed(args.steps, args.warmup)
+    rec = {"workload": workload_config("sharded", cfg, world)["workload"], "n_gpus": world, "scaling": "strong",
+           "unit": "TFLOP/s", "value": flops / (ms * 1e-3) / 1e12, "ms_per_step": ms, "steps": args.steps,
+           "exchange": b.exchange, "outputs": "y row-sharded (each rank keeps its columns), dX token-sharded, dC input-feature-sharded",
+           "phases_ms": b.phases()}
+    rec["frac_of_peak_per_gpu"] = rec["value"] / world / peaks["tensor"]
+    if world > 1:
+        # the same layer on ONE GPU, measured by every rank at the same time in this same process: the denominator of the speed-up
+        one = ShardedLayerBench(cfg, dev, 1, 0, rb, K)
+        ms1 = one.timed(args.steps, args.warmup)
+        del one
+        torch.cuda.empty_cache()
+        rec["single_gpu_ms_per_step"] = ms1
+        rec["speedup_vs_single_gpu"] = ms1 / ms
+        ms_g = b.timed(args.steps, args.warmup, gather_output=True)
+        rec["gather_output"] = {"what": "the same step with y all-gathered over NVLink (NCCL, beside the backward products): every rank "
+                                        "receives (G-1)/G of 537 MB", "ms_per_step": ms_g, "value": flops / (ms_g * 1e-3) / 1e12,
+                                "speedup_vs_single_gpu": ms1 / ms_g}
+        if b.ex is not None and args.exchange == "peer":
+            nccl = ShardedLayerBench(cfg, dev, world, rank, rb, K, exchange="nccl")
+            ms_n = nccl.timed(args.steps, args.warmup)
+            rec["nccl_exchange"] = {"what": "the same step with NCCL all-gather / all-reduce between the products", "ms_per_step": ms_n,
+                                    "value": flops / (ms_n * 1e-3) / 1e12, "speedup_vs_single_gpu": ms1 / ms_n}
+            del nccl
+    else:
+        rec["single_gpu_ms_per_step"], rec["speedup_vs_single_gpu"] = ms, 1.0
+    del b
+    torch.cuda.empty_cache()
+    return rec
+
+
+# --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
 def run_ours(args, cfg):
@@ -239,31 +380,24 @@ def run_ours(args, cfg):
     dt = torch.bfloat16 if cfg["dtype"] == "bf16" else torch.float32
     T, Kin, N, R, seed = cfg["T"], cfg["K"], cfg["N"], cfg["R"], cfg["seed"]
     row0, n_local = 0, N
-    plan = None
+    sb = None
     if args.workload == "sharded":
-        plan = rb.parallel.ShardedLayerPlan(T, N, world, rank)
-        row0, n_local = plan.row_lo, plan.row_hi - plan.row_lo
-    g = torch.Generator().manual_seed(1003 + (rank if args.workload == "gemm" else 0))
-    x_host = torch.randn(T, Kin, generator=g).to(dt).pin_memory()
-    C = (torch.randn(R, Kin, generator=torch.Generator().manual_seed(7)) * cfg["coef_std"]).to(dt).to(dev)
-    x = x_host.to(dev)
-    dy = torch.randn(T, n_local, generator=g).to(dt).to(dev)
+        sb = ShardedLayerBench(cfg, dev, world, rank, rb, K, exchange=args.exchange)
+        row0, n_local = sb.row0, sb.n_local
+        x, C, dy = sb.x, sb.C, sb.dy
+        x_host = x.cpu().pin_memory()
+    else:
+        g = torch.Generator().manual_seed(1003 + (rank if args.workload == "gemm" else 0))
+        x_host = torch.randn(T, Kin, generator=g).to(dt).pin_memory()
+        C = (torch.randn(R, Kin, generator=torch.Generator().manual_seed(7)) * cfg["coef_std"]).to(dt).to(dev)
+        x = x_host.to(dev)
+        dy = torch.randn(T, n_local, generator=g).to(dt).to(dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.workload == "gemv" else None
-    y_all = (torch.empty((world * T, n_local), dtype=dt, device=dev)
-             if args.workload == "sharded" and args.gather_output and world > 1 else None)
 
     def step():
-        if plan is not None and world > 1:
-            # rows split over ranks: z all-gather, g all-reduce, dX all-gather, dC all-reduce
-            y = rb.parallel.sharded_forward(x, C, seed, plan)
-            work = None
-            if args.gather_output:
-                # every rank receives all column blocks of y (rank-major [G, T, N/G]); runs beside the backward products
-                work = dist.all_gather_into_tensor(y_all, y, async_op=True)
-            dx, dc = rb.parallel.sharded_backward(dy, x, C, seed, plan, replicate=args.replicate_grads)
-            if work is not None:
-                work.wait()
-            return y, dx, dc
+        if sb is not None:
+            # rows split over ranks: z gathered, g summed; by default dX stays token-sharded and dC input-feature-sharded
+            return sb.step(args.gather_output, args.replicate_grads)
         y = K.linear_fwd(x, C, seed, n_local, row0)
         if world > 1:
             # data parallel: dC first, its all-reduce overlapped with the dX product
@@ -373,7 +507,8 @@ def run_ours(args, cfg):
             torch.cuda.synchronize()
             fill_ms = e0.elapsed_time(e1) / 20
             kernel = ("dense_pair_kernel (cta_group::2; dense_gemm_kernel where the tiles would not fill the CTA pairs): y = z S^T and "
-                      "g = dY S, average over both launches, on S hashed once per call into a bf16 scratch by noise_bf16x8_kernel")
+                      "g = dY S, average over both launches, on S hashed once per call into a bf16 scratch by noise_bf16_seg_kernel "
+                      "(noise_bf16x8_kernel when d_c is not a multiple of 1024)")
         else:
             avg_ms, fill_ms, kernel = fused_ms, None, fused["kernel"]
         achieved = flops_launch / (avg_ms * 1e-3) / 1e12
@@ -444,7 +579,9 @@ def run_ours(args, cfg):
             "metric": metric_name(args.workload), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if args.workload == "sharded" else "weak", "vs_baseline": None,
-            "dtype": cfg["dtype"], "data": "synthetic", "config": workload_config(args.workload, cfg, world, args.replicate_grads, args.gather_output),
+            "dtype": cfg["dtype"], "data": "synthetic",
+            "config": dict(workload_config(args.workload, cfg, world, args.replicate_grads, args.gather_output),
+                           **({"exchange": sb.exchange} if sb is not None else {})),
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(args.workload, staged) * args.steps,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
@@ -455,6 +592,15 @@ def run_ours(args, cfg):
         if eager_ms is not None:
             line["config"]["launch"] = "the step's four kernels replayed as one CUDA graph"
             line["eager_ms_per_step"] = eager_ms
+    sharded = None
+    if args.workload == "gemm" and not args.no_sharded_record:
+        # the second scaling curve: the row-sharded layer on the same N GPUs, same steps and warm-up, same process
+        del x, dy
+        torch.cuda.empty_cache()
+        sharded = sharded_record(args, dev, world, rank, rb, K)
+    if rank == 0:
+        if sharded is not None:
+            line["sharded"] = sharded
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -558,8 +704,24 @@ def run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier):
     else:
         work = algorithmic_flops(T, Kin, N, R) * (world if args.workload == "gemm" else 1) / 1e12
         unit = "TFLOP/s"
-    return {"value": work * n_e2e / (ms * 1e-3), "unit": unit, "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
+    # the host -> device copy on its own, all ranks copying at the same time (what the end-to-end step is bound by when the
+    # layer is faster than the copy): GB/s per rank, slowest rank
+    h2d_bytes = x_host.numel() * x_host.element_size()
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for i in range(6):
+        bufs[i % 2].copy_(hosts[i % 2], non_blocking=True)
+    c1.record()
+    barrier()
+    tcopy = torch.tensor([c0.elapsed_time(c1) / 6], device=dev)
+    if world > 1:
+        dist.all_reduce(tcopy, op=dist.ReduceOp.MAX)
+    copy_ms = float(tcopy.item())
+    return {"value": work * n_e2e / (ms * 1e-3), "unit": unit, "h2d_bytes_per_step": h2d_bytes,
             "d2h_bytes_per_step": 4, "steps": n_e2e, "ms_per_step": ms / n_e2e,
+            "h2d_gbs": h2d_bytes / (copy_ms * 1e-3) / 1e9, "h2d_copy_ms": copy_ms,
+            "h2d_note": f"pinned-host -> device copy of one step's x alone, {world} rank(s) copying at once: the step cannot be shorter",
             "what": "pinned-host x -> device (copy stream, overlapped), rlinear forward, mean-square loss, autograd backward "
                     "(dX and dC), loss.item() back to the host"}
 
@@ -738,6 +900,109 @@ def run_gpt2mlp(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------------
+# small cases for profilers (`--profile-case`): a few launches of one kind of kernel, then exit
+# --------------------------------------------------------------------------------------------------
+ROLE_NAMES = ["mma_wait_full_or_A", "mma_wait_B", "mma_wait_tmem", "mma_total", "tma_wait_free", "gen_wait_free", "gen_busy",
+              "epilogue_busy"]
+
+
+def profile_case(args):
+    """Self-terminating cases sized for `ncu` (device footprint a few hundred MB, launches of 0.01-0.3 ms):
+
+        --profile-case noise     2 launches each of the y- and g-shaped product with S regenerated in the kernel (-k regex:noise_)
+        --profile-case staged    2 x (noise fill + plain product) for y and g on the staged S (-k "regex:dense_|noise_bf16")
+        --profile-case products  2 launches each of the five plain products of one step (z, y, g, dX, dC)
+        --profile-case gemv      3 forward + backward steps of the batch-1 float32 layer, L2 flushed in between (-k regex:gemv)
+        --profile-case roles     per-role cycle counters of the generated-operand kernel variants and of the pair kernel
+      with --tokens / --out / --dc for the shape (defaults 2048 / 4096 / 8192 tokens, 16384 rows, d_c 1024).
+    """
+    from randumb_b200 import kernels as K, _lib
+    assert torch.cuda.is_available(), "profile cases run on a GPU"
+    case, out, dc, seed = args.profile_case, args.out, args.dc, 42
+    tokens = args.tokens or {"noise": 2048, "staged": 4096, "products": 4096, "roles": 8192, "gemv": 1}[case]
+    dev = torch.device("cuda", 0)
+    if case == "gemv":
+        cfg = WORKLOADS["gemv"]
+        g = torch.Generator().manual_seed(1002)
+        x = torch.randn(1, cfg["K"], generator=g).to(dev)
+        C = (torch.randn(cfg["R"], cfg["K"], generator=g) * cfg["coef_std"]).to(dev)
+        dy = torch.randn(1, cfg["N"], generator=g).to(dev)
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            flush.zero_()
+            K.linear_fwd(x, C, cfg["seed"], cfg["N"])
+            K.linear_bwd(dy, x, C, cfg["seed"])
+        torch.cuda.synchronize()
+        print("ok")
+        return
+    z = torch.randn(tokens, dc, device=dev).bfloat16()
+    dy = torch.randn(tokens, out, device=dev).bfloat16()
+    if case == "noise":
+        for _ in range(2):
+            K.gemm_noise(z, out, seed, False, impl=K.IMPL_UMMA)       # y = z S^T
+            K.gemm_noise(dy, dc, seed, True, impl=K.IMPL_UMMA)        # g = dY S
+    elif case == "staged":
+        assert K.linear_stages_noise(tokens, 8, out, dc, torch.bfloat16, K.PATH_FACTORED)
+        for _ in range(2):
+            K.noise_product(z, out, seed, False)       # noise fill + y = z S^T
+            K.noise_product(dy, dc, seed, True)        # noise fill + g = dY S
+    elif case == "products":
+        kin = 4096
+        x = torch.randn(tokens, kin, device=dev).bfloat16()
+        C = (torch.randn(dc, kin, device=dev) * 0.01).bfloat16()
+        S = K.noise(out, dc, seed, 0, 0, torch.bfloat16, dev)
+        for _ in range(2):
+            K.gemm_dense(x, C)                         # z = x C^T
+            K.gemm_dense(z, S)                         # y = z S^T
+            K.gemm_dense(dy, S, True, False)           # g = dY S
+            K.gemm_dense(z, C, True, False)            # dX = g C
+            K.gemm_dense(z, x, False, False)           # dC = g^T x
+    else:
+        L = _lib.lib()
+        prof = torch.zeros(148 * 16, dtype=torch.int64, device=dev)
+        S = K.noise(out, dc, seed, 0, 0, torch.bfloat16, dev)
+
+        def counters(label, fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            prof.zero_()
+            L.rdb_set_profile_buffer(prof.data_ptr(), prof.numel() * 8)
+            fn()
+            torch.cuda.synchronize()
+            L.rdb_set_profile_buffer(None, 0)
+            p = prof.view(148, 16).double()[:, :8]
+            issuing = p[p[:, 3] > 0]
+            total = float(issuing[:, 3].mean())
+            vals = issuing.mean(0)
+            gens = p[p[:, 6] > 0]
+            if gens.numel():
+                vals[4:7] = gens.mean(0)[4:7]
+            print(f"{label}: {e0.elapsed_time(e1) / 5:.4f} ms  mma_total {total / 1e3:.0f} kcycles  " +
+                  "  ".join(f"{n}={100 * float(v) / total:.0f}%" for n, v in zip(ROLE_NAMES, vals.tolist())), flush=True)
+
+        for tile in (1, 3, 7, 8):
+            prev = K.set_option(_lib.OPT_NOISE_TILE, tile)
+            try:
+                counters(f"generated-operand variant {tile} y", lambda: K.gemm_noise(z, out, seed, False, impl=K.IMPL_UMMA))
+                counters(f"generated-operand variant {tile} g", lambda: K.gemm_noise(dy, dc, seed, True, impl=K.IMPL_UMMA))
+            finally:
+                K.set_option(_lib.OPT_NOISE_TILE, prev)
+        pair = _lib.CallOptions(dense_pair=2)
+        counters("pair kernel y = z S^T", lambda: K.gemm_dense(z, S, options=pair))
+        counters("pair kernel g = dY S", lambda: K.gemm_dense(dy, S, True, False, options=pair))
+    torch.cuda.synchronize()
+    K.check_status()
+    print("ok")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -751,7 +1016,20 @@ def main():
     ap.add_argument("--replicate-grads", action="store_true",
                     help="sharded workload: all-gather dX and all-reduce dC so that every rank holds both in full")
     ap.add_argument("--no-graph", action="store_true", help="gemv workload: launch the four kernels eagerly in the timed region")
+    ap.add_argument("--no-sharded-record", action="store_true",
+                    help="default workload: skip the `sharded` sub-record (the row-sharded 65536 x 16384 layer measured after the headline)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="row-sharded layer: exchanges by the library's kernels over peer memory (falls back to NCCL when the ranks "
+                         "cannot map each other's memory) or by NCCL collectives")
+    ap.add_argument("--profile-case", default=None, choices=["noise", "staged", "roles", "products", "gemv"],
+                    help="run a small self-terminating case for a profiler instead of the benchmark")
+    ap.add_argument("--tokens", type=int, default=None, help="profile case: token count")
+    ap.add_argument("--out", type=int, default=16384, help="profile case: output rows")
+    ap.add_argument("--dc", type=int, default=1024, help="profile case: coefficient dimension")
     args = ap.parse_args()
+    if args.profile_case:
+        profile_case(args)
+        return
     if args.workload == "gpt2mlp" and args.impl == "ours":
         run_gpt2mlp(args)
         return

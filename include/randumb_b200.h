@@ -348,6 +348,46 @@ int rdb_embed_fwd(float *out, const int64_t *idx, const float *coef, int64_t n_i
 int rdb_embed_bwd(float *dcoef, const float *dout, const int64_t *idx, float *workspace, int64_t n_idx,
                   int64_t rowsize, int64_t M, uint32_t seed, void *stream);
 
+/*
+ * Exchange steps of a layer whose output rows are split over the GPUs of one node (each rank regenerates its own noise
+ * rows, so only activations move: z = x C^T is gathered, g = dY S is summed).  The reference has no counterpart -- its
+ * only collectives are DDP's (modded-nanogpt/train_gpt2.py:346, 441); these are this library's own kernels over peer
+ * memory, plain stores through NVLink / NVSwitch (no TMA multicast, no multimem), as an alternative to NCCL calls
+ * between the products.  The caller owns all memory: every rank allocates one exchange buffer that the other ranks of
+ * the node have mapped (symmetric memory or CUDA IPC) and passes the resulting pointer lists -- `ptrs[r]` is rank r's
+ * buffer as addressable from the calling process, 16-byte aligned, at most RDB_MAX_PEERS of them.
+ *
+ * rdb_peer_barrier   every rank has enqueued the barrier with this `epoch` and everything it stored before has landed.
+ *                    flag_ptrs[r]: RDB_MAX_PEERS uint64 words in rank r's buffer, zero before the first barrier; epochs
+ *                    must grow (1, 2, 3, ...) and be the same on all ranks for the same barrier.  A rank that waits longer
+ *                    than RDB_PEER_WAIT_LIMIT_NS writes RDB_STATUS_TIMEOUT_PEER to status[0] and returns.  Never enqueue
+ *                    the barriers of several ranks on ONE GPU: they wait for each other and nothing makes two launches
+ *                    run at the same time.
+ * rdb_peer_copy      src[0, nbytes) -> dst_ptrs[d] + dst_offset_bytes for every d < ndst (an all-gather step: every
+ *                    rank sends its block to the same place in all buffers).  max_blocks <= 0: library default.
+ * rdb_peer_scatter   block j of src (block_bytes each) -> dst_ptrs[j] + dst_offset_bytes (the scatter half of a
+ *                    reduce-scatter: rank j collects everybody's contribution to its block).
+ * rdb_reduce_slots_bf16   out[i] = sum over s < nslots of slots[s * slot_stride_bytes + i] (bf16, float32 accumulation,
+ *                    fixed order s = 0, 1, ...: the result does not depend on arrival order).
+ * rdb_gemm_dense_scatter  D = A op(B)^T (bf16, CTA-pair tcgen05 kernel) with the scatter fused into the product: row block
+ *                    j of D (rows_per_dst rows, a multiple of 32) is stored by the kernel's epilogue straight into
+ *                    dst_ptrs[j] + dst_offset_bytes as a dense [rows_per_dst x N] matrix, tile by tile while later tiles are
+ *                    still being computed.  A is [M, Kc] row-major; B is [N, Kc] (b_kmajor) or [Kc, N].  Needs M and N
+ *                    above 128 and extents in multiples of 8 (else RDB_ERR_UNSUPPORTED: use rdb_gemm_dense +
+ *                    rdb_peer_scatter).
+ */
+#define RDB_MAX_PEERS 8
+#define RDB_PEER_WAIT_LIMIT_NS 4000000000ull
+int rdb_peer_barrier(void *const *flag_ptrs, int rank, int world, uint64_t epoch, int32_t *status, void *stream);
+int rdb_peer_copy(void *const *dst_ptrs, int ndst, size_t dst_offset_bytes, const void *src, size_t nbytes, int max_blocks,
+                  void *stream);
+int rdb_peer_scatter(void *const *dst_ptrs, int ndst, size_t dst_offset_bytes, const void *src, size_t block_bytes,
+                     int max_blocks, void *stream);
+int rdb_reduce_slots_bf16(void *out, const void *slots, size_t slot_stride_bytes, int nslots, size_t nbytes, void *stream);
+int rdb_gemm_dense_scatter(void *const *dst_ptrs, int ndst, size_t dst_offset_bytes, int64_t rows_per_dst, const void *a,
+                           const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb, int b_kmajor,
+                           const rdb_call_options *options, int32_t *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

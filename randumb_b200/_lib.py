@@ -22,6 +22,7 @@ OPT_STAGE_NOISE = 3
 OPT_RESERVE_SMS = 4
 OPT_FILL_OVERLAP = 5
 MAX_RESERVE_SMS = 64
+MAX_PEERS = 8
 STATUS_NAMES = {0: "ok", 1: "producer wait expired", 2: "mma wait expired", 3: "epilogue wait expired",
                 4: "generator wait expired", 5: "peer wait expired"}
 
@@ -72,6 +73,11 @@ PROTOTYPES = {
     "rdb_gemm_dense_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "rdb_gemm_dense_ws": (_i32, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp,
                           _vp]),
+    "rdb_peer_barrier": (_i32, [_vp, _i32, _i32, ctypes.c_uint64, _vp, _vp]),
+    "rdb_peer_copy": (_i32, [_vp, _i32, _sz, _vp, _sz, _i32, _vp]),
+    "rdb_peer_scatter": (_i32, [_vp, _i32, _sz, _vp, _sz, _i32, _vp]),
+    "rdb_reduce_slots_bf16": (_i32, [_vp, _vp, _sz, _i32, _sz, _vp]),
+    "rdb_gemm_dense_scatter": (_i32, [_vp, _i32, _sz, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _op, _vp, _vp]),
     "rdb_materialize_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _u32, _vp]),
     "rdb_materialize_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "rdb_materialize_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _u32, _vp]),

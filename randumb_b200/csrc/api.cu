@@ -277,6 +277,28 @@ extern "C" int rdb_gemm_dense_ex(void *d, const void *a, const void *b, void *wo
                      b_kmajor ? ldb : 1, b_kmajor ? 1 : ldb, none, M, N, Kc, st);
 }
 
+extern "C" int rdb_gemm_dense_scatter(void *const *dst_ptrs, int ndst, size_t dst_offset_bytes, int64_t rows_per_dst, const void *a,
+                                      const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb, int b_kmajor,
+                                      const rdb_call_options *options, int32_t *status, void *stream) {
+    if (M < 0 || N < 0 || Kc < 0 || lda < Kc || ldb < (b_kmajor ? Kc : N)) return RDB_ERR_SHAPE;
+    CallOpts o;
+    int rc = resolve_opts(options, &o);
+    if (rc) return rc;
+    if (!dst_ptrs || ndst < 1 || ndst > RDB_MAX_PEERS || rows_per_dst <= 0 || (rows_per_dst % 32) != 0 ||
+        (M + rows_per_dst - 1) / rows_per_dst > ndst || (dst_offset_bytes & 15))
+        return RDB_ERR_PEER;
+    if (M == 0 || N == 0) return RDB_OK;
+    if (!a || !b) return RDB_ERR_NULL;
+    void *dsts[RDB_MAX_PEERS];
+    for (int i = 0; i < ndst; ++i) {
+        if (!dst_ptrs[i] || (reinterpret_cast<uintptr_t>(dst_ptrs[i]) & 15)) return RDB_ERR_PEER;
+        dsts[i] = reinterpret_cast<uint8_t *>(dst_ptrs[i]) + dst_offset_bytes;
+    }
+    if (M <= 128 || N <= 128 || !umma_shape_ok_dense(M, N, Kc, lda, ldb, N, RDB_BF16, 1, b_kmajor, a, b, dsts[0]))
+        return RDB_ERR_UNSUPPORTED;
+    return umma_gemm_dense_scatter(dsts, ndst, rows_per_dst, a, b, M, N, Kc, lda, ldb, b_kmajor, status, (cudaStream_t)stream, o);
+}
+
 extern "C" int rdb_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda,
                               int64_t ldb, int64_t ldd, int a_dtype, int b_dtype, int d_dtype, int a_kmajor, int b_kmajor,
                               int impl, int32_t *status, void *stream) {

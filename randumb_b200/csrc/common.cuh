@@ -61,4 +61,8 @@ int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N,
                     int64_t ldb, int64_t ldd, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status,
                     cudaStream_t stream, const CallOpts &o);
 
+int umma_gemm_dense_scatter(void *const *dsts, int ndst, int64_t rows_per_dst, const void *a, const void *b, int64_t M, int64_t N,
+                            int64_t Kc, int64_t lda, int64_t ldb, int b_kmajor, int32_t *status, cudaStream_t stream,
+                            const CallOpts &o);
+
 }  // namespace rdb

@@ -71,10 +71,7 @@ __global__ void __launch_bounds__(256) noise_bf16x8_kernel(uint4 *__restrict__ o
         uint32_t p[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float f0 = sq5_to_float(sq5_tail(b0 + (uint32_t)(2 * j) * lin.sk));
-            const float f1 = sq5_to_float(sq5_tail(b0 + (uint32_t)(2 * j + 1) * lin.sk));
-            __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
-            p[j] = *reinterpret_cast<uint32_t *>(&h);
+            p[j] = sq5_pack_bf16x2(sq5_tail(b0 + (uint32_t)(2 * j) * lin.sk), sq5_tail(b0 + (uint32_t)(2 * j + 1) * lin.sk));
         }
         out[(size_t)r * ld_groups + cg] = make_uint4(p[0], p[1], p[2], p[3]);
     }
@@ -98,10 +95,7 @@ __global__ void __launch_bounds__(256) noise_bf16_seg_kernel(uint4 *__restrict__
             uint32_t p[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const float f0 = sq5_to_float(sq5_tail(b + (uint32_t)(2 * j) * lin.sk));
-                const float f1 = sq5_to_float(sq5_tail(b + (uint32_t)(2 * j + 1) * lin.sk));
-                __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
-                p[j] = *reinterpret_cast<uint32_t *>(&h);
+                p[j] = sq5_pack_bf16x2(sq5_tail(b + (uint32_t)(2 * j) * lin.sk), sq5_tail(b + (uint32_t)(2 * j + 1) * lin.sk));
             }
             dst[c * 32] = make_uint4(p[0], p[1], p[2], p[3]);
         }

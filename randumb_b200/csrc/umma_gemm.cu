@@ -368,10 +368,7 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
                     uint32_t p[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float f0 = sq5_to_float(sq5_tail(bstart[c] + (uint32_t)(2 * j) * lin.sk));
-                        const float f1 = sq5_to_float(sq5_tail(bstart[c] + (uint32_t)(2 * j + 1) * lin.sk));
-                        __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
-                        p[j] = *reinterpret_cast<uint32_t *>(&h);
+                        p[j] = sq5_pack_bf16x2(sq5_tail(bstart[c] + (uint32_t)(2 * j) * lin.sk), sq5_tail(bstart[c] + (uint32_t)(2 * j + 1) * lin.sk));
                     }
                     if (CS > 1) {
 #pragma unroll
@@ -700,10 +697,7 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     uint32_t p[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float f0 = sq5_to_float(sq5_tail(bstart[c] + (uint32_t)(2 * j) * lin.sk));
-                        const float f1 = sq5_to_float(sq5_tail(bstart[c] + (uint32_t)(2 * j + 1) * lin.sk));
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(f0, f1);
-                        p[j] = *reinterpret_cast<uint32_t *>(&h2);
+                        p[j] = sq5_pack_bf16x2(sq5_tail(bstart[c] + (uint32_t)(2 * j) * lin.sk), sq5_tail(bstart[c] + (uint32_t)(2 * j + 1) * lin.sk));
                     }
                     // own copy: plain store; the other CTAs that hold this half get asynchronous 16-byte stores that
                     // complete their bytes on the receiver's `full` barrier
@@ -1059,10 +1053,20 @@ struct DensePairCfg {
     static_assert(SMEM_DYN <= 232448 - 512, "shared memory");
 };
 
-template <int MT, int D, int A_MN, int B_MN>
+// Output tensor maps of the pair kernel.  NDST == 1: the one output matrix.  NDST > 1 (the scatter half of a reduce-scatter
+// fused into the product): row block j of the output -- rows [j * rows_per_dst, (j + 1) * rows_per_dst) -- is stored into
+// destination j, a dense [rows_per_dst x N] matrix that may live in another GPU's memory (plain TMA tile stores over
+// NVLink, no multicast); rows_per_dst is a multiple of 32, so no 32-row store box spans two destinations.
+template <int NDST>
+struct OutMaps {
+    CUtensorMap m[NDST];
+};
+
+template <int MT, int D, int A_MN, int B_MN, int NDST>
 __global__ void __launch_bounds__(DensePairCfg<MT, D>::THREADS, 1)
 dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ CUtensorMap tmap_d, int64_t M, int64_t N, int64_t Kc, int m_fast, int32_t *status, long long *prof) {
+                  const __grid_constant__ OutMaps<NDST> out, int64_t rows_per_dst, int64_t M, int64_t N, int64_t Kc, int m_fast,
+                  int32_t *status, long long *prof) {
     long long pc0 = 0, pc2 = 0;
     using Cfg = DensePairCfg<MT, D>;
     constexpr int BN = Cfg::BN;
@@ -1321,13 +1325,19 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0 && row_w < M && n0 + c0 < N) {
-                        tma_store_2d(&tmap_d, stag, (int32_t)(n0 + c0), (int32_t)row_w);
+                        int di = 0;
+                        int64_t row_l = row_w;
+                        if (NDST > 1) {
+                            di = (int)(row_w / rows_per_dst);
+                            row_l = row_w - di * rows_per_dst;
+                        }
+                        tma_store_2d(&out.m[di], stag, (int32_t)(n0 + c0), (int32_t)row_l);
                         bulk_commit_group();
                     }
                 }
             }
         }
-        if (lane == 0) bulk_wait_group0();   // all output tiles written before the CTA retires
+        if (lane == 0) bulk_wait_group0();   // all output tiles written (remote ones included) before the CTA retires
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -1555,18 +1565,26 @@ static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_
     return launch_status();
 }
 
-template <int MT, int D, int A_MN, int B_MN>
-static int launch_dense_pair(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
-                             int64_t ldd, int64_t tiles, int max_pairs, int32_t *status, cudaStream_t st, int reserve_sms) {
+template <int MT, int D, int A_MN, int B_MN, int NDST>
+static int launch_dense_pair(void *const *dsts, int64_t rows_per_dst, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc,
+                             int64_t lda, int64_t ldb, int64_t ldd, int64_t tiles, int max_pairs, int32_t *status, cudaStream_t st,
+                             int reserve_sms) {
     using Cfg = DensePairCfg<MT, D>;
-    CUtensorMap ta, tb, td;
+    CUtensorMap ta, tb;
+    OutMaps<NDST> out;
     int rc = A_MN ? make_tmap(&ta, a, M, Kc, lda, 64, BK) : make_tmap(&ta, a, Kc, M, lda, BK, BM);
     if (rc) return rc;
     rc = B_MN ? make_tmap(&tb, b, N, Kc, ldb, 64, BK) : make_tmap(&tb, b, Kc, N, ldb, BK, Cfg::HALF);
     if (rc) return rc;
-    rc = make_tmap(&td, d, N, M, ldd, 64, 32);   // output tiles of 32 rows x 64 columns
-    if (rc) return rc;
-    auto kern = dense_pair_kernel<MT, D, A_MN, B_MN>;
+    const int64_t ndst_used = NDST > 1 ? cdiv64(M, rows_per_dst) : 1;
+    for (int j = 0; j < NDST; ++j) {
+        // output tiles of 32 rows x 64 columns; unused entries repeat the first destination
+        const int jj = j < ndst_used ? j : 0;
+        const int64_t rows = NDST > 1 ? (M - jj * rows_per_dst < rows_per_dst ? M - jj * rows_per_dst : rows_per_dst) : M;
+        rc = make_tmap(&out.m[j], dsts[jj], N, rows, ldd, 64, 32);
+        if (rc) return rc;
+    }
+    auto kern = dense_pair_kernel<MT, D, A_MN, B_MN, NDST>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
@@ -1587,7 +1605,7 @@ static int launch_dense_pair(void *d, const void *a, const void *b, int64_t M, i
     // stream the larger operand once: consecutive tiles share the B panel when A is the smaller matrix
     const int m_fast = (M <= N) ? 1 : 0;
     long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 16 * sizeof(long long)) ? g_prof : nullptr;
-    e = cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, Kc, m_fast, status, prof);
+    e = cudaLaunchKernelEx(&cfg, kern, ta, tb, out, rows_per_dst, M, N, Kc, m_fast, status, prof);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
@@ -1598,7 +1616,7 @@ static int max_resident_pairs() {
     int dev = 0;
     (void)cudaGetDevice(&dev);
     if (dev == cached_dev && cached > 0) return cached;
-    auto kern = dense_pair_kernel<2, 4, 0, 0>;
+    auto kern = dense_pair_kernel<2, 4, 0, 0, 1>;
     int n = 0, fallback = sm_count() / 2;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DensePairCfg<2, 4>::SMEM_DYN) == cudaSuccess) {
         cudaLaunchConfig_t cfg = {};
@@ -1640,8 +1658,8 @@ static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_
     if (d_dtype == RDB_BF16 && o.dense_pair && M > BM && N > BM) {
         const int P = max_resident_pairs();
         if (o.dense_pair == 2 || prefer_dense_pair(M, N, Kc, P))
-            return launch_dense_pair<2, 4, A_MN, B_MN>(d, a, b, M, N, Kc, lda, ldb, ldd, cdiv64(M, 4 * BM) * cdiv64(N, 256), P,
-                                                       status, st, rs);
+            return launch_dense_pair<2, 4, A_MN, B_MN, 1>(&d, M, a, b, M, N, Kc, lda, ldb, ldd, cdiv64(M, 4 * BM) * cdiv64(N, 256), P,
+                                                          status, st, rs);
     }
     // at most 128 output columns (a coefficient dimension of 128 or less): 128-column tiles, half the MMA and B traffic
     if (d_dtype == RDB_BF16 && N <= 128)
@@ -1715,6 +1733,20 @@ int umma_gemm_dense_split_k(void *d, const void *a, const void *b, float *partia
     else
         split_k_reduce_kernel<float><<<grid, 256, 0, st>>>(reinterpret_cast<float *>(d), partials, n4, split, stride / 4);
     return launch_status();
+}
+
+// D = A op(B)^T on CTA pairs with row block j of D stored into dsts[j] (dense [rows_per_dst x N] bf16 each, possibly in
+// peer memory).  A K-major; B K-major or MN-major.
+int umma_gemm_dense_scatter(void *const *dsts, int ndst, int64_t rows_per_dst, const void *a, const void *b, int64_t M, int64_t N,
+                            int64_t Kc, int64_t lda, int64_t ldb, int b_kmajor, int32_t *status, cudaStream_t st, const CallOpts &o) {
+    if (M == 0 || N == 0) return RDB_OK;
+    if (ndst < 1 || ndst > RDB_MAX_PEERS || rows_per_dst <= 0 || (rows_per_dst % 32) != 0 || cdiv64(M, rows_per_dst) > ndst)
+        return RDB_ERR_PEER;
+    const int P = max_resident_pairs();
+    const int64_t tiles = cdiv64(M, 4 * BM) * cdiv64(N, 256);
+    if (b_kmajor)
+        return launch_dense_pair<2, 4, 0, 0, RDB_MAX_PEERS>(dsts, rows_per_dst, a, b, M, N, Kc, lda, ldb, N, tiles, P, status, st, o.reserve_sms);
+    return launch_dense_pair<2, 4, 0, 1, RDB_MAX_PEERS>(dsts, rows_per_dst, a, b, M, N, Kc, lda, ldb, N, tiles, P, status, st, o.reserve_sms);
 }
 
 int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,

@@ -104,9 +104,16 @@ def noise_bits(rows: int, cols: int, seed: int, row0: int = 0, col0: int = 0, de
     return out
 
 
-def noise(rows: int, cols: int, seed: int, row0: int = 0, col0: int = 0, dtype=torch.float32, device="cuda") -> torch.Tensor:
-    dev = torch.device(device)
-    out = torch.empty((rows, cols), dtype=dtype, device=dev)
+def noise(rows: int, cols: int, seed: int, row0: int = 0, col0: int = 0, dtype=torch.float32, device="cuda",
+          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """S[row0:row0+rows, col0:col0+cols] as float32 or bfloat16; ``out``: a contiguous [rows, cols] tensor to fill instead."""
+    if out is not None:
+        if tuple(out.shape) != (rows, cols) or not out.is_contiguous() or not out.is_cuda:
+            raise RuntimeError(f"noise: out must be a contiguous CUDA tensor of shape [{rows}, {cols}]")
+        dev, dtype = out.device, out.dtype
+    else:
+        dev = torch.device(device)
+        out = torch.empty((rows, cols), dtype=dtype, device=dev)
     with torch.cuda.device(dev):
         rc = _lib.lib().rdb_noise(_ptr(out), _dt(dtype), rows, cols, cols, row0, col0, _seed(seed), _stream(out.device))
     _lib.check(rc, "rdb_noise")
@@ -269,6 +276,14 @@ def noise_product(a: torch.Tensor, n: int, seed: int, transposed: bool = False, 
     return gemm_noise(a, n, seed, transposed, row0)
 
 
+def _rows_ok(t: torch.Tensor) -> bool:
+    return t.shape[0] <= 1 or t.shape[1] == 0 or (t.stride(1) == 1 and t.stride(0) >= t.shape[1]) or t.is_contiguous()
+
+
+def _pitch(t: torch.Tensor) -> int:
+    return t.stride(0) if t.shape[0] > 1 and t.shape[1] > 0 else t.shape[1]
+
+
 def gemm_dense(a: torch.Tensor, b: torch.Tensor, a_kmajor: bool = True, b_kmajor: bool = True,
                out_dtype: Optional[torch.dtype] = None, impl: int = IMPL_AUTO, options: Optional[_lib.CallOptions] = None,
                out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -276,7 +291,8 @@ def gemm_dense(a: torch.Tensor, b: torch.Tensor, a_kmajor: bool = True, b_kmajor
     ``options``: per-call tuning switches (e.g. ``CallOptions(reserve_sms=32)`` for a launch that should leave SMs to a
     collective); ``out``: a contiguous [M, N] tensor to write into instead of a fresh one."""
     dev = _need_cuda(a, b)
-    assert a.dim() == 2 and b.dim() == 2 and a.is_contiguous() and b.is_contiguous()
+    # rows may be further apart than their length (a column slice of a wider matrix): the row pitch is passed on
+    assert a.dim() == 2 and b.dim() == 2 and _rows_ok(a) and _rows_ok(b), "gemm_dense: operands need unit stride along rows"
     M, Kc = (a.shape[0], a.shape[1]) if a_kmajor else (a.shape[1], a.shape[0])
     N, Kb = (b.shape[0], b.shape[1]) if b_kmajor else (b.shape[1], b.shape[0])
     if Kc != Kb:
@@ -293,7 +309,7 @@ def gemm_dense(a: torch.Tensor, b: torch.Tensor, a_kmajor: bool = True, b_kmajor
         # few output tiles and a long contraction: scratch for split-K (float32 partial products, ordered sum)
         nbytes = L.rdb_gemm_dense_workspace_bytes(M, N, Kc) if impl != IMPL_SIMT and a.dtype == torch.bfloat16 else 0
         ws = _workspace(nbytes, dev) if nbytes else None
-        rc = L.rdb_gemm_dense_ex(_ptr(d), _ptr(a), _ptr(b), _ptr(ws), nbytes, M, N, Kc, a.shape[1], b.shape[1], N, _dt(a.dtype),
+        rc = L.rdb_gemm_dense_ex(_ptr(d), _ptr(a), _ptr(b), _ptr(ws), nbytes, M, N, Kc, _pitch(a), _pitch(b), N, _dt(a.dtype),
                                  _dt(b.dtype), _dt(out_dtype), 1 if a_kmajor else 0, 1 if b_kmajor else 0, impl, _opts(options),
                                  _ptr(status_buffer(dev)), _stream(dev))
     _lib.check(rc, "rdb_gemm_dense_ex")
@@ -389,3 +405,63 @@ def embed_bwd(idx: torch.Tensor, dout: torch.Tensor, dcoefs_size: int, rowsize: 
                              _seed(seed), _stream(dev))
     _lib.check(rc, "rdb_embed_bwd")
     return dcoef
+
+
+# ------------------------------------------------------------------------------------------ exchange over peer memory
+def _ptr_array(ptrs):
+    arr = (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+    return arr
+
+
+def peer_barrier(flag_ptrs, rank: int, world: int, epoch: int, dev: torch.device) -> None:
+    """Enqueue the barrier kernel of this rank (see rdb_peer_barrier); ``flag_ptrs``: a ctypes array from ``_ptr_array``."""
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_peer_barrier(flag_ptrs, rank, world, epoch, _ptr(status_buffer(dev)), _stream(dev))
+    _lib.check(rc, "rdb_peer_barrier")
+
+
+def peer_copy(dst_ptrs, ndst: int, dst_offset: int, src: torch.Tensor, max_blocks: int = 0) -> None:
+    dev = _need_cuda(src)
+    assert src.is_contiguous()
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_peer_copy(dst_ptrs, ndst, dst_offset, _ptr(src), src.numel() * src.element_size(), max_blocks, _stream(dev))
+    _lib.check(rc, "rdb_peer_copy")
+
+
+def peer_scatter(dst_ptrs, ndst: int, dst_offset: int, src: torch.Tensor, max_blocks: int = 0) -> None:
+    """Row block j of the contiguous ``src`` (``src.shape[0] / ndst`` rows each) -> destination j."""
+    dev = _need_cuda(src)
+    assert src.is_contiguous() and src.shape[0] % ndst == 0
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_peer_scatter(dst_ptrs, ndst, dst_offset, _ptr(src), src.numel() * src.element_size() // ndst, max_blocks,
+                                         _stream(dev))
+    _lib.check(rc, "rdb_peer_scatter")
+
+
+def reduce_slots(out: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """``out = slots.sum(0)`` for bf16 ``slots[nslots, ...]``, float32 accumulation in slot order."""
+    dev = _need_cuda(out, slots)
+    assert out.dtype == torch.bfloat16 and slots.dtype == torch.bfloat16 and out.is_contiguous() and slots.is_contiguous()
+    assert slots.shape[1:] == out.shape
+    nb = out.numel() * 2
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_reduce_slots_bf16(_ptr(out), _ptr(slots), nb, slots.shape[0], nb, _stream(dev))
+    _lib.check(rc, "rdb_reduce_slots_bf16")
+    return out
+
+
+def gemm_dense_scatter(dst_ptrs, ndst: int, dst_offset: int, rows_per_dst: int, a: torch.Tensor, b: torch.Tensor,
+                       b_kmajor: bool = True, options: Optional[_lib.CallOptions] = None) -> bool:
+    """``a @ op(b).T`` on the CTA-pair kernel with row block j of the result stored into destination j by the kernel's
+    epilogue (see rdb_gemm_dense_scatter).  Returns False, having launched nothing, when the shape does not qualify."""
+    dev = _need_cuda(a, b)
+    assert a.dim() == 2 and b.dim() == 2 and _rows_ok(a) and _rows_ok(b) and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    M, Kc = a.shape
+    N = b.shape[0] if b_kmajor else b.shape[1]
+    with torch.cuda.device(dev):
+        rc = _lib.lib().rdb_gemm_dense_scatter(dst_ptrs, ndst, dst_offset, rows_per_dst, _ptr(a), _ptr(b), M, N, Kc, _pitch(a), _pitch(b),
+                                               1 if b_kmajor else 0, _opts(options), _ptr(status_buffer(dev)), _stream(dev))
+    if rc == -6:
+        return False
+    _lib.check(rc, "rdb_gemm_dense_scatter")
+    return True

@@ -165,10 +165,30 @@ def _mat_setup(ctx, inputs, output):
     ctx.fused_bias = fused_bias
     ctx.bias_dtype = scale_bias.dtype if scale_bias is not None else None
     ctx.bias_shape = scale_bias.shape if scale_bias is not None else None
+    ctx.view_size, ctx.view_strides = list(size), list(strides)
+
+
+def _natural_order(grad: torch.Tensor, size: List[int], strides: List[int]) -> torch.Tensor:
+    """Gradient of a strided view, laid out in the order of the virtual tensor's own elements.
+
+    Element ``n`` of the virtual tensor always uses noise row ``n``; a view (a transpose, say) only changes which ``n`` sits
+    at which output position: ``sq = sum_d index_d * stride_d`` (src/rten_cpp/RandumbTensor.py:264).  The backward kernels
+    walk the noise rows in order (:304-359), so the incoming gradient is scattered back to ``flat[sq]`` first; positions
+    the view does not reach keep a zero gradient."""
+    expect, acc = [], 1
+    for d in reversed(size):
+        expect.append(acc)
+        acc *= d
+    if list(strides) == list(reversed(expect)):
+        return grad.contiguous()
+    extent = 1 + sum((d - 1) * st for d, st in zip(size, strides)) if all(d > 0 for d in size) else 0
+    flat = grad.new_zeros((extent,))
+    flat.as_strided(size, strides).copy_(grad)
+    return flat
 
 
 def _mat_backward(ctx, grad):
-    grad = grad.contiguous()
+    grad = _natural_order(grad, ctx.view_size, ctx.view_strides)
     dcoefs = materialize_bwd(grad, ctx.dcoefs_size, ctx.seed).to(ctx.coef_dtype)
     dscale_bias = None
     if ctx.fused_bias:

@@ -248,6 +248,218 @@ def sharded_backward(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor
 
 
 # ------------------------------------------------------------------------------------------------
+# the same layer with the exchanges done by the library's own kernels over peer memory
+# ------------------------------------------------------------------------------------------------
+class PhaseTimer:
+    """Device time of the phases of one step as the launching stream sees them: ``mark(name)`` records an event on the
+    current stream after a phase; ``durations()`` (after a synchronise) gives name -> milliseconds since the previous mark."""
+
+    def __init__(self):
+        self.events: List[Tuple[str, torch.cuda.Event]] = []
+        self.mark("start")
+
+    def mark(self, name: str) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.events.append((name, ev))
+
+    def durations(self) -> dict:
+        out: dict = {}
+        for (_, a), (name, b) in zip(self.events, self.events[1:]):
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
+
+
+def _mark(timer: Optional[PhaseTimer], name: str) -> None:
+    if timer is not None:
+        timer.mark(name)
+
+
+class PeerExchange:
+    """Exchange buffer of a row-sharded layer, mapped into every rank of the node, plus this rank's scratch.
+
+    Layout of the shared buffer (identical on every rank, byte offsets):
+        [0, 4096)      barrier flags: one uint64 per peer, written only by that peer (epochs only grow)
+        z_full         [T, R] bf16   z = x C^T, every rank stores its token slice into all ranks' copies
+        g_parts        [G, t_r, R] bf16   slot s = rank s's partial g = dY_s S_s for MY token slice
+        g_full         [T, R] bf16   the summed g, every rank stores its reduced token slice into all ranks' copies
+    Local (not shared): S [n_local, R] bf16 (this rank's noise rows, refilled in every forward and backward) and
+    g_loc [t_r, R].
+
+    The buffer comes from ``torch.distributed._symmetric_memory`` (its NVLink multicast binding switched off: the kernels
+    use plain stores to the peers' mappings) or, failing that, from CUDA IPC handles of an ordinary allocation.  Needs one
+    GPU per rank, equal token shards in multiples of 32, at most 8 ranks; ``PeerExchange.create`` returns None otherwise and
+    the NCCL path is used.
+    """
+    FLAG_BYTES = 4096
+
+    def __init__(self, plan: "ShardedLayerPlan", R: int, buf: torch.Tensor, ptrs: Sequence[int], how: str, keep=None):
+        from . import kernels as K
+        self.plan, self.R, self.buf, self.how, self._keep = plan, R, buf, how, keep
+        self.world, self.rank, self.dev = plan.world, plan.rank, buf.device
+        T = sum(plan.tok_sizes)
+        self.T, self.t_r = T, plan.tok_sizes[0]
+        self.z_off = self.FLAG_BYTES
+        self.parts_off = self.z_off + T * R * 2
+        self.gfull_off = self.parts_off + T * R * 2
+        self.ptrs = K._ptr_array(ptrs)
+
+        def view(off, rows):
+            return buf[off:off + rows * R * 2].view(torch.bfloat16).view(rows, R)
+        self.z_full, self.g_full = view(self.z_off, T), view(self.gfull_off, T)
+        self.g_parts = view(self.parts_off, T).view(self.world, self.t_r, R)
+        n_local = plan.row_hi - plan.row_lo
+        self.S = torch.empty((n_local, R), dtype=torch.bfloat16, device=self.dev)
+        self.g_loc = torch.empty((self.t_r, R), dtype=torch.bfloat16, device=self.dev)
+        self.side = torch.cuda.Stream(device=self.dev)
+        self.epoch = 0
+
+    @staticmethod
+    def total_bytes(T: int, R: int) -> int:
+        return PeerExchange.FLAG_BYTES + 3 * T * R * 2
+
+    @classmethod
+    def create(cls, plan: "ShardedLayerPlan", R: int, device: torch.device, group=None) -> Optional["PeerExchange"]:
+        sizes = plan.tok_sizes
+        if (plan.world < 2 or plan.world > _lib.MAX_PEERS or not dist.is_initialized() or dist.get_backend(group) != "nccl"
+                or any(n != sizes[0] for n in sizes) or sizes[0] % 32 or R % 8):
+            return None
+        # one GPU per rank: ranks that share a GPU must not wait for each other inside kernels
+        seen = [None] * plan.world
+        dist.all_gather_object(seen, str(torch.cuda.get_device_properties(device).uuid), group=group)
+        if len(set(seen)) != plan.world:
+            return None
+        nbytes = cls.total_bytes(sum(sizes), R)
+        ex = None
+        try:
+            ex = cls._from_symmetric_memory(plan, R, device, nbytes, group)
+        except Exception as e_symm:          # not available in this build / on this box: try plain CUDA IPC
+            try:
+                ex = cls._from_ipc(plan, R, device, nbytes, group)
+            except Exception as e_ipc:
+                if os.environ.get("RANDUMB_B200_DEBUG"):
+                    print(f"PeerExchange unavailable: symmetric memory: {e_symm!r}; IPC: {e_ipc!r}", flush=True)
+                ex = None
+        # every rank must take the same path
+        ok = torch.tensor([1 if ex is not None else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            return None
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)            # every rank's flags are zero before anybody signals
+        return ex
+
+    @classmethod
+    def _from_symmetric_memory(cls, plan, R, device, nbytes, group):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        grp = group if group is not None else dist.group.WORLD
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        buf.zero_()
+        torch.cuda.synchronize(device)
+        hdl = symm_mem.rendezvous(buf, grp)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        if len(ptrs) != plan.world or ptrs[plan.rank] != buf.data_ptr():
+            raise RuntimeError("symmetric memory handle does not describe this buffer")
+        return cls(plan, R, buf, ptrs, "torch symmetric memory", keep=hdl)
+
+    @classmethod
+    def _from_ipc(cls, plan, R, device, nbytes, group):
+        buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        torch.cuda.synchronize(device)
+        handle = buf.untyped_storage()._share_cuda_()
+        handles = [None] * plan.world
+        dist.all_gather_object(handles, handle, group=group)
+        ptrs, keep = [], []
+        for r, h in enumerate(handles):
+            if r == plan.rank:
+                ptrs.append(buf.data_ptr())
+                continue
+            st = torch.UntypedStorage._new_shared_cuda(*h)
+            keep.append(st)
+            ptrs.append(st.data_ptr())
+        return cls(plan, R, buf, ptrs, "CUDA IPC", keep=keep)
+
+    def barrier(self) -> None:
+        """Enqueue this rank's barrier kernel on the current stream (same sequence of calls on every rank)."""
+        from . import kernels as K
+        self.epoch += 1
+        K.peer_barrier(self.ptrs, self.rank, self.world, self.epoch, self.dev)
+
+    def slice_offset(self, base: int, row: int) -> int:
+        return base + row * self.R * 2
+
+
+def sharded_forward_peer(x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan, ex: PeerExchange,
+                         timer: Optional[PhaseTimer] = None) -> torch.Tensor:
+    """``sharded_forward`` with the z all-gather done by this library's kernels: this rank's noise rows are hashed on a side
+    stream while the tensor cores compute the local token slice of z, which is written into this rank's copy of ``z_full``
+    and then stored into every peer's copy; after the barrier every rank holds all of z and computes its columns of y."""
+    from . import kernels as K
+    cur = torch.cuda.current_stream(ex.dev)
+    ex.side.wait_stream(cur)
+    with torch.cuda.stream(ex.side):
+        K.noise(ex.S.shape[0], ex.R, seed, plan.row_lo, 0, out=ex.S)
+    z_loc = ex.z_full[plan.tok_lo:plan.tok_hi]
+    K.gemm_dense(x[plan.tok_lo:plan.tok_hi], coef, out=z_loc)                                  # [t_r, R], in place in z_full
+    _mark(timer, "z product")
+    K.peer_copy(_others(ex), ex.world - 1, ex.slice_offset(ex.z_off, plan.tok_lo), z_loc)
+    ex.barrier()
+    _mark(timer, "z exchange")
+    cur.wait_stream(ex.side)
+    y = K.gemm_dense(ex.z_full, ex.S)                                                           # [T, n_r] = z S_r^T
+    _mark(timer, "y product")
+    return y
+
+
+def _others(ex: PeerExchange):
+    """Pointer list of the other ranks' buffers (this rank's own copy is written by the local kernel)."""
+    from . import kernels as K
+    if not hasattr(ex, "_others"):
+        ex._others = K._ptr_array([ex.ptrs[r] for r in range(ex.world) if r != ex.rank])
+    return ex._others
+
+
+def sharded_backward_peer(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan,
+                          ex: PeerExchange, timer: Optional[PhaseTimer] = None, fused_scatter: bool = True
+                          ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``sharded_backward(replicate=False)`` -- (dX[tok_lo:tok_hi, :], dC[:, k_lo:k_hi]) -- with the sum of g over the ranks
+    done by this library's kernels.  The partial g = dY_r S_r leaves the product kernel's epilogue tile by tile straight into
+    the owner of each token slice (``rdb_gemm_dense_scatter``: the scatter half of a reduce-scatter fused into the product);
+    after a barrier every rank sums the G contributions to its slice in rank order; the reduced slice is stored into every
+    rank's ``g_full`` on a side stream while the tensor cores compute dX from it; dC (all tokens, this rank's input
+    features) follows the second barrier."""
+    from . import kernels as K
+    R, G = ex.R, ex.world
+    cur = torch.cuda.current_stream(ex.dev)
+    K.noise(ex.S.shape[0], R, seed, plan.row_lo, 0, out=ex.S)
+    _mark(timer, "noise fill")
+    slot = ex.parts_off + ex.rank * ex.t_r * R * 2            # my slot in every owner's g_parts
+    done = fused_scatter and K.gemm_dense_scatter(ex.ptrs, G, slot, ex.t_r, dy_local, ex.S, b_kmajor=False)
+    if not done:
+        g = K.gemm_dense(dy_local, ex.S, True, False)                                        # partial [T, R]
+        K.peer_scatter(ex.ptrs, G, slot, g)
+    _mark(timer, "g product")
+    ex.barrier()
+    K.reduce_slots(ex.g_loc, ex.g_parts)                                                      # [t_r, R], summed in rank order
+    _mark(timer, "g exchange")
+    ex.side.wait_stream(cur)
+    with torch.cuda.stream(ex.side):
+        K.peer_copy(ex.ptrs, G, ex.slice_offset(ex.gfull_off, plan.tok_lo), ex.g_loc, max_blocks=32)
+        ex.barrier()
+    # the copy's 32 small blocks need somewhere to run while the persistent product holds one CTA per SM: leave them 20 SMs
+    # (64 CTA pairs are still resident, one per 512 x 256 tile of a 512-token slice with 16384 input features)
+    dx_loc = K.gemm_dense(ex.g_loc, coef, True, False, options=_lib.CallOptions(reserve_sms=20))   # [t_r, K]
+    _mark(timer, "dX product")
+    cur.wait_stream(ex.side)
+    _mark(timer, "g all-gather tail")
+    k_lo, k_hi = shard_range(x.shape[1], plan.world, plan.rank)
+    dc_cols = K.gemm_dense(ex.g_full, x[:, k_lo:k_hi], False, False)                          # [R, k_r]
+    _mark(timer, "dC product")
+    return dx_loc, dc_cols
+
+
+# ------------------------------------------------------------------------------------------------
 # data-parallel backward with the dC all-reduce hidden behind the dX product
 # ------------------------------------------------------------------------------------------------
 def data_parallel_backward(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, row0: int = 0, group=None,

@@ -115,6 +115,31 @@ def test_association_and_kernel_decision_table(built_lib):
     assert L.rdb_linear_workspace_bytes(1, 8192, k, n, r, _lib.BF16, 0, 0) == n * r * 2 + 2 * n * k * 2
 
 
+def test_peer_exchange_arguments_are_checked_on_host(built_lib):
+    L = _lib.lib()
+    ok = 0x7F0000001000
+    two = (ctypes.c_void_p * 2)(ok, ok + 4096)
+    bad = (ctypes.c_void_p * 2)(ok, ok + 8)                                 # second pointer not 16-byte aligned
+    nul = (ctypes.c_void_p * 2)(ok, None)
+    assert L.rdb_peer_barrier(None, 0, 2, 1, None, None) == -9
+    assert L.rdb_peer_barrier(two, 2, 2, 1, None, None) == -9              # rank out of range
+    assert L.rdb_peer_barrier(two, 0, 2, 0, None, None) == -9              # epochs start at 1
+    assert L.rdb_peer_barrier(two, 0, 9, 1, None, None) == -9              # more than RDB_MAX_PEERS
+    assert L.rdb_peer_barrier(nul, 0, 2, 1, None, None) == -9
+    assert L.rdb_peer_copy(bad, 2, 0, ok, 64, 0, None) == -9
+    assert L.rdb_peer_copy(two, 2, 8, ok, 64, 0, None) == -4               # offset not a multiple of 16
+    assert L.rdb_peer_copy(two, 2, 0, ok, 0, 0, None) == 0                 # nothing to copy
+    assert L.rdb_peer_scatter(two, 2, 0, ok + 4, 64, 0, None) == -4
+    assert L.rdb_reduce_slots_bf16(ok, ok, 64, 0, 64, None) == -9
+    assert L.rdb_reduce_slots_bf16(ok, ok, 64, 2, 0, None) == 0
+    # fused product + scatter: destinations, block size and shape are validated before anything is launched
+    assert L.rdb_gemm_dense_scatter(two, 2, 0, 500, ok, ok, 1024, 256, 264, 264, 256, 0, None, None, None) == -9   # 500 % 32
+    assert L.rdb_gemm_dense_scatter(two, 2, 0, 256, ok, ok, 1024, 256, 264, 264, 256, 0, None, None, None) == -9   # 4 blocks, 2 destinations
+    assert L.rdb_gemm_dense_scatter(two, 2, 0, 512, ok, ok, 1024, 72, 264, 264, 72, 0, None, None, None) == -6     # too narrow for the pair kernel
+    assert L.rdb_gemm_dense_scatter(two, 2, 0, 512, ok, ok, 1024, 256, 264, 100, 256, 0, None, None, None) == -2   # lda < Kc
+    assert "peer" in _lib.strerror(-9)
+
+
 def test_workspace_sizes(built_lib):
     L = _lib.lib()
     # bf16 factored on tensor cores: z or g, bf16 [T, R], plus S bf16 [N, R] when the noise operand is staged
