@@ -104,12 +104,14 @@ const char *rdb_strerror(int code);
  *                        CTA.  Their CTAs take a whole SM each for the length of the launch, so a collective enqueued
  *                        beside them (an NCCL all-reduce of the previous product's result) only runs at the same time
  *                        if some SMs are left free.  Meant to be given per call, for the launch that should overlap.
- *   RDB_OPT_FILL_OVERLAP 1 (default): rdb_linear_fwd hashes the staged S on a stream of the library's own, forked from
- *                        and joined back into the caller's stream with events, so the integer-ALU fill runs beside the
- *                        tensor-core product z = x C^T it does not depend on.  The stream and its two events are created
- *                        once per device by the first such call (make it before any stream capture; a call that finds
- *                        its stream capturing before they exist keeps the fill on the caller's stream).  0: always on
- *                        the caller's stream.
+ *   RDB_OPT_FILL_OVERLAP 1 (default): automatic -- when S has 64 Mi elements or more, rdb_linear_fwd hashes the staged S on
+ *                        a stream of the library's own, forked from and joined back into the caller's stream with events,
+ *                        so the integer-ALU fill runs beside the tensor-core product z = x C^T it does not depend on (a
+ *                        shorter fill stays on the caller's stream: beside a short product its resident threads cost the
+ *                        product's MMA-issuing thread as much as the fill takes).  The stream and its two events are
+ *                        created once per device by the first such call (make it before any stream capture; a call that
+ *                        finds its stream capturing before they exist keeps the fill on the caller's stream).
+ *                        0: always on the caller's stream.   2: always beside the z product.
  * rdb_set_option returns the previous default, or RDB_ERR_UNSUPPORTED for an unknown key or a value outside the
  * range above (nothing changes then); a call whose rdb_call_options holds such a value returns the same error.
  */
@@ -259,9 +261,15 @@ int rdb_gemv_fwd_static(float *y, const float *x, const float *coef, int64_t K, 
                         int64_t row0, uint32_t seed, void *stream);
 
 /*
- * Batch-1 float32 backward: g = S^T dy (workspace, R floats), dx[K] = g C, dc[R,K] = g x^T.
- * dx or dc may be NULL.
+ * Batch-1 float32 backward: g = S^T dy, dx[K] = g C, dc[R,K] = g x^T.  dx or dc may be NULL.
+ * workspace: rdb_gemv_bwd_workspace_bytes(K, N, R) bytes, 256-byte aligned (g, the per-slice partial sums of dx -- the pass
+ * over C is cut into row slices so that enough blocks keep HBM busy, and the slices are added in a fixed order -- and one
+ * arrival counter per 32 columns; contents on entry do not matter).
+ * The four kernels of a forward + backward step are launched with programmatic stream serialization: each one's blocks
+ * become resident while the previous kernel of the stream is still running and wait for its completion on the device,
+ * which takes the launch gap out of a step that is only a few microseconds of memory traffic.
  */
+size_t rdb_gemv_bwd_workspace_bytes(int64_t K, int64_t N, int64_t R);
 int rdb_gemv_bwd(float *dx, float *dc, const float *dy, const float *x, const float *coef, float *workspace,
                  int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed, void *stream);
 

@@ -66,6 +66,7 @@ PROTOTYPES = {
     "rdb_linear_weight": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _u32, _i32, _vp]),
     "rdb_gemv_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_gemv_fwd_static": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
+    "rdb_gemv_bwd_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "rdb_gemv_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _u32, _vp]),
     "rdb_gemm_noise": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i64, _i64, _u32, _i32, _vp, _vp]),
     "rdb_gemm_dense": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp,

@@ -20,7 +20,7 @@ static bool opt_in_range(int key, int v) {
         case RDB_OPT_DENSE_PAIR: return v >= 0 && v <= 2;
         case RDB_OPT_STAGE_NOISE: return v >= 0 && v <= 2;
         case RDB_OPT_RESERVE_SMS: return v >= 0 && v <= RDB_MAX_RESERVE_SMS;
-        case RDB_OPT_FILL_OVERLAP: return v == 0 || v == 1;
+        case RDB_OPT_FILL_OVERLAP: return v >= 0 && v <= 2;
         default: return false;
     }
 }
@@ -100,7 +100,7 @@ struct WsLayout {
 //   UMMA W path    fwd: S bf16[N,R], W bf16[N,K]      bwd: S bf16[N,R], W bf16[N,K], dW bf16[N,K]
 //   SIMT factored  fwd: z f32[T,R]           bwd: g f32[T,R]
 //   SIMT W path    fwd: W f32[N,K]           bwd: W f32[N,K], dW f32[N,K]
-static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, int path, int impl, const CallOpts &o) {
+static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, int path, int impl, const CallOpts &o, int dtype) {
     WsLayout w{};
     size_t seg[4] = {0, 0, 0, 0};
     if (path == RDB_PATH_FACTORED) {
@@ -120,6 +120,8 @@ static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, in
             }
         } else {
             seg[0] = (size_t)T * R * 4;
+            // a single float32 row goes to the matrix-vector kernels, whose backward keeps per-slice sums and counters too
+            if (T == 1 && dtype == RDB_F32 && op == 1) seg[0] = rdb_gemv_bwd_workspace_bytes(K, N, R);
         }
     } else if (impl == RDB_IMPL_UMMA) {
         seg[0] = (size_t)N * R * 2;
@@ -321,7 +323,7 @@ extern "C" size_t rdb_linear_workspace_bytes_ex(int op, int64_t T, int64_t K, in
     const int p = choose_path(path, T, K, N, R);
     const int im = choose_impl(impl, T, K, N, R, dtype, p, true);
     if (im < 0) return 0;
-    return ws_layout(op, T, K, N, R, p, im, o).total;
+    return ws_layout(op, T, K, N, R, p, im, o, dtype).total;
 }
 
 extern "C" size_t rdb_linear_workspace_bytes(int op, int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path,
@@ -411,7 +413,7 @@ extern "C" int rdb_linear_fwd_ex(void *y, const void *x, const void *coef, void 
     const int p = choose_path(path, T, K, N, R);
     const int im = choose_impl(impl, T, K, N, R, dtype, p, aligned16(x) && aligned16(coef) && aligned16(y));
     if (im < 0) return im;
-    const WsLayout w = ws_layout(0, T, K, N, R, p, im, o);
+    const WsLayout w = ws_layout(0, T, K, N, R, p, im, o, dtype);
     if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return RDB_ERR_WORKSPACE;
     uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
     const Sq5Lin rows = sq5_lin_rows(seed, (uint32_t)row0, 0);
@@ -422,8 +424,12 @@ extern "C" int rdb_linear_fwd_ex(void *y, const void *x, const void *coef, void 
             void *z = ws + w.off[0];
             const bool staged = stage_noise(T, N, R, o);
             void *S = ws + w.off[1];
-            // the hash of S (integer ALU) does not depend on z = x C^T (tensor pipe): run it beside that product
-            SideStream *side = (staged && o.fill_overlap) ? side_stream(st) : nullptr;
+            // the hash of S (integer ALU) does not depend on z = x C^T (tensor pipe), so a long fill runs beside that product.
+            // A short one does not: the fill's two thousand resident threads per SM slow the product's single MMA-issuing
+            // thread down by about as much as the fill takes (measured: 16.8 M elements beside a 40-50 us product lose,
+            // 67 M and more beside a 100-180 us product win 20 us)
+            const bool beside = o.fill_overlap == 2 || (o.fill_overlap == 1 && (double)N * (double)R >= 64.0 * 1024 * 1024);
+            SideStream *side = (staged && beside) ? side_stream(st) : nullptr;
             std::unique_lock<std::mutex> side_lock;
             if (side) side_lock = std::unique_lock<std::mutex>(side->mu);
             if (staged && side) {
@@ -502,7 +508,7 @@ extern "C" int rdb_linear_bwd_ex(void *dx, void *dc, const void *dy, const void 
     const bool al = aligned16(dy) && aligned16(dx) && aligned16(dc) && (!dx || aligned16(coef)) && (!dc || aligned16(x));
     const int im = choose_impl(impl, T, K, N, R, dtype, p, al);
     if (im < 0) return im;
-    const WsLayout w = ws_layout(1, T, K, N, R, p, im, o);
+    const WsLayout w = ws_layout(1, T, K, N, R, p, im, o, dtype);
     if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return RDB_ERR_WORKSPACE;
     uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
     const Sq5Lin rows = sq5_lin_rows(seed, (uint32_t)row0, 0);

@@ -29,6 +29,37 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// ---- programmatic dependent launch -------------------------------------------------------------------
+// The products of one layer call are a chain of kernels, each a few to a few hundred microseconds long; the gap between one
+// kernel's last block and the next kernel's first block (a few microseconds) is paid once per link.  The kernels of this
+// library are launched with the programmatic-serialization attribute: their blocks may become resident -- and run their
+// prologue: barrier initialisation, TMEM allocation, tensor-map prefetch -- while the previous kernel of the stream is
+// still running, wait in pdl_wait() until that kernel has completed and its writes are visible, and let the launch of the
+// kernel after them proceed with pdl_launch_dependents().  Nothing a predecessor may have written is touched before
+// pdl_wait().  (Both are no-ops for a launch without the attribute; the attribute is captured into CUDA graphs.)
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// <<<grid, block, smem, stream>>> with programmatic stream serialization allowed
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kern)(KArgs...), dim3 grid, int block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return (int)e;
+    return launch_status();
+}
+#endif
+
 // ---- implemented in simt.cu ------------------------------------------------------------------
 // D(m,n) = sum_k A(m,k) * B(n,k); element (i,j) of an operand lives at base[i*rs + j*cs].
 // When b == nullptr the B operand is generated: B(n,k) = value(lin.base + n*lin.sn + k*lin.sk).

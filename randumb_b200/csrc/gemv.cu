@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(256) gemv_cx_kernel(float *__restrict__ z, con
     const int64_t r = blockIdx.x;
     const float *row = C + r * K;
     float acc = 0.0f;
+    pdl_launch_dependents();
+    pdl_wait();
     const bool vec = ((K & 3) == 0) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     if (vec) {
@@ -54,6 +56,8 @@ __global__ void __launch_bounds__(256) gemv_cx_kernel(float *__restrict__ z, con
 __global__ void __launch_bounds__(256) gemv_sz_kernel(float *__restrict__ y, const float *__restrict__ z, int64_t N,
                                                       int64_t R, Sq5Lin lin) {
     const int64_t o = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    pdl_launch_dependents();
+    pdl_wait();
     if (o >= N) return;
     const int lane = threadIdx.x & 31;
     const uint32_t rowb = lin.base + (uint32_t)o * lin.sn;
@@ -64,12 +68,16 @@ __global__ void __launch_bounds__(256) gemv_sz_kernel(float *__restrict__ y, con
     if (lane == 0) y[o] = acc;
 }
 
-// g[k] = sum_o dy[o] * S[row0+o, k]; one block per noise column k.
+// g[k] = sum_o dy[o] * S[row0+o, k]; one block per noise column k.  Also clears the arrival counters of the kernel that
+// follows (one per 32-column group).
 __global__ void __launch_bounds__(256) gemv_stdy_kernel(float *__restrict__ g, const float *__restrict__ dy, int64_t N,
-                                                        Sq5Lin lin) {
+                                                        Sq5Lin lin, unsigned int *__restrict__ counters, int64_t ncounters) {
     __shared__ float red[8];
     const uint32_t colb = lin.base + (uint32_t)blockIdx.x * lin.sk;
     float acc = 0.0f;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < ncounters; i += (int64_t)gridDim.x * 256) counters[i] = 0u;
     for (int64_t o = threadIdx.x; o < N; o += 256)
         acc = fmaf(sq5_to_float(sq5_tail(colb + (uint32_t)o * lin.sn)), __ldg(dy + o), acc);
     acc = warp_sum(acc);
@@ -84,23 +92,33 @@ __global__ void __launch_bounds__(256) gemv_stdy_kernel(float *__restrict__ g, c
 }
 
 // dx[i] = sum_r g[r] * C[r,i]  and  dc[r,i] = g[r] * x[i], one pass over C.
-// A block owns 32 columns (8 lanes x float4 = one 128-byte line per row) and walks all rows
-// with 32 row slots; slot partials of dx are summed in a fixed order.
+// A block owns 32 columns (8 lanes x float4 = one 128-byte line per row) and one of gridDim.y slices of the rows, which it
+// walks with 32 row slots: K/32 x gridDim.y blocks keep enough bytes in flight for HBM (C read once, dC written once).
+// dx: every block writes its slice's partial sums to `part[slice][K]`; the block of a column group that arrives last
+// (one counter per group, cleared by the previous kernel) adds the slices in slice order, so the result does not depend
+// on which block that was.
 __global__ void __launch_bounds__(256) gemv_dxdc_kernel(float *__restrict__ dx, float *__restrict__ dc,
                                                         const float *__restrict__ g, const float *__restrict__ x,
-                                                        const float *__restrict__ C, int64_t K, int64_t R) {
-    __shared__ float part[32][33];
+                                                        const float *__restrict__ C, int64_t K, int64_t R,
+                                                        float *__restrict__ part, unsigned int *__restrict__ counters) {
+    __shared__ float sums[32][33];
+    __shared__ unsigned int arrived;
     const int slot = threadIdx.x >> 3;  // 0..31
     const int l8 = threadIdx.x & 7;     // 0..7
     const int64_t c0 = (int64_t)blockIdx.x * 32 + l8 * 4;
+    const int nsl = gridDim.y, sl = blockIdx.y;
+    const int64_t rows_per = (R + nsl - 1) / nsl;
+    const int64_t r_lo = sl * rows_per, r_hi = (r_lo + rows_per < R) ? r_lo + rows_per : R;
     float ax[4] = {0.f, 0.f, 0.f, 0.f};
     float xv[4] = {0.f, 0.f, 0.f, 0.f};
     const bool vec = ((K & 3) == 0) && (c0 + 3 < K) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) &&
                      (dc == nullptr || (reinterpret_cast<uintptr_t>(dc) & 15) == 0);
+    pdl_launch_dependents();
+    pdl_wait();
 #pragma unroll
     for (int j = 0; j < 4; ++j)
         if (dc && c0 + j < K) xv[j] = x[c0 + j];
-    for (int64_t r = slot; r < R; r += 32) {
+    for (int64_t r = r_lo + slot; r < r_hi; r += 32) {
         const float gr = __ldg(g + r);
         if (vec) {
             if (dx) {
@@ -124,14 +142,30 @@ __global__ void __launch_bounds__(256) gemv_dxdc_kernel(float *__restrict__ dx, 
     }
     if (!dx) return;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) part[slot][l8 * 4 + j] = ax[j];
+    for (int j = 0; j < 4; ++j) sums[slot][l8 * 4 + j] = ax[j];
     __syncthreads();
+    const int64_t c = (int64_t)blockIdx.x * 32 + threadIdx.x;
     if (threadIdx.x < 32) {
         float s = 0.0f;
 #pragma unroll
-        for (int sidx = 0; sidx < 32; ++sidx) s += part[sidx][threadIdx.x];
-        const int64_t c = (int64_t)blockIdx.x * 32 + threadIdx.x;
-        if (c < K) dx[c] = s;
+        for (int sidx = 0; sidx < 32; ++sidx) s += sums[sidx][threadIdx.x];
+        if (nsl == 1) {
+            if (c < K) dx[c] = s;
+        } else if (c < K) {
+            part[(int64_t)sl * K + c] = s;
+        }
+    }
+    if (nsl == 1) return;
+    __threadfence();                       // this block's partial sums are visible before it is counted
+    __syncthreads();
+    if (threadIdx.x == 0) arrived = atomicAdd(&counters[blockIdx.x], 1u);
+    __syncthreads();
+    if (arrived != (unsigned)(nsl - 1)) return;
+    __threadfence();                       // the last block of the group: the other slices' sums are visible to it
+    if (threadIdx.x < 32 && c < K) {
+        float s = 0.0f;
+        for (int q = 0; q < nsl; ++q) s += __ldcg(part + (int64_t)q * K + c);
+        dx[c] = s;
     }
 }
 
@@ -159,9 +193,27 @@ static int gemv_static_scratch(float **out) {
     return RDB_OK;
 }
 
+// row slices of the dX / dC kernel: enough blocks to keep HBM busy (about four per SM), at least 32 rows per slice
+static int dxdc_slices(int64_t K, int64_t R) {
+    const int64_t groups = cdiv64(K, 32);
+    int64_t want = cdiv64(148 * 4, groups);
+    if (want > R / 32) want = R / 32;
+    if (want > 16) want = 16;
+    int s = 1;
+    while (2 * s <= want) s *= 2;          // a power of two: every slice is a whole number of 32-row passes when R is one too
+    return s;
+}
+
 }  // namespace rdb
 
 using namespace rdb;
+
+extern "C" size_t rdb_gemv_bwd_workspace_bytes(int64_t K, int64_t N, int64_t R) {
+    (void)N;
+    if (K <= 0 || R <= 0) return 0;
+    // g[R], then per-slice partial sums of dx [slices, K], then one arrival counter per 32-column group
+    return (size_t)(align_up((size_t)R * 4, 256) + align_up((size_t)dxdc_slices(K, R) * K * 4, 256) + align_up((size_t)cdiv64(K, 32) * 4, 256));
+}
 
 extern "C" int rdb_gemv_fwd(float *y, const float *x, const float *coef, float *workspace, int64_t K, int64_t N,
                             int64_t R, int64_t row0, uint32_t seed, void *stream) {
@@ -171,12 +223,11 @@ extern "C" int rdb_gemv_fwd(float *y, const float *x, const float *coef, float *
     if (R > 0x7fffffffLL || cdiv64(N, 8) > 0x7fffffffLL) return RDB_ERR_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream;
     if (R > 0) {
-        gemv_cx_kernel<<<(unsigned)R, 256, 0, st>>>(workspace, coef, x, K);
-        int rc = launch_status();
+        int rc = launch_pdl(gemv_cx_kernel, dim3((unsigned)R), 256, 0, st, workspace, coef, x, K);
         if (rc) return rc;
     }
-    gemv_sz_kernel<<<(unsigned)cdiv64(N, 8), 256, 0, st>>>(y, workspace, N, R, sq5_lin_rows(seed, (uint32_t)row0, 0));
-    return launch_status();
+    return launch_pdl(gemv_sz_kernel, dim3((unsigned)cdiv64(N, 8)), 256, 0, st, y, (const float *)workspace, N, R,
+                      sq5_lin_rows(seed, (uint32_t)row0, 0));
 }
 
 extern "C" int rdb_gemv_fwd_static(float *y, const float *x, const float *coef, int64_t K, int64_t N, int64_t R, int64_t row0,
@@ -206,9 +257,16 @@ extern "C" int rdb_gemv_bwd(float *dx, float *dc, const float *dy, const float *
     }
     if (!workspace || (N > 0 && !dy) || (dx && !coef) || (dc && !x)) return RDB_ERR_NULL;
     if (R > 0x7fffffffLL || cdiv64(K, 32) > 0x7fffffffLL) return RDB_ERR_TOO_LARGE;
-    gemv_stdy_kernel<<<(unsigned)R, 256, 0, st>>>(workspace, dy, N, sq5_lin_rows(seed, (uint32_t)row0, 0));
-    int rc = launch_status();
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return RDB_ERR_WORKSPACE;
+    const int slices = dxdc_slices(K, R);
+    uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
+    float *g = workspace;
+    float *part = reinterpret_cast<float *>(ws + align_up((size_t)R * 4, 256));
+    unsigned int *counters = reinterpret_cast<unsigned int *>(ws + align_up((size_t)R * 4, 256) + align_up((size_t)slices * K * 4, 256));
+    const int64_t groups = cdiv64(K, 32);
+    int rc = launch_pdl(gemv_stdy_kernel, dim3((unsigned)R), 256, 0, st, g, dy, N, sq5_lin_rows(seed, (uint32_t)row0, 0), counters,
+                        slices > 1 ? groups : (int64_t)0);
     if (rc) return rc;
-    gemv_dxdc_kernel<<<(unsigned)cdiv64(K, 32), 256, 0, st>>>(dx, dc, workspace, x, coef, K, R);
-    return launch_status();
+    return launch_pdl(gemv_dxdc_kernel, dim3((unsigned)groups, (unsigned)slices), 256, 0, st, dx, dc, (const float *)g, x, coef, K, R,
+                      part, counters);
 }

@@ -64,6 +64,8 @@ __global__ void noise_kernel(void *__restrict__ out, int64_t rows, int64_t cols,
 // all index arithmetic is 32-bit.
 __global__ void __launch_bounds__(256) noise_bf16x8_kernel(uint4 *__restrict__ out, uint32_t total, uint32_t cgroups,
                                                            uint32_t ld_groups, Sq5Lin lin) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const uint32_t r = idx / cgroups;
         const uint32_t cg = idx - r * cgroups;
@@ -84,6 +86,8 @@ __global__ void __launch_bounds__(256) noise_bf16_seg_kernel(uint4 *__restrict__
                                                              uint32_t ld_groups, Sq5Lin lin) {
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warps = (gridDim.x * blockDim.x) >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
     for (uint32_t w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total_segs; w += warps) {
         const uint32_t r = w / segs_per_row;
         const uint32_t sg = w - r * segs_per_row;
@@ -126,16 +130,14 @@ static int launch_noise(void *out, int64_t rows, int64_t cols, int64_t ld, int64
             const uint32_t total_segs = (uint32_t)(rows * (cols >> 10));
             const int64_t want = cdiv64(total_segs, 8);        // eight warps per block, one segment per warp and pass
             const int grid = (int)(want < 148 * 8 ? (want < 1 ? 1 : want) : 148 * 8);
-            noise_bf16_seg_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<uint4 *>(out), total_segs, (uint32_t)(cols >> 10),
-                                                       (uint32_t)(ld >> 3), lin);
-            return launch_status();
+            return launch_pdl(noise_bf16_seg_kernel, dim3(grid), 256, 0, st, reinterpret_cast<uint4 *>(out), total_segs,
+                              (uint32_t)(cols >> 10), (uint32_t)(ld >> 3), lin);
         }
         const uint32_t total = (uint32_t)(rows * (cols >> 3));
         const int64_t want = cdiv64(total, 256 * 4);           // about four groups (32 elements) per thread
         const int grid = (int)(want < 148 * 8 ? (want < 1 ? 1 : want) : 148 * 8);
-        noise_bf16x8_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<uint4 *>(out), total, (uint32_t)(cols >> 3),
-                                                 (uint32_t)(ld >> 3), lin);
-        return launch_status();
+        return launch_pdl(noise_bf16x8_kernel, dim3(grid), 256, 0, st, reinterpret_cast<uint4 *>(out), total, (uint32_t)(cols >> 3),
+                          (uint32_t)(ld >> 3), lin);
     }
     const int64_t items = rows * ((cols + 3) >> 2);
     noise_kernel<MODE><<<grid_for(items, 256), 256, 0, st>>>(out, rows, cols, ld, lin);

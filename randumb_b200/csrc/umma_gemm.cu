@@ -174,6 +174,8 @@ noise_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, __nv_bfloat16 *__r
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_holder;
     volatile int *abortp = &abort_flag;
+    pdl_launch_dependents();   // the next kernel of the stream may start its own prologue
+    pdl_wait();                // ... and this one touches global memory only after its predecessor has completed
 
     const int64_t tiles_n = (N + BN - 1) / BN;
     const int64_t tiles_m = (M + (int64_t)MT * BM - 1) / ((int64_t)MT * BM);
@@ -490,6 +492,8 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_holder;
     volatile int *abortp = &abort_flag;
+    pdl_launch_dependents();   // the next kernel of the stream may start its own prologue
+    pdl_wait();                // ... and this one touches global memory only after its predecessor has completed
 
     const int64_t tiles_n = (N + BN - 1) / BN;
     const int64_t tiles_m = (M + (int64_t)MT * 2 * BM - 1) / ((int64_t)MT * 2 * BM);   // 512-token pair tiles
@@ -820,6 +824,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_holder;
     volatile int *abortp = &abort_flag;
+    pdl_launch_dependents();   // the next kernel of the stream may start its own prologue
+    pdl_wait();                // ... and this one touches global memory only after its predecessor has completed
 
     const int64_t tiles_n = (N + BN - 1) / BN;
     const int64_t tiles_m = (M + BM - 1) / BM;
@@ -1105,6 +1111,8 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_holder;
     volatile int *abortp = &abort_flag;
+    pdl_launch_dependents();   // the next kernel of the stream may start its own prologue
+    pdl_wait();                // ... and this one touches global memory only after its predecessor has completed
 
     const int64_t tiles_m = (M + (int64_t)MT * 2 * BM - 1) / ((int64_t)MT * 2 * BM);
     const int64_t tiles_n = (N + BN - 1) / BN;
@@ -1439,13 +1447,15 @@ static int launch_noise_gemm(void *d, const void *a, int64_t M, int64_t N, int64
     cfg.blockDim = dim3(Cfg::THREADS);
     cfg.dynamicSmemBytes = Cfg::SMEM_DYN;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 1;                       // the occupancy query below sees the cluster shape only
     int max_clusters = sm_count() / CS;
     if (CS > 1) {
         cfg.gridDim = dim3(CS);
@@ -1455,6 +1465,7 @@ static int launch_noise_gemm(void *d, const void *a, int64_t M, int64_t N, int64
     }
     const int64_t nclusters = ctiles < max_clusters ? ctiles : max_clusters;
     cfg.gridDim = dim3((unsigned)(nclusters * CS));
+    cfg.numAttrs = 2;
     __nv_bfloat16 *dp = reinterpret_cast<__nv_bfloat16 *>(d);
     long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 16 * sizeof(long long)) ? g_prof : nullptr;
     e = cudaLaunchKernelEx(&cfg, kern, ta, dp, ldd, M, N, Kc, lin, status, prof);
@@ -1481,19 +1492,22 @@ static int launch_noise_pair(void *d, const void *a, int64_t M, int64_t N, int64
     cfg.blockDim = dim3(Cfg::THREADS);
     cfg.dynamicSmemBytes = Cfg::SMEM_DYN;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CSZ;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 1;                       // the occupancy query below sees the cluster shape only
     cfg.gridDim = dim3(CSZ);
     int max_clusters = sm_count() / CSZ, n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) max_clusters = n;
     else (void)cudaGetLastError();
     const int64_t nclusters = ctiles < max_clusters ? ctiles : max_clusters;
     cfg.gridDim = dim3((unsigned)(nclusters * CSZ));
+    cfg.numAttrs = 2;
     long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 16 * sizeof(long long)) ? g_prof : nullptr;
     e = cudaLaunchKernelEx(&cfg, kern, ta, td, M, N, Kc, lin, status, prof);
     if (e != cudaSuccess) return (int)e;
@@ -1560,9 +1574,8 @@ static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_
     const int grid = (int)(tiles < ctas ? tiles : ctas);
     // tiles that run at the same time share the panel of the larger operand, which is then streamed from memory once
     const int m_fast = (M <= N) ? 1 : 0;
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_DYN, st>>>(ta, tb, td, reinterpret_cast<OutT *>(d), ldd, M, N, Kc, m_fast, split, slice_stride,
-                                                    f32_tma, status);
-    return launch_status();
+    return launch_pdl(kern, dim3(grid), Cfg::THREADS, Cfg::SMEM_DYN, st, ta, tb, td, reinterpret_cast<OutT *>(d), ldd, M, N, Kc, m_fast,
+                      split, slice_stride, f32_tma, status);
 }
 
 template <int MT, int D, int A_MN, int B_MN, int NDST>
@@ -1591,13 +1604,15 @@ static int launch_dense_pair(void *const *dsts, int64_t rows_per_dst, const void
     cfg.blockDim = dim3(Cfg::THREADS);
     cfg.dynamicSmemBytes = Cfg::SMEM_DYN;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     int pairs = max_pairs - (reserve_sms + 1) / 2;
     if (pairs < 1) pairs = 1;
     const int64_t npairs = tiles < pairs ? tiles : pairs;
@@ -1690,6 +1705,8 @@ template <typename OutT>
 __global__ void split_k_reduce_kernel(OutT *__restrict__ out, const float *__restrict__ partials, int64_t n4, int split,
                                       int64_t slice_stride4) {
     const float4 *p = reinterpret_cast<const float4 *>(partials);
+    pdl_launch_dependents();
+    pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
         float4 acc = p[i];
         for (int s = 1; s < split; ++s) {
@@ -1729,10 +1746,10 @@ int umma_gemm_dense_split_k(void *d, const void *a, const void *b, float *partia
     const int64_t n4 = stride / 4;
     const int grid = (int)(cdiv64(n4, 256) < 148 * 8 ? cdiv64(n4, 256) : 148 * 8);
     if (d_dtype == RDB_BF16)
-        split_k_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16 *>(d), partials, n4, split, stride / 4);
-    else
-        split_k_reduce_kernel<float><<<grid, 256, 0, st>>>(reinterpret_cast<float *>(d), partials, n4, split, stride / 4);
-    return launch_status();
+        return launch_pdl(split_k_reduce_kernel<__nv_bfloat16>, dim3(grid), 256, 0, st, reinterpret_cast<__nv_bfloat16 *>(d),
+                          (const float *)partials, n4, split, stride / 4);
+    return launch_pdl(split_k_reduce_kernel<float>, dim3(grid), 256, 0, st, reinterpret_cast<float *>(d), (const float *)partials, n4,
+                      split, stride / 4);
 }
 
 // D = A op(B)^T on CTA pairs with row block j of D stored into dsts[j] (dense [rows_per_dst x N] bf16 each, possibly in

@@ -222,7 +222,7 @@ def gemv_bwd(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, r
     N = dy.numel()
     dx = torch.empty((K,), dtype=torch.float32, device=dev) if need_dx else None
     dc = torch.empty((R, K), dtype=torch.float32, device=dev) if need_dc else None
-    ws = torch.empty((max(R, 1),), dtype=torch.float32, device=dev)
+    ws = _workspace(_lib.lib().rdb_gemv_bwd_workspace_bytes(K, N, R), dev)
     with torch.cuda.device(dev):
         rc = _lib.lib().rdb_gemv_bwd(_ptr(dx), _ptr(dc), _ptr(dy), _ptr(x), _ptr(coef), _ptr(ws), K, N, R, row0,
                                      _seed(seed), _stream(dev))

@@ -392,21 +392,23 @@ class PeerExchange:
 
 def sharded_forward_peer(x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan, ex: PeerExchange,
                          timer: Optional[PhaseTimer] = None) -> torch.Tensor:
-    """``sharded_forward`` with the z all-gather done by this library's kernels: this rank's noise rows are hashed on a side
-    stream while the tensor cores compute the local token slice of z, which is written into this rank's copy of ``z_full``
-    and then stored into every peer's copy; after the barrier every rank holds all of z and computes its columns of y."""
+    """``sharded_forward`` with the z all-gather done by this library's kernels: the tensor cores compute the local token
+    slice of z straight into this rank's copy of ``z_full``; the slice is then stored into every peer's copy, and while those
+    stores and the barrier are in flight (NVLink-bound, a few SMs) this rank's noise rows are hashed on a side stream (integer
+    ALU on all SMs).  After both, every rank holds all of z and computes its columns of y.  (The hash is not started beside
+    the z product: its two thousand resident threads per SM starve the product's single MMA-issuing thread.)"""
     from . import kernels as K
     cur = torch.cuda.current_stream(ex.dev)
-    ex.side.wait_stream(cur)
-    with torch.cuda.stream(ex.side):
-        K.noise(ex.S.shape[0], ex.R, seed, plan.row_lo, 0, out=ex.S)
     z_loc = ex.z_full[plan.tok_lo:plan.tok_hi]
     K.gemm_dense(x[plan.tok_lo:plan.tok_hi], coef, out=z_loc)                                  # [t_r, R], in place in z_full
     _mark(timer, "z product")
+    ex.side.wait_stream(cur)
+    with torch.cuda.stream(ex.side):
+        K.noise(ex.S.shape[0], ex.R, seed, plan.row_lo, 0, out=ex.S)
     K.peer_copy(_others(ex), ex.world - 1, ex.slice_offset(ex.z_off, plan.tok_lo), z_loc)
     ex.barrier()
-    _mark(timer, "z exchange")
     cur.wait_stream(ex.side)
+    _mark(timer, "z exchange + noise fill")
     y = K.gemm_dense(ex.z_full, ex.S)                                                           # [T, n_r] = z S_r^T
     _mark(timer, "y product")
     return y
@@ -445,9 +447,9 @@ def sharded_backward_peer(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.T
     _mark(timer, "g exchange")
     ex.side.wait_stream(cur)
     with torch.cuda.stream(ex.side):
-        K.peer_copy(ex.ptrs, G, ex.slice_offset(ex.gfull_off, plan.tok_lo), ex.g_loc, max_blocks=32)
+        K.peer_copy(ex.ptrs, G, ex.slice_offset(ex.gfull_off, plan.tok_lo), ex.g_loc, max_blocks=64)
         ex.barrier()
-    # the copy's 32 small blocks need somewhere to run while the persistent product holds one CTA per SM: leave them 20 SMs
+    # the copy's 64 small blocks need somewhere to run while the persistent product holds one CTA per SM: leave them 20 SMs
     # (64 CTA pairs are still resident, one per 512 x 256 tile of a 512-token slice with 16384 input features)
     dx_loc = K.gemm_dense(ex.g_loc, coef, True, False, options=_lib.CallOptions(reserve_sms=20))   # [t_r, K]
     _mark(timer, "dX product")

@@ -323,6 +323,29 @@ def test_partial_backward_and_graph_replay(K, T, Kin, N, R):
     K.check_status()
 
 
+def test_noise_fill_beside_the_z_product_gives_the_same_bits(K):
+    """RDB_OPT_FILL_OVERLAP: the staged noise operand hashed on the library's own stream beside z = x C^T (forced here; by
+    default only large fills take that route) -- same result bit for bit, eagerly and replayed from a CUDA graph."""
+    from randumb_b200 import _lib
+    T, Kin, N, R = 2048, 264, 520, 72
+    x, C, _ = _inputs(T, Kin, N, R, torch.bfloat16, 6)
+    xg, Cg = x.cuda(), C.cuda()
+    y_plain = K.linear_fwd(xg, Cg, 9, N, 8, options=_lib.CallOptions(fill_overlap=0))
+    beside = _lib.CallOptions(fill_overlap=2)
+    y_side = K.linear_fwd(xg, Cg, 9, N, 8, options=beside)          # also creates the stream and events, outside any capture
+    torch.cuda.synchronize()
+    assert torch.equal(y_side, y_plain)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_g = K.linear_fwd(xg, Cg, 9, N, 8, options=beside)
+    for _ in range(2):
+        y_g.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y_g, y_plain)
+    K.check_status()
+
+
 # ---- full benchmark sizes ------------------------------------------------------------------------------------------
 def test_full_size_properties(K):
     """8192 x 4096 -> 16384, d_c = 1024 (the headline configuration): size-independent properties."""
