@@ -733,6 +733,111 @@ def run_e2e(args, cfg, rb, dev, world, dt, x_host, C, n_local, row0, barrier):
 GPT2 = dict(T=8192, d=768, mlp=3072, R=128, blocks=12, seed0=13, seed_step=7, coef_std=(3 * 0.02 ** 2 / 128) ** 0.5)
 
 
+def gpt2_whole_step(args, dev, world, rank, rb, randumb_ms):
+    """One training step of a GPT-2-small-shaped model (12 pre-LN blocks, d 768, 12 heads, MLP 3072 with tanh-GELU, vocabulary
+    50257, 8 x 1024 tokens per GPU) whose MLP projections are the pseudorandom-weight layers (d_c = 128, seeds 13 + 7 i); every
+    other weight is a random bf16 tensor.  Forward, cross-entropy, backward, one flat all-reduce of the coefficient
+    gradients, fused Adam on the coefficients.  Attention, layer norms and the dense projections are PyTorch's own kernels:
+    this measures where the pseudorandom-weight layers sit in a step, not those kernels."""
+    import torch.distributed as dist
+    import torch.nn as nn
+    import torch.nn.functional as F
+    c = GPT2
+    d, mlp, R, nb, heads, vocab, B, S = c["d"], c["mlp"], c["R"], c["blocks"], 12, 50257, 8, 1024
+    dt = torch.bfloat16
+    seeds = rb.stepgen(c["seed0"], c["seed_step"])
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln1, self.ln2 = nn.LayerNorm(d), nn.LayerNorm(d)
+            self.qkv, self.proj = nn.Linear(d, 3 * d), nn.Linear(d, d)
+            self.fc = rb.RandumbLinear(d, mlp, R, next(seeds), init_std=0.02)
+            self.cproj = rb.RandumbLinear(mlp, d, R, next(seeds), init_std=0.02)
+
+        def forward(self, x):
+            b, s, _ = x.shape
+            q, k, v = self.qkv(self.ln1(x)).view(b, s, 3, heads, d // heads).permute(2, 0, 3, 1, 4)
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(b, s, d)
+            x = x + self.proj(a)
+            return x + self.cproj(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.wte, self.wpe = nn.Embedding(vocab, d), nn.Embedding(S, d)
+            self.blocks = nn.ModuleList([Block() for _ in range(nb)])
+            self.ln_f = nn.LayerNorm(d)
+            self.lm_head = nn.Linear(d, vocab, bias=False)
+
+        def forward(self, idx, targets):
+            x = self.wte(idx) + self.wpe(torch.arange(idx.shape[1], device=idx.device))
+            for blk in self.blocks:
+                x = blk(x)
+            logits = self.lm_head(self.ln_f(x))
+            return F.cross_entropy(logits.float().view(-1, vocab), targets.view(-1))
+
+    torch.manual_seed(1234)
+    model = Model()
+    for name, p in model.named_parameters():
+        if not name.endswith("weight_coef") and p.dim() >= 2:
+            nn.init.normal_(p, 0.0, 0.02)
+    model = model.to(dev).to(dt)
+    coefs = [p for n, p in model.named_parameters() if n.endswith("weight_coef")]
+    g = torch.Generator().manual_seed(1004 + rank)
+    idx_host = torch.randint(0, vocab, (B, S), generator=g).pin_memory()
+    tgt_host = torch.randint(0, vocab, (B, S), generator=g).pin_memory()
+    out = {}
+    for variant in ("frozen", "all_trainable"):
+        for n, p in model.named_parameters():
+            p.requires_grad_(variant == "all_trainable" or n.endswith("weight_coef"))
+            p.grad = None
+        params = [p for p in model.parameters() if p.requires_grad]
+        opt = torch.optim.Adam(params, lr=1e-4, fused=True)
+
+        def step():
+            idx = idx_host.to(dev, non_blocking=True)
+            tgt = tgt_host.to(dev, non_blocking=True)
+            loss = model(idx, tgt)
+            loss.backward()
+            if world > 1:
+                rb.parallel.allreduce_coef_grads(params)          # one flat bucket: the coefficients, or every weight
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            return loss
+
+        for _ in range(3):
+            loss = step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        n = max(3, min(args.steps, 10))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            loss = step()
+        e1.record()
+        first_loss = float(loss.item())
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        out[variant] = {"ms_per_step": ms, "tokens_per_s": world * B * S / (ms * 1e-3),
+                        "trainable_parameters": sum(p.numel() for p in params), "loss": first_loss,
+                        "pseudorandom_layers_share": randumb_ms / ms}
+        del opt
+    out["what"] = ("GPT-2-small-shaped step (12 blocks, d 768, 12 heads, MLP 3072, vocabulary 50257, 8 x 1024 tokens per GPU): forward, "
+                   "cross-entropy, backward, flat gradient all-reduce, fused Adam; 'frozen' trains the 24 coefficient matrices only (the "
+                   "all-reduce carries only dC), 'all_trainable' every weight.  pseudorandom_layers_share = the 24 layers' own time "
+                   "(this line's ms_per_step) over the whole step; the rest is PyTorch's attention, layer norms, dense projections, "
+                   "embedding and loss kernels")
+    out["expected_initial_loss"] = "about ln(50257) = 10.82 for random weights (modded-nanogpt/train_gpt2.py:241 of the reference)"
+    return out
+
+
 def run_gpt2mlp(args):
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -876,6 +981,11 @@ def run_gpt2mlp(args):
         cpu_baseline = {"value": fl_cpu / dt_cpu / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "cpu": cpu_model(), "kind": "port",
                         "sample": f"one block's two layers (of 12 blocks) at all {T} tokens in {dt_cpu:.2f} s: explicit S from the C "
                                   "oracle, W = S @ C, F.linear, autograd; float32"}
+    whole = None
+    if not args.no_whole_step:
+        del blocks, params
+        torch.cuda.empty_cache()
+        whole = gpt2_whole_step(args, dev, world, rank, rb, elapsed_ms / args.steps)
     if rank == 0:
         peaks = measured_peaks()
         per_gpu = value / world
@@ -895,6 +1005,8 @@ def run_gpt2mlp(args):
                          "peak_source": f"{peaks['src']} burst bf16", "traffic": None},
             "cpu_baseline": cpu_baseline,
         }
+        if whole is not None:
+            line["whole_step"] = whole
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -1016,6 +1128,8 @@ def main():
     ap.add_argument("--replicate-grads", action="store_true",
                     help="sharded workload: all-gather dX and all-reduce dC so that every rank holds both in full")
     ap.add_argument("--no-graph", action="store_true", help="gemv workload: launch the four kernels eagerly in the timed region")
+    ap.add_argument("--no-whole-step", action="store_true",
+                    help="gpt2mlp workload: skip the `whole_step` sub-record (the full GPT-2-small-shaped training step around the layers)")
     ap.add_argument("--no-sharded-record", action="store_true",
                     help="default workload: skip the `sharded` sub-record (the row-sharded 65536 x 16384 layer measured after the headline)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],

@@ -63,11 +63,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if failed:
         sys.stderr.write("\n".join(log))
         raise RuntimeError("nvcc failed; see randumb_b200/lib/build.log")
-    link = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB_PATH] + objs
+    # link beside the target and rename: a reader (another process loading the library, a snapshot of the tree) never sees a
+    # half-written file
+    tmp = LIB_PATH + f".{os.getpid()}.tmp"
+    link = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", tmp] + objs
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout)
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("link failed")
+    os.replace(tmp, LIB_PATH)
     if verbose:
         sys.stdout.write("\n".join(log))
     return LIB_PATH

@@ -30,13 +30,24 @@ __global__ void __launch_bounds__(256) gemv_cx_kernel(float *__restrict__ z, con
     if (vec) {
         const float4 *row4 = reinterpret_cast<const float4 *>(row);
         const float4 *x4 = reinterpret_cast<const float4 *>(x);
-        for (int64_t i = threadIdx.x; i < (K >> 2); i += 256) {
-            const float4 c = __ldg(row4 + i);
-            const float4 v = __ldg(x4 + i);
-            acc = fmaf(c.x, v.x, acc);
-            acc = fmaf(c.y, v.y, acc);
-            acc = fmaf(c.z, v.z, acc);
-            acc = fmaf(c.w, v.w, acc);
+        // four 128-bit loads of the row in flight per thread before the first multiply-add needs one: a K = 4096 row is
+        // a single round trip to memory instead of four dependent ones
+        const int64_t K4 = K >> 2;
+        for (int64_t i0 = threadIdx.x; i0 < K4; i0 += 4 * 256) {
+            float4 c[4], v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int64_t i = i0 + u * 256;
+                c[u] = i < K4 ? __ldg(row4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[u] = i < K4 ? __ldg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                acc = fmaf(c[u].x, v[u].x, acc);
+                acc = fmaf(c[u].y, v[u].y, acc);
+                acc = fmaf(c[u].z, v[u].z, acc);
+                acc = fmaf(c[u].w, v[u].w, acc);
+            }
         }
     } else {
         for (int64_t i = threadIdx.x; i < K; i += 256) acc = fmaf(row[i], x[i], acc);

@@ -437,6 +437,7 @@ def sharded_backward_peer(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.T
     K.noise(ex.S.shape[0], R, seed, plan.row_lo, 0, out=ex.S)
     _mark(timer, "noise fill")
     slot = ex.parts_off + ex.rank * ex.t_r * R * 2            # my slot in every owner's g_parts
+    fused_scatter = fused_scatter and os.environ.get("RANDUMB_B200_FUSED_SCATTER", "1") != "0"
     done = fused_scatter and K.gemm_dense_scatter(ex.ptrs, G, slot, ex.t_r, dy_local, ex.S, b_kmajor=False)
     if not done:
         g = K.gemm_dense(dy_local, ex.S, True, False)                                        # partial [T, R]
