@@ -112,6 +112,11 @@ const char *rdb_strerror(int code);
  *                        created once per device by the first such call (make it before any stream capture; a call that
  *                        finds its stream capturing before they exist keeps the fill on the caller's stream).
  *                        0: always on the caller's stream.   2: always beside the z product.
+ *   RDB_OPT_GEMV_FUSED   0 (default): the batch-1 entry points (rdb_gemv_fwd, rdb_gemv_bwd, and rdb_linear_* for one float32 row)
+ *                        launch one kernel per step (two forward, two backward), chained with programmatic dependent launch.
+ *                        1: ONE cooperative launch each, the steps separated by grid-wide barriers (when the device supports
+ *                        cooperative launch).  Same results bit for bit; measured slower (28.6 against 18.2 us per forward +
+ *                        backward of the 4096 x 4096, d_c = 256 layer), kept as a switch.  Process default only.
  * rdb_set_option returns the previous default, or RDB_ERR_UNSUPPORTED for an unknown key or a value outside the
  * range above (nothing changes then); a call whose rdb_call_options holds such a value returns the same error.
  */
@@ -120,6 +125,7 @@ const char *rdb_strerror(int code);
 #define RDB_OPT_STAGE_NOISE 3
 #define RDB_OPT_RESERVE_SMS 4
 #define RDB_OPT_FILL_OVERLAP 5
+#define RDB_OPT_GEMV_FUSED 6
 #define RDB_MAX_RESERVE_SMS 64
 int rdb_set_option(int key, int value);
 

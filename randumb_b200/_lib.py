@@ -21,6 +21,7 @@ OPT_DENSE_PAIR = 2
 OPT_STAGE_NOISE = 3
 OPT_RESERVE_SMS = 4
 OPT_FILL_OVERLAP = 5
+OPT_GEMV_FUSED = 6
 MAX_RESERVE_SMS = 64
 MAX_PEERS = 8
 STATUS_NAMES = {0: "ok", 1: "producer wait expired", 2: "mma wait expired", 3: "epilogue wait expired",

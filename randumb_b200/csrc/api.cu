@@ -21,6 +21,7 @@ static bool opt_in_range(int key, int v) {
         case RDB_OPT_STAGE_NOISE: return v >= 0 && v <= 2;
         case RDB_OPT_RESERVE_SMS: return v >= 0 && v <= RDB_MAX_RESERVE_SMS;
         case RDB_OPT_FILL_OVERLAP: return v >= 0 && v <= 2;
+        case RDB_OPT_GEMV_FUSED: return v == 0 || v == 1;
         default: return false;
     }
 }
@@ -213,6 +214,12 @@ extern "C" int rdb_set_option(int key, int value) {
         case RDB_OPT_STAGE_NOISE: slot = &g_stage_noise; break;
         case RDB_OPT_RESERVE_SMS: slot = &g_reserve_sms; break;
         case RDB_OPT_FILL_OVERLAP: slot = &g_fill_overlap; break;
+        case RDB_OPT_GEMV_FUSED: {
+            if (!opt_in_range(key, value)) return RDB_ERR_UNSUPPORTED;
+            const int prev = get_gemv_fused();
+            set_gemv_fused(value);
+            return prev;
+        }
         default: return RDB_ERR_UNSUPPORTED;
     }
     if (!opt_in_range(key, value)) return RDB_ERR_UNSUPPORTED;   // nothing changes

@@ -77,6 +77,10 @@ struct CallOpts {
     int fill_overlap;  // RDB_OPT_FILL_OVERLAP
 };
 
+// ---- implemented in gemv.cu ---------------------------------------------------------------------
+void set_gemv_fused(int v);
+int get_gemv_fused();
+
 // ---- implemented in umma_gemm.cu -------------------------------------------------------------
 void set_profile_buffer(void *p, size_t bytes);
 bool umma_shape_ok_noise(int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldd, const void *a, const void *d);

@@ -72,6 +72,38 @@ def test_f32_gemv(K, Kin, N, R, seed):
     assert none is None and torch.equal(dx3, dxg)
 
 
+@pytest.mark.parametrize("Kin,N,R,seed", [(4096, 4096, 256, 42), (4098, 513, 33, 9), (640, 4099, 1024, 3)])
+def test_gemv_single_launch_equals_one_kernel_per_step(K, Kin, N, R, seed):
+    """RDB_OPT_GEMV_FUSED: forward and backward as one cooperative launch each (grid-wide barriers between the steps) against
+    one kernel per step chained with programmatic dependent launch -- the same device functions in the same order, so the
+    same bits; and both replay from a CUDA graph."""
+    from randumb_b200 import _lib
+    x, C, dy = _inputs(1, Kin, N, R, torch.float32, seed)
+    xg, Cg, dyg = x.cuda().view(-1), C.cuda(), dy.cuda().view(-1)
+    res = {}
+    for fused in (1, 0):
+        prev = K.set_option(_lib.OPT_GEMV_FUSED, fused)
+        try:
+            y = K.gemv_fwd(xg, Cg, seed, N)
+            dx, dc = K.gemv_bwd(dyg, xg, Cg, seed)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                y_g = K.gemv_fwd(xg, Cg, seed, N)
+                dx_g, dc_g = K.gemv_bwd(dyg, xg, Cg, seed)
+            y_g.zero_(); dx_g.zero_(); dc_g.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(y_g, y) and torch.equal(dx_g, dx) and torch.equal(dc_g, dc)
+            res[fused] = (y, dx, dc)
+        finally:
+            K.set_option(_lib.OPT_GEMV_FUSED, prev)
+    for a, b in zip(res[1], res[0]):
+        assert torch.equal(a, b)
+    y_ref, dx_ref, dc_ref = O.linear_reference(x, C, seed, N, 0, dy)
+    assert O.close(res[1][0].view(1, -1), y_ref, F32_TOL) and O.close(res[1][1].view(1, -1), dx_ref, F32_TOL) and O.close(res[1][2], dc_ref, F32_TOL)
+
+
 # ---- bf16 on tensor cores --------------------------------------------------------------------------
 @pytest.mark.parametrize("T,Kin,N,R,seed,row0", [
     (512, 256, 384, 128, 42, 0),
