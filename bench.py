@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemm|sharded|gemv|gpt2mlp]
                     [--gather-output] [--replicate-grads] [--no-graph] [--no-cpu-baseline] [--no-sharded-record]
-                    [--exchange peer|nccl] [--profile-case noise|staged|roles|products|gemv ...]
+                    [--exchange peer|nccl] [--profile-case noise|staged|roles|products|gemv|hash|overlap ...]
 
 One step = one forward + backward pass of the layer over one batch of seeded synthetic input.
 Default workload ("gemm"): x bf16 [8192 x 4096], virtual W [16384 x 4096], d_c = 1024, seed 42, float32
@@ -1027,11 +1027,62 @@ def profile_case(args):
         --profile-case products  2 launches each of the five plain products of one step (z, y, g, dX, dC)
         --profile-case gemv      3 forward + backward steps of the batch-1 float32 layer, L2 flushed in between (-k regex:gemv)
         --profile-case roles     per-role cycle counters of the generated-operand kernel variants and of the pair kernel
+        --profile-case overlap   the noise fill beside the z product against one after the other
+        --profile-case hash      throughput of alternative formulations of the hash, each checked bit for bit (randumb_b200/lab)
       with --tokens / --out / --dc for the shape (defaults 2048 / 4096 / 8192 tokens, 16384 rows, d_c 1024).
     """
     from randumb_b200 import kernels as K, _lib
     assert torch.cuda.is_available(), "profile cases run on a GPU"
     case, out, dc, seed = args.profile_case, args.out, args.dc, 42
+    if case == "hash":
+        # alternative formulations of the hash (randumb_b200/lab/hash_variants.cu): compile with nvcc, run, print its table
+        from randumb_b200 import build as _build
+        src = os.path.join(ROOT, "randumb_b200", "lab", "hash_variants.cu")
+        exe = os.path.join(ROOT, "randumb_b200", "lib", "hash_variants")
+        os.makedirs(os.path.dirname(exe), exist_ok=True)
+        subprocess.run([_build._nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", exe, src], check=True)
+        subprocess.run([exe], check=True)
+        print("ok")
+        return
+    if case == "overlap":
+        # the noise fill beside the z product (a stream of its own) against the two in a row, at three shapes
+        side = torch.cuda.Stream()
+
+        def med(f, reps=20):
+            for _ in range(3):
+                f()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                f()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps * 1e3
+
+        for (T, Kin, R, nloc, tag) in ((512, 16384, 2048, 8192, "token slice of the row-sharded layer at 8 ranks"),
+                                       (2048, 16384, 2048, 32768, "the same at 2 ranks"), (8192, 4096, 1024, 16384, "headline layer")):
+            x = torch.randn(T, Kin, device="cuda").bfloat16()
+            C = (torch.randn(R, Kin, device="cuda") * 0.01).bfloat16()
+            S = torch.empty(nloc, R, device="cuda", dtype=torch.bfloat16)
+            z = torch.empty(T, R, device="cuda", dtype=torch.bfloat16)
+            prod = lambda: K.gemm_dense(x, C, out=z)
+            fill = lambda: K.noise(nloc, R, 7, 0, 0, out=S)
+
+            def serial():
+                fill(); prod()
+
+            def beside():
+                cur = torch.cuda.current_stream()
+                side.wait_stream(cur)
+                with torch.cuda.stream(side):
+                    fill()
+                prod()
+                cur.wait_stream(side)
+            print(f"{tag}: z = x C^T [{T} x {R}, contraction {Kin}] {med(prod):.1f} us, fill of S [{nloc} x {R}] {med(fill):.1f} us, "
+                  f"one after the other {med(serial):.1f} us, fill on a second stream beside the product {med(beside):.1f} us", flush=True)
+        print("ok")
+        return
     tokens = args.tokens or {"noise": 2048, "staged": 4096, "products": 4096, "roles": 8192, "gemv": 1}[case]
     dev = torch.device("cuda", 0)
     if case == "gemv":
@@ -1135,7 +1186,7 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="row-sharded layer: exchanges by the library's kernels over peer memory (falls back to NCCL when the ranks "
                          "cannot map each other's memory) or by NCCL collectives")
-    ap.add_argument("--profile-case", default=None, choices=["noise", "staged", "roles", "products", "gemv"],
+    ap.add_argument("--profile-case", default=None, choices=["noise", "staged", "roles", "products", "gemv", "hash", "overlap"],
                     help="run a small self-terminating case for a profiler instead of the benchmark")
     ap.add_argument("--tokens", type=int, default=None, help="profile case: token count")
     ap.add_argument("--out", type=int, default=16384, help="profile case: output rows")
