@@ -17,7 +17,7 @@ static std::atomic<int> g_fill_overlap{1};   // RDB_OPT_FILL_OVERLAP
 static bool opt_in_range(int key, int v) {
     switch (key) {
         case RDB_OPT_NOISE_TILE: return v >= 0 && v <= 9;
-        case RDB_OPT_DENSE_PAIR: return v >= 0 && v <= 3;
+        case RDB_OPT_DENSE_PAIR: return v >= 0 && v <= 2;
         case RDB_OPT_STAGE_NOISE: return v >= 0 && v <= 2;
         case RDB_OPT_RESERVE_SMS: return v >= 0 && v <= RDB_MAX_RESERVE_SMS;
         case RDB_OPT_FILL_OVERLAP: return v >= 0 && v <= 2;

@@ -1670,12 +1670,6 @@ template <int A_MN, int B_MN>
 static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
                         int64_t ldd, int d_dtype, int32_t *status, cudaStream_t st, const CallOpts &o) {
     const int rs = o.reserve_sms;
-    if (d_dtype == RDB_BF16 && o.dense_pair == 3 && M > BM && N > BM) {
-        // 256 x 256 tiles: one accumulator per tile, the two TMEM halves alternate, so the epilogue of a tile runs under the
-        // main loop of the next; 32 KB of operands per 64-wide k-block and CTA, six stages
-        return launch_dense_pair<1, 6, A_MN, B_MN, 1>(&d, M, a, b, M, N, Kc, lda, ldb, ldd, cdiv64(M, 2 * BM) * cdiv64(N, 256),
-                                                      max_resident_pairs(), status, st, rs);
-    }
     if (d_dtype == RDB_BF16 && o.dense_pair && M > BM && N > BM) {
         const int P = max_resident_pairs();
         if (o.dense_pair == 2 || prefer_dense_pair(M, N, Kc, P))

@@ -235,7 +235,7 @@ def test_dense_products_random_shapes(K):
         N = 8 * rnd.randint(1, 160)
         Kc = 8 * rnd.randint(1, 300)
         akm, bkm = rnd.random() < 0.5, rnd.random() < 0.5
-        pair = rnd.choice((0, 1, 2, 3))
+        pair = rnd.choice((0, 1, 2))
         A = torch.randn(M, Kc, generator=g).bfloat16()
         B = torch.randn(N, Kc, generator=g).bfloat16()
         a = (A if akm else A.t().contiguous()).cuda()
@@ -279,7 +279,7 @@ def test_dense_products_on_cta_pairs(K, akm, bkm, M, N, Kc):
     a = (A if akm else A.t().contiguous()).cuda()
     b = (B if bkm else B.t().contiguous()).cuda()
     outs = []
-    for pair in (0, 2, 3):                    # never the pair kernel / 512 x 256 pair tiles / 256 x 256 pair tiles
+    for pair in (0, 2):                       # never / always the pair kernel
         prev = K.set_option(2, pair)
         try:
             outs.append(K.gemm_dense(a, b, akm, bkm, impl=K.IMPL_UMMA))
@@ -288,9 +288,8 @@ def test_dense_products_on_cta_pairs(K, akm, bkm, M, N, Kc):
     K.check_status()
     # same bits, unless the single-CTA side ran split-K (few tiles, long contraction: 304 x 1032 x 4096)
     assert torch.equal(outs[0], outs[1]) or O.close(outs[0], outs[1], 1e-2)
-    assert torch.equal(outs[1], outs[2])       # both pair tilings accumulate every output element in the same order
     ref = A.float() @ B.float().t()
-    assert all(O.close(o, ref, 1e-2) for o in outs)
+    assert O.close(outs[0], ref, 1e-2) and O.close(outs[1], ref, 1e-2)
 
 
 # ---- edge cases ----------------------------------------------------------------------------------------
