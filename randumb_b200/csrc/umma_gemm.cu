@@ -1068,11 +1068,14 @@ struct OutMaps {
     CUtensorMap m[NDST];
 };
 
-template <int MT, int D, int A_MN, int B_MN, int NDST>
+// F32 (split-K): the contraction is cut into `split` slices of whole k-blocks; work item = (slice, tile), and slice s writes its
+// float32 partial product into rows [s * M, (s + 1) * M) of the output map, a float32 [split * M, N] matrix (M a multiple of
+// 32, so no 32-row store box crosses into the next slice); split_k_reduce_kernel adds the slices in order afterwards.
+template <int MT, int D, int A_MN, int B_MN, int NDST, bool F32>
 __global__ void __launch_bounds__(DensePairCfg<MT, D>::THREADS, 1)
 dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ OutMaps<NDST> out, int64_t rows_per_dst, int64_t M, int64_t N, int64_t Kc, int m_fast,
-                  int32_t *status, long long *prof) {
+                  int split, int32_t *status, long long *prof) {
     long long pc0 = 0, pc2 = 0;
     using Cfg = DensePairCfg<MT, D>;
     constexpr int BN = Cfg::BN;
@@ -1116,13 +1119,17 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
     const int64_t tiles_m = (M + (int64_t)MT * 2 * BM - 1) / ((int64_t)MT * 2 * BM);
     const int64_t tiles_n = (N + BN - 1) / BN;
-    const int64_t total_tiles = tiles_m * tiles_n;
+    const int64_t tiles_mn = tiles_m * tiles_n;
+    const int64_t total_tiles = tiles_mn * split;          // work items: (slice, tile)
     const int64_t pair_id = blockIdx.x >> 1;
     const int64_t num_pairs = gridDim.x >> 1;
-    const int num_kb = (int)((Kc + BK - 1) / BK);
+    const int all_kb = (int)((Kc + BK - 1) / BK);
+    const int kb_per = (all_kb + split - 1) / split;
+    auto kb_lo = [&](int64_t w) { return (int)(w / tiles_mn) * kb_per; };
+    auto kb_hi = [&](int64_t w) { const int hi = ((int)(w / tiles_mn) + 1) * kb_per; return hi < all_kb ? hi : all_kb; };
     // consecutive tiles share the B panel (m_fast) or the A panel: the larger operand is the one streamed once
-    auto tile_m = [&](int64_t t) { return m_fast ? (t % tiles_m) : (t / tiles_n); };
-    auto tile_n = [&](int64_t t) { return m_fast ? (t / tiles_m) : (t % tiles_n); };
+    auto tile_m = [&](int64_t w) { const int64_t t = w % tiles_mn; return m_fast ? (t % tiles_m) : (t / tiles_n); };
+    auto tile_n = [&](int64_t w) { const int64_t t = w % tiles_mn; return m_fast ? (t / tiles_m) : (t % tiles_n); };
     // accumulator and barrier parity used by sub-tile s of this CTA's it-th tile
     auto acc_of = [&](int64_t it, int s) { return MT == 2 ? s : (int)(it & 1); };
     auto par_of = [&](int64_t it) { return (uint32_t)(MT == 2 ? (it & 1) : ((it >> 1) & 1)); };
@@ -1137,7 +1144,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs) {
                 const int32_t m0 = (int32_t)(tile_m(t) * MT * 2 * BM + half * BM);
                 const int32_t n0 = (int32_t)(tile_n(t) * BN + half * Cfg::HALF);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb_lo(t); kb < kb_hi(t); ++kb) {
                     const long long tw = prof ? clock64() : 0;
                     if (!mbar_wait_cluster(smem_u32(&bar_free[st.idx]), st.phase ^ 1, abortp)) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_PRODUCER);
@@ -1191,7 +1198,8 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             int64_t it = 0;
             const long long t_start = prof ? clock64() : 0;
             for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
-                for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int kb0 = kb_lo(t), kb1 = kb_hi(t);
+                for (int kb = kb0; kb < kb1 && ok; ++kb) {
                     const long long tw = prof ? clock64() : 0;
                     if (!mbar_wait_cluster(smem_u32(&bar_full[st.idx]), st.phase, abortp)) {
                         raise_abort(abortp, status, RDB_STATUS_TIMEOUT_MMA);
@@ -1206,9 +1214,9 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         const uint32_t a_lo = smem_desc_lo(sa + s * SUB_BYTES, A_LBO);
                         const uint64_t adesc = pack_desc(a_lo + ((k * A_KSTEP) >> 4), desc_hi);
                         const uint64_t bdesc = pack_desc(b_lo + ((k * B_KSTEP) >> 4), desc_hi);
-                        umma_bf16_pair(tmem_base + acc_of(it, s) * BN, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_bf16_pair(tmem_base + acc_of(it, s) * BN, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
                     };
-                    const bool first = (kb == 0), last = (kb == num_kb - 1);
+                    const bool first = (kb == kb0), last = (kb == kb1 - 1);
                     if (MT == 2 && (first || last)) {
                         // tile boundaries, one accumulator after the other: the first k-block of accumulator 0 starts as soon
                         // as the epilogue has drained it (accumulator 1 is still being stored), and the last k-block hands
@@ -1283,6 +1291,45 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int64_t t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
             const int64_t m0 = tile_m(t) * MT * 2 * BM + half * BM;
             const int64_t n0 = tile_n(t) * BN;
+            if (F32) {
+                // float32 partial products of a split-K work item: [32 rows x 32 columns] boxes (128-byte rows) through the
+                // staging box, straight from TMEM; the accumulator goes back when all of it has been read
+                const int64_t row_base = (t / tiles_mn) * M;
+#pragma unroll 1
+                for (int s = 0; s < MT && ok; ++s) {
+                    const int a = acc_of(it, s);
+                    if (!mbar_wait_warp<true>(smem_u32(&bar_tmem_full[a]), par_of(it), abortp)) {
+                        raise_abort(abortp, status, RDB_STATUS_TIMEOUT_EPILOGUE);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const int64_t row_w = m0 + s * 2 * BM + q * 32;
+#pragma unroll 1
+                    for (int c0 = cg * 128; c0 < cg * 128 + 128; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c0), r);
+                        if (lane == 0) bulk_wait_group_read0();
+                        __syncwarp();
+                        tmem_ld_wait();
+                        const uint32_t rowaddr = stag + (uint32_t)lane * 128u;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)((j ^ (lane & 7)) << 4)),
+                                         "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && row_w < M && n0 + c0 < N) {
+                            tma_store_2d(&out.m[0], stag, (int32_t)(n0 + c0), (int32_t)(row_base + row_w));
+                            bulk_commit_group();
+                        }
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
+                }
+                continue;
+            }
             uint32_t packed[MT][64];                 // [sub-tile][16-byte chunk * 4 + word]: 128 bf16 columns of this lane's row
 #pragma unroll
             for (int s = 0; s < MT; ++s) {
@@ -1578,10 +1625,10 @@ static int launch_dense(void *d, const void *a, const void *b, int64_t M, int64_
                       split, slice_stride, f32_tma, status);
 }
 
-template <int MT, int D, int A_MN, int B_MN, int NDST>
+template <int MT, int D, int A_MN, int B_MN, int NDST, bool F32 = false>
 static int launch_dense_pair(void *const *dsts, int64_t rows_per_dst, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc,
                              int64_t lda, int64_t ldb, int64_t ldd, int64_t tiles, int max_pairs, int32_t *status, cudaStream_t st,
-                             int reserve_sms) {
+                             int reserve_sms, int split = 1) {
     using Cfg = DensePairCfg<MT, D>;
     CUtensorMap ta, tb;
     OutMaps<NDST> out;
@@ -1594,10 +1641,11 @@ static int launch_dense_pair(void *const *dsts, int64_t rows_per_dst, const void
         // output tiles of 32 rows x 64 columns; unused entries repeat the first destination
         const int jj = j < ndst_used ? j : 0;
         const int64_t rows = NDST > 1 ? (M - jj * rows_per_dst < rows_per_dst ? M - jj * rows_per_dst : rows_per_dst) : M;
-        rc = make_tmap(&out.m[j], dsts[jj], N, rows, ldd, 64, 32);
+        rc = F32 ? make_tmap(&out.m[j], dsts[jj], N, (int64_t)split * M, ldd, 32, 32, true)   // float32 [split * M, N], 32 x 32 boxes
+                 : make_tmap(&out.m[j], dsts[jj], N, rows, ldd, 64, 32);
         if (rc) return rc;
     }
-    auto kern = dense_pair_kernel<MT, D, A_MN, B_MN, NDST>;
+    auto kern = dense_pair_kernel<MT, D, A_MN, B_MN, NDST, F32>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_DYN);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
@@ -1620,7 +1668,7 @@ static int launch_dense_pair(void *const *dsts, int64_t rows_per_dst, const void
     // stream the larger operand once: consecutive tiles share the B panel when A is the smaller matrix
     const int m_fast = (M <= N) ? 1 : 0;
     long long *prof = (g_prof && g_prof_bytes >= (size_t)cfg.gridDim.x * 16 * sizeof(long long)) ? g_prof : nullptr;
-    e = cudaLaunchKernelEx(&cfg, kern, ta, tb, out, rows_per_dst, M, N, Kc, m_fast, status, prof);
+    e = cudaLaunchKernelEx(&cfg, kern, ta, tb, out, rows_per_dst, M, N, Kc, m_fast, split, status, prof);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
@@ -1631,7 +1679,7 @@ static int max_resident_pairs() {
     int dev = 0;
     (void)cudaGetDevice(&dev);
     if (dev == cached_dev && cached > 0) return cached;
-    auto kern = dense_pair_kernel<2, 4, 0, 0, 1>;
+    auto kern = dense_pair_kernel<2, 4, 0, 0, 1, false>;
     int n = 0, fallback = sm_count() / 2;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DensePairCfg<2, 4>::SMEM_DYN) == cudaSuccess) {
         cudaLaunchConfig_t cfg = {};
@@ -1688,18 +1736,45 @@ static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_
 // ---- split-K: few output tiles, long contraction (dC = g^T x of a layer with a small coefficient matrix) ---------------
 // Slices the contraction into `split` pieces that run as independent work items writing float32 partial products
 // [split, M, N] into `partials`; split_k_reduce_kernel then sums the slices in a fixed order.
-int dense_split_k_slices(int64_t M, int64_t N, int64_t Kc) {
-    const int64_t tiles = cdiv64(M, BM) * cdiv64(N, N <= 128 ? 128 : 256);
+// Which kernel a split product runs on, and in how many slices.
+//   CTA pairs: the 512 x 256 tiles would occupy at most half the resident pairs and the contraction is long enough for
+//              slices of 64 k-blocks or more (256 in all at least) that together fill at least 80 % of the pairs (the
+//              token-sliced z = x C^T of the row-sharded layer at 2 and 4 ranks); shorter slices lose to the single-CTA
+//              kernel (ring start-up and an unoverlapped epilogue once per slice: 8 x 32 k-blocks measured 72 against 40 us,
+//              2 x 64 of the headline dC 60.7 against 59.8);
+//   single CTAs: the same idea on 128-row tiles for everything else with few tiles and a long contraction.
+struct SplitPlan {
+    int slices;
+    bool pair;
+};
+
+static SplitPlan split_plan(int64_t M, int64_t N, int64_t Kc) {
     const int64_t kbs = cdiv64(Kc, BK);
+    if (M > BM && N > BM && (M % 32) == 0 && kbs >= 256) {
+        const int P = max_resident_pairs();
+        const int64_t tiles_p = cdiv64(M, 4 * BM) * cdiv64(N, 256);
+        if (tiles_p * 2 <= P) {
+            int64_t sp = P / tiles_p;
+            if (sp > kbs / 64) sp = kbs / 64;
+            if (sp > 8) sp = 8;
+            if (sp >= 2 && tiles_p * sp * 5 >= (int64_t)P * 4) {
+                const int64_t kb_per = cdiv64(kbs, sp);
+                return SplitPlan{(int)cdiv64(kbs, kb_per), true};
+            }
+        }
+    }
+    const int64_t tiles = cdiv64(M, BM) * cdiv64(N, N <= 128 ? 128 : 256);
     const int sms = sm_count();
-    if (tiles * 2 > sms || kbs < 16) return 1;
+    if (tiles * 2 > sms || kbs < 16) return SplitPlan{1, false};
     int64_t s = sms / tiles;                 // one wave of work items
     if (s > kbs / 4) s = kbs / 4;            // at least four k-blocks per slice
     if (s > 16) s = 16;                      // every slice writes and re-reads a float32 copy of the output
-    if (s < 2) return 1;
+    if (s < 2) return SplitPlan{1, false};
     const int64_t kb_per = cdiv64(kbs, s);   // the kernel gives every slice this many k-blocks ...
-    return (int)cdiv64(kbs, kb_per);         // ... so this many slices are non-empty
+    return SplitPlan{(int)cdiv64(kbs, kb_per), false};   // ... so this many slices are non-empty
 }
+
+int dense_split_k_slices(int64_t M, int64_t N, int64_t Kc) { return split_plan(M, N, Kc).slices; }
 
 template <typename OutT>
 __global__ void split_k_reduce_kernel(OutT *__restrict__ out, const float *__restrict__ partials, int64_t n4, int split,
@@ -1733,7 +1808,15 @@ int umma_gemm_dense_split_k(void *d, const void *a, const void *b, float *partia
     const int64_t stride = M * N;
     const int rs = o.reserve_sms;
     int rc;
-    if (N <= 128) {
+    void *pp = partials;
+    if (split_plan(M, N, Kc).pair) {
+        const int P = max_resident_pairs();
+        const int64_t items = cdiv64(M, 4 * BM) * cdiv64(N, 256) * split;
+        if (a_kmajor && b_kmajor) rc = launch_dense_pair<2, 4, 0, 0, 1, true>(&pp, M, a, b, M, N, Kc, lda, ldb, N, items, P, status, st, rs, split);
+        else if (a_kmajor) rc = launch_dense_pair<2, 4, 0, 1, 1, true>(&pp, M, a, b, M, N, Kc, lda, ldb, N, items, P, status, st, rs, split);
+        else if (b_kmajor) rc = launch_dense_pair<2, 4, 1, 0, 1, true>(&pp, M, a, b, M, N, Kc, lda, ldb, N, items, P, status, st, rs, split);
+        else rc = launch_dense_pair<2, 4, 1, 1, 1, true>(&pp, M, a, b, M, N, Kc, lda, ldb, N, items, P, status, st, rs, split);
+    } else if (N <= 128) {
         if (a_kmajor && b_kmajor) rc = launch_dense<128, 6, 0, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
         else if (a_kmajor) rc = launch_dense<128, 6, 0, 1, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);
         else if (b_kmajor) rc = launch_dense<128, 6, 1, 0, float>(partials, a, b, M, N, Kc, lda, ldb, N, status, st, rs, split, stride);

@@ -249,10 +249,12 @@ def test_dense_products_random_shapes(K):
         assert O.close(d, A.float() @ B.float().t(), 1e-2), (case, M, N, Kc, akm, bkm, pair)
 
 
-@pytest.mark.parametrize("M,N,Kc", [(512, 2048, 16384), (128, 768, 8192), (72, 264, 1504), (256, 128, 3072)])
+@pytest.mark.parametrize("M,N,Kc", [(512, 2048, 16384), (128, 768, 8192), (72, 264, 1504), (256, 128, 3072),
+                                    (1024, 2048, 16384), (2048, 2048, 16384), (1056, 520, 16392)])
 def test_dense_products_split_k(K, M, N, Kc):
     """Few output tiles and a long contraction: slices of the contraction as independent work items, float32 partial
-    products, ordered sum -- within bf16 rounding of the unsplit kernel, identical from run to run."""
+    products, ordered sum -- within bf16 rounding of the unsplit kernel, identical from run to run.  The last three shapes run
+    on CTA pairs (512 x 256 tiles, ragged in the last one), the others on single CTAs."""
     from randumb_b200 import _lib
     assert _lib.lib().rdb_gemm_dense_workspace_bytes(M, N, Kc) > 0
     g = torch.Generator().manual_seed(8)
