@@ -32,6 +32,12 @@ def test_default_workload_line():
     e = d["e2e"]
     assert e["h2d_bytes_per_step"] == 8192 * 4096 * 2 and e["d2h_bytes_per_step"] == 4 and 0 < e["value"] < d["value"]
     assert "workload" in d["config"] and "l2" in d["config"]
+    assert e["h2d_gbs"] > 1.0 and e["h2d_copy_ms"] > 0
+    # the second scaling curve travels in the same line: the row-sharded 65536 x 16384 layer on the same GPUs
+    sh = d["sharded"]
+    assert sh["n_gpus"] == 1 and sh["scaling"] == "strong" and sh["unit"] == "TFLOP/s" and "65536x16384" in sh["workload"]
+    assert sh["speedup_vs_single_gpu"] == 1.0 and sh["exchange"] == "single GPU" and sh["phases_ms"]
+    assert abs(sh["value"] - 3.0236e12 / (sh["ms_per_step"] * 1e-3) / 1e12) < 1e-2 * sh["value"]
 
 
 def test_gemv_workload_line():

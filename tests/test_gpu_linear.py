@@ -380,6 +380,23 @@ def test_noise_fill_beside_the_z_product_gives_the_same_bits(K):
     K.check_status()
 
 
+def test_per_call_options_change_the_launch_not_the_result(K):
+    """rdb_call_options: leaving SMs to a collective, or forcing one kernel family, for one call -- same bits as the default
+    launch, and the process defaults are untouched afterwards."""
+    from randumb_b200 import _lib
+    g = torch.Generator().manual_seed(12)
+    A = torch.randn(2048, 1024, generator=g).bfloat16().cuda()
+    B = torch.randn(1024, 1024, generator=g).bfloat16().cuda()
+    base = K.gemm_dense(A, B)
+    for opts in (_lib.CallOptions(reserve_sms=32), _lib.CallOptions(reserve_sms=64, dense_pair=2), _lib.CallOptions(dense_pair=0)):
+        assert torch.equal(K.gemm_dense(A, B, options=opts), base)
+    with pytest.raises(RuntimeError, match="options"):
+        K.gemm_dense(A, B, options=_lib.CallOptions(reserve_sms=65))
+    L = _lib.lib()
+    assert L.rdb_set_option(_lib.OPT_RESERVE_SMS, 0) == 0 and L.rdb_set_option(_lib.OPT_DENSE_PAIR, 1) == 1
+    K.check_status()
+
+
 # ---- full benchmark sizes ------------------------------------------------------------------------------------------
 def test_full_size_properties(K):
     """8192 x 4096 -> 16384, d_c = 1024 (the headline configuration): size-independent properties."""
