@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemm|sharded|gemv|gpt2mlp]
                     [--gather-output] [--replicate-grads] [--no-graph] [--no-cpu-baseline] [--no-sharded-record]
-                    [--exchange peer|nccl] [--profile-case noise|staged|roles|products|gemv|hash|overlap ...]
+                    [--exchange peer|nccl] [--profile-case noise|staged|roles|products|gemv|hash|overlap|formr ...]
 
 One step = one forward + backward pass of the layer over one batch of seeded synthetic input.
 Default workload ("gemm"): x bf16 [8192 x 4096], virtual W [16384 x 4096], d_c = 1024, seed 42, float32
@@ -222,9 +222,11 @@ def run_reference(args, cfg):
         "impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": dict(workload_config(args.workload, cfg, args.gpus, args.replicate_grads, args.gather_output),
-                       parallelism=f"ONE host process on {cores} threads at any --gpus value (the reference's CPU path does not shard); "
-                                   "a ratio against an N-GPU line compares N GPUs with this one host"),
+        # same `config` as the GPU arm's line for this --gpus value (the two lines are compared key by key); what differs is said
+        # in `reference_arm`: this arm never shards
+        "config": workload_config(args.workload, cfg, args.gpus, args.replicate_grads, args.gather_output),
+        "reference_arm": f"ONE host process on {cores} threads at any --gpus value (the reference's CPU path does not shard): a ratio "
+                         "against an N-GPU line compares N GPUs with this one host",
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "cpu": cpu_model(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -1058,6 +1060,7 @@ def profile_case(args):
         --profile-case gemv      3 forward + backward steps of the batch-1 float32 layer, L2 flushed in between (-k regex:gemv)
         --profile-case roles     per-role cycle counters of the generated-operand kernel variants and of the pair kernel
         --profile-case overlap   the noise fill beside the z product against one after the other
+        --profile-case formr     materialise forward / backward and embedding rows of the 1-D-coefficient form, in hashes per second
         --profile-case hash      throughput of alternative formulations of the hash, each checked bit for bit (randumb_b200/lab)
       with --tokens / --out / --dc for the shape (defaults 2048 / 4096 / 8192 tokens, 16384 rows, d_c 1024).
     """
@@ -1072,6 +1075,38 @@ def profile_case(args):
         os.makedirs(os.path.dirname(exe), exist_ok=True)
         subprocess.run([_build._nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", exe, src], check=True)
         subprocess.run([exe], check=True)
+        print("ok")
+        return
+    if case == "formr":
+        # the reference's own parameterisation (1-D coefficient vector): materialise forward / backward of a GPT-2-small MLP
+        # weight and of an embedding lookup, against the rate of the bare hash loop (`--profile-case hash`)
+        dev = torch.device("cuda", 0)
+
+        def med(f, reps=10):
+            for _ in range(2):
+                f()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                f()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps
+
+        for (P, Q, M) in ((3072, 768, 256), (3072, 768, 128), (50304, 768, 256)):
+            coef = torch.randn(M, device=dev)
+            dout = torch.randn(P * Q, device=dev)
+            t_f = med(lambda: K.materialize_fwd(coef, [P, Q], [Q, 1], 13), reps=5 if P > 10000 else 10)
+            t_b = med(lambda: K.materialize_bwd(dout, M, 13), reps=5 if P > 10000 else 10)
+            h = P * Q * M
+            print(f"weight [{P} x {Q}], int_dim {M}: {h / 1e9:.2f} G hashes per pass; materialize_fwd {t_f:.3f} ms = {h / t_f / 1e9:.0f} G hashes/s, "
+                  f"materialize_bwd {t_b:.3f} ms = {h / t_b / 1e9:.0f} G hashes/s", flush=True)
+        idx = torch.randint(0, 50304, (8 * 1024,), device=dev)
+        coef = torch.randn(256, device=dev)
+        t_e = med(lambda: K.embed_fwd(idx, coef, 768, 9))
+        h = idx.numel() * 768 * 256
+        print(f"embedding rows: 8192 tokens x 768, int_dim 256: {h / 1e9:.2f} G hashes; embed_fwd {t_e:.3f} ms = {h / t_e / 1e9:.0f} G hashes/s")
         print("ok")
         return
     if case == "overlap":
@@ -1216,7 +1251,7 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="row-sharded layer: exchanges by the library's kernels over peer memory (falls back to NCCL when the ranks "
                          "cannot map each other's memory) or by NCCL collectives")
-    ap.add_argument("--profile-case", default=None, choices=["noise", "staged", "roles", "products", "gemv", "hash", "overlap"],
+    ap.add_argument("--profile-case", default=None, choices=["noise", "staged", "roles", "products", "gemv", "hash", "overlap", "formr"],
                     help="run a small self-terminating case for a profiler instead of the benchmark")
     ap.add_argument("--tokens", type=int, default=None, help="profile case: token count")
     ap.add_argument("--out", type=int, default=16384, help="profile case: output rows")
