@@ -106,6 +106,13 @@ def _rows_worker(rank, world, port):
     try:
         sizes = [3, 2]
         x = torch.full((sizes[rank], 4), float(rank + 1), requires_grad=True)
+        # the plan of the peer-memory layer: contiguous row and token ranges that cover everything once
+        plan = parallel.ShardedLayerPlan(96, 44, world, rank)
+        assert plan.row_ranges == parallel.all_shard_ranges(44, world) and plan.tok_sizes == [48, 48]
+        assert (plan.row_lo, plan.row_hi) == plan.row_ranges[rank] and (plan.tok_lo, plan.tok_hi) == (48 * rank, 48 * rank + 48)
+        # the peer-memory exchange exists only between GPUs on NCCL ranks: on a gloo group it declines (the caller
+        # then uses the collective path) without touching CUDA
+        assert parallel.PeerExchange.create(plan, 16, torch.device("cpu")) is None
         z = parallel.all_gather_rows(x, sizes)
         assert z.shape == (5, 4) and float(z[0, 0]) == 1.0 and float(z[4, 0]) == 2.0
         (z * (rank + 1)).sum().backward()          # d/dz = rank+1 on every rank -> summed = 3
