@@ -117,6 +117,13 @@ const char *rdb_strerror(int code);
  *                        1: ONE cooperative launch each, the steps separated by grid-wide barriers (when the device supports
  *                        cooperative launch).  Same results bit for bit; measured slower (28.6 against 18.2 us per forward +
  *                        backward of the 4096 x 4096, d_c = 256 layer), kept as a switch.  Process default only.
+ *   RDB_OPT_GRADS_BESIDE 1 (default): automatic -- rdb_linear_bwd (bf16, factored, both gradients asked for) runs dX = g C and
+ *                        dC = g^T x at the same time, dX on the library's own stream (the one RDB_OPT_FILL_OVERLAP describes,
+ *                        same fork and join by events, same rule about stream capture) on some of the CTA pairs and dC on the
+ *                        caller's stream on the others, when both can run on CTA pairs and their tile lists pack at least 7 %
+ *                        better side by side than one after the other (the headline layer: 256 tiles of 16 k-blocks and 32
+ *                        tiles of 128 k-blocks for 74 pairs).  Same results bit for bit as RDB_OPT_DENSE_PAIR = 2 gives.
+ *                        0: one after the other on the caller's stream.   2: side by side whenever both can run on CTA pairs.
  * rdb_set_option returns the previous default, or RDB_ERR_UNSUPPORTED for an unknown key or a value outside the
  * range above (nothing changes then); a call whose rdb_call_options holds such a value returns the same error.
  */
@@ -126,6 +133,7 @@ const char *rdb_strerror(int code);
 #define RDB_OPT_RESERVE_SMS 4
 #define RDB_OPT_FILL_OVERLAP 5
 #define RDB_OPT_GEMV_FUSED 6
+#define RDB_OPT_GRADS_BESIDE 7
 #define RDB_MAX_RESERVE_SMS 64
 int rdb_set_option(int key, int value);
 
@@ -135,6 +143,7 @@ typedef struct rdb_call_options {
     int32_t stage_noise;  /* RDB_OPT_STAGE_NOISE  ... */
     int32_t reserve_sms;  /* RDB_OPT_RESERVE_SMS  ... */
     int32_t fill_overlap; /* RDB_OPT_FILL_OVERLAP ... */
+    int32_t grads_beside; /* RDB_OPT_GRADS_BESIDE ... */
 } rdb_call_options;
 
 /*

@@ -22,6 +22,7 @@ OPT_STAGE_NOISE = 3
 OPT_RESERVE_SMS = 4
 OPT_FILL_OVERLAP = 5
 OPT_GEMV_FUSED = 6
+OPT_GRADS_BESIDE = 7
 MAX_RESERVE_SMS = 64
 MAX_PEERS = 8
 STATUS_NAMES = {0: "ok", 1: "producer wait expired", 2: "mma wait expired", 3: "epilogue wait expired",
@@ -33,11 +34,11 @@ _i64, _u32, _i32, _vp, _sz = ctypes.c_int64, ctypes.c_uint32, ctypes.c_int, ctyp
 class CallOptions(ctypes.Structure):
     """``rdb_call_options``: per-call values of the tuning switches; a field < 0 keeps the process default."""
     _fields_ = [("noise_tile", ctypes.c_int32), ("dense_pair", ctypes.c_int32), ("stage_noise", ctypes.c_int32),
-                ("reserve_sms", ctypes.c_int32), ("fill_overlap", ctypes.c_int32)]
+                ("reserve_sms", ctypes.c_int32), ("fill_overlap", ctypes.c_int32), ("grads_beside", ctypes.c_int32)]
 
     def __init__(self, noise_tile: int = -1, dense_pair: int = -1, stage_noise: int = -1, reserve_sms: int = -1,
-                 fill_overlap: int = -1):
-        super().__init__(noise_tile, dense_pair, stage_noise, reserve_sms, fill_overlap)
+                 fill_overlap: int = -1, grads_beside: int = -1):
+        super().__init__(noise_tile, dense_pair, stage_noise, reserve_sms, fill_overlap, grads_beside)
 
 
 _op = ctypes.POINTER(CallOptions)

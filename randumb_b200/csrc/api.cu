@@ -13,6 +13,7 @@ static std::atomic<int> g_dense_pair{1};     // RDB_OPT_DENSE_PAIR
 static std::atomic<int> g_stage_noise{0};    // RDB_OPT_STAGE_NOISE
 static std::atomic<int> g_reserve_sms{0};    // RDB_OPT_RESERVE_SMS
 static std::atomic<int> g_fill_overlap{1};   // RDB_OPT_FILL_OVERLAP
+static std::atomic<int> g_grads_beside{1};   // RDB_OPT_GRADS_BESIDE
 
 static bool opt_in_range(int key, int v) {
     switch (key) {
@@ -21,6 +22,7 @@ static bool opt_in_range(int key, int v) {
         case RDB_OPT_STAGE_NOISE: return v >= 0 && v <= 2;
         case RDB_OPT_RESERVE_SMS: return v >= 0 && v <= RDB_MAX_RESERVE_SMS;
         case RDB_OPT_FILL_OVERLAP: return v >= 0 && v <= 2;
+        case RDB_OPT_GRADS_BESIDE: return v >= 0 && v <= 2;
         case RDB_OPT_GEMV_FUSED: return v == 0 || v == 1;
         default: return false;
     }
@@ -28,12 +30,14 @@ static bool opt_in_range(int key, int v) {
 
 // Options of one call: the caller's values where given (>= 0), the process defaults elsewhere.
 static int resolve_opts(const rdb_call_options *o, CallOpts *out) {
-    CallOpts c{g_noise_tile.load(), g_dense_pair.load(), g_stage_noise.load(), g_reserve_sms.load(), g_fill_overlap.load()};
+    CallOpts c{g_noise_tile.load(), g_dense_pair.load(), g_stage_noise.load(), g_reserve_sms.load(), g_fill_overlap.load(),
+               g_grads_beside.load()};
     if (o) {
-        const int keys[5] = {RDB_OPT_NOISE_TILE, RDB_OPT_DENSE_PAIR, RDB_OPT_STAGE_NOISE, RDB_OPT_RESERVE_SMS, RDB_OPT_FILL_OVERLAP};
-        const int vals[5] = {o->noise_tile, o->dense_pair, o->stage_noise, o->reserve_sms, o->fill_overlap};
-        int *dst[5] = {&c.noise_tile, &c.dense_pair, &c.stage_noise, &c.reserve_sms, &c.fill_overlap};
-        for (int i = 0; i < 5; ++i) {
+        const int keys[6] = {RDB_OPT_NOISE_TILE,  RDB_OPT_DENSE_PAIR,   RDB_OPT_STAGE_NOISE,
+                             RDB_OPT_RESERVE_SMS, RDB_OPT_FILL_OVERLAP, RDB_OPT_GRADS_BESIDE};
+        const int vals[6] = {o->noise_tile, o->dense_pair, o->stage_noise, o->reserve_sms, o->fill_overlap, o->grads_beside};
+        int *dst[6] = {&c.noise_tile, &c.dense_pair, &c.stage_noise, &c.reserve_sms, &c.fill_overlap, &c.grads_beside};
+        for (int i = 0; i < 6; ++i) {
             if (vals[i] < 0) continue;
             if (!opt_in_range(keys[i], vals[i])) return RDB_ERR_UNSUPPORTED;
             *dst[i] = vals[i];
@@ -142,7 +146,8 @@ static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, in
 }
 
 // One extra stream and two events per device, created on first use: the forward's noise fill (integer ALU) runs on it
-// beside the z product (tensor pipe) and joins the caller's stream before the y product.  Nothing is created per call.
+// beside the z product (tensor pipe) and joins the caller's stream before the y product; the backward's dX runs on it
+// beside dC.  Nothing is created per call.
 struct SideStream {
     cudaStream_t stream = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr;
@@ -214,6 +219,7 @@ extern "C" int rdb_set_option(int key, int value) {
         case RDB_OPT_STAGE_NOISE: slot = &g_stage_noise; break;
         case RDB_OPT_RESERVE_SMS: slot = &g_reserve_sms; break;
         case RDB_OPT_FILL_OVERLAP: slot = &g_fill_overlap; break;
+        case RDB_OPT_GRADS_BESIDE: slot = &g_grads_beside; break;
         case RDB_OPT_GEMV_FUSED: {
             if (!opt_in_range(key, value)) return RDB_ERR_UNSUPPORTED;
             const int prev = get_gemv_fused();
@@ -540,6 +546,25 @@ extern "C" int rdb_linear_bwd_ex(void *dx, void *dc, const void *dy, const void 
                 rc = umma_gemm_noise(g, dy, T, R, N, N, R, cols, status, st, o);
             }
             if (rc) return rc;
+            // dX and dC both read g and nothing of one another: when their tile lists pack better side by side than one after
+            // the other, dX goes to the library's own stream on some of the CTA pairs and dC stays here on the rest
+            int pairs_dx = 0, pairs_dc = 0;
+            if (dx && dc && o.grads_beside && o.dense_pair && dense_split_k_slices(R, K, T) == 1 &&
+                dense_beside_plan(T, K, R, R, K, T, o.reserve_sms, o.grads_beside == 2, &pairs_dx, &pairs_dc)) {
+                if (SideStream *side = side_stream(st)) {
+                    std::lock_guard<std::mutex> side_lock(side->mu);
+                    cudaError_t e = cudaEventRecord(side->fork, st);
+                    if (e == cudaSuccess) e = cudaStreamWaitEvent(side->stream, side->fork, 0);
+                    if (e != cudaSuccess) return (int)e;
+                    rc = umma_gemm_dense_on_pairs(dx, g, coef, T, K, R, R, K, K, 1, 0, pairs_dx, status, side->stream);
+                    // the join is recorded and waited for even after a failed launch, so a captured fork always rejoins
+                    e = cudaEventRecord(side->join, side->stream);
+                    const int rc2 = rc ? rc : umma_gemm_dense_on_pairs(dc, g, x, R, K, T, R, K, K, 0, 0, pairs_dc, status, st);
+                    const cudaError_t ej = (e == cudaSuccess) ? cudaStreamWaitEvent(st, side->join, 0) : e;
+                    if (rc2) return rc2;
+                    return ej == cudaSuccess ? RDB_OK : (int)ej;
+                }
+            }
             if (dx) {
                 rc = umma_gemm_dense(dx, g, coef, T, K, R, R, K, K, RDB_BF16, 1, 0, status, st, o);
                 if (rc) return rc;

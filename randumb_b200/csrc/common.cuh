@@ -75,6 +75,7 @@ struct CallOpts {
     int stage_noise;   // RDB_OPT_STAGE_NOISE
     int reserve_sms;   // RDB_OPT_RESERVE_SMS
     int fill_overlap;  // RDB_OPT_FILL_OVERLAP
+    int grads_beside;  // RDB_OPT_GRADS_BESIDE
 };
 
 // ---- implemented in gemv.cu ---------------------------------------------------------------------
@@ -95,6 +96,11 @@ int umma_gemm_dense_split_k(void *d, const void *a, const void *b, float *partia
 int umma_gemm_dense(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda,
                     int64_t ldb, int64_t ldd, int d_dtype, int a_kmajor, int b_kmajor, int32_t *status,
                     cudaStream_t stream, const CallOpts &o);
+
+bool dense_beside_plan(int64_t M1, int64_t N1, int64_t Kc1, int64_t M2, int64_t N2, int64_t Kc2, int reserve_sms, bool always,
+                       int *pairs1, int *pairs2);
+int umma_gemm_dense_on_pairs(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
+                             int64_t ldd, int a_kmajor, int b_kmajor, int pairs, int32_t *status, cudaStream_t stream);
 
 int umma_gemm_dense_scatter(void *const *dsts, int ndst, int64_t rows_per_dst, const void *a, const void *b, int64_t M, int64_t N,
                             int64_t Kc, int64_t lda, int64_t ldb, int b_kmajor, int32_t *status, cudaStream_t stream,

@@ -1733,6 +1733,57 @@ static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_
     return RDB_ERR_DTYPE;
 }
 
+// ---- two independent products at the same time on disjoint sets of CTA pairs ------------------------------------------
+// dX = g C (tokens x inputs, short contraction) and dC = g^T x (coefficients x inputs, long contraction) both read g and
+// nothing of one another.  Alone, each leaves SMs idle when its tiles do not divide by the resident pairs (the headline
+// layer: 256 tiles of 16 k-blocks and 32 tiles of 128 k-blocks for 74 pairs), and the single-CTA kernel that fills the SMs
+// better pays a third more shared-memory traffic per MMA.  Side by side on p and P - p pairs the two tile lists pack
+// (32 pairs x 128 k-blocks next to 42 pairs x 7 tiles x 16 k-blocks).  Costs are in SM cycles at the nominal MMA rate:
+// a k-block of a 512 x 256 pair tile is 1024 cycles, of a 128 x 256 single-CTA tile 512 cycles times the measured 1.27.
+static double pair_cost(int64_t M, int64_t N, int64_t Kc, int pairs) {
+    const int64_t tiles = cdiv64(M, 4 * BM) * cdiv64(N, 256);
+    return (double)cdiv64(tiles, pairs) * ((double)cdiv64(Kc, BK) * 1024.0 + 2500.0);   // + ring start and epilogue per tile
+}
+
+static double alone_cost(int64_t M, int64_t N, int64_t Kc, int P) {
+    const int64_t tiles = cdiv64(M, BM) * cdiv64(N, 256);
+    const double single = (double)cdiv64(tiles, sm_count()) * (double)cdiv64(Kc, BK) * 512.0 * 1.27;
+    const double pair = pair_cost(M, N, Kc, P);
+    return single < pair ? single : pair;
+}
+
+// Pairs for the first and the second product when running them side by side is expected to take less than 93 % of
+// running them one after the other (`always`: whenever both can run on pairs); false otherwise.  `reserve_sms` SMs stay
+// free as in every plain-product launch.
+bool dense_beside_plan(int64_t M1, int64_t N1, int64_t Kc1, int64_t M2, int64_t N2, int64_t Kc2, int reserve_sms, bool always,
+                       int *pairs1, int *pairs2) {
+    if (M1 <= BM || N1 <= BM || M2 <= BM || N2 <= BM || Kc1 < BK || Kc2 < BK) return false;
+    const int P = max_resident_pairs() - (reserve_sms + 1) / 2;
+    if (P < 2) return false;
+    double best = 0.0;
+    int best_p = 0;
+    for (int p = 1; p < P; ++p) {
+        const double c1 = pair_cost(M1, N1, Kc1, p), c2 = pair_cost(M2, N2, Kc2, P - p);
+        const double c = c1 > c2 ? c1 : c2;
+        if (best_p == 0 || c < best) { best = c; best_p = p; }
+    }
+    if (!always && best > 0.93 * (alone_cost(M1, N1, Kc1, P) + alone_cost(M2, N2, Kc2, P))) return false;
+    *pairs1 = best_p;
+    *pairs2 = P - best_p;
+    return true;
+}
+
+// D = op(A) op(B)^T (bf16) on at most `pairs` CTA pairs, whatever the tile count
+int umma_gemm_dense_on_pairs(void *d, const void *a, const void *b, int64_t M, int64_t N, int64_t Kc, int64_t lda, int64_t ldb,
+                             int64_t ldd, int a_kmajor, int b_kmajor, int pairs, int32_t *status, cudaStream_t st) {
+    if (M == 0 || N == 0) return RDB_OK;
+    const int64_t tiles = cdiv64(M, 4 * BM) * cdiv64(N, 256);
+    if (a_kmajor && b_kmajor) return launch_dense_pair<2, 4, 0, 0, 1>(&d, M, a, b, M, N, Kc, lda, ldb, ldd, tiles, pairs, status, st, 0);
+    if (a_kmajor) return launch_dense_pair<2, 4, 0, 1, 1>(&d, M, a, b, M, N, Kc, lda, ldb, ldd, tiles, pairs, status, st, 0);
+    if (b_kmajor) return launch_dense_pair<2, 4, 1, 0, 1>(&d, M, a, b, M, N, Kc, lda, ldb, ldd, tiles, pairs, status, st, 0);
+    return launch_dense_pair<2, 4, 1, 1, 1>(&d, M, a, b, M, N, Kc, lda, ldb, ldd, tiles, pairs, status, st, 0);
+}
+
 // ---- split-K: few output tiles, long contraction (dC = g^T x of a layer with a small coefficient matrix) ---------------
 // Slices the contraction into `split` pieces that run as independent work items writing float32 partial products
 // [split, M, N] into `partials`; split_k_reduce_kernel then sums the slices in a fixed order.

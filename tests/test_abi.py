@@ -60,6 +60,7 @@ def test_options_are_validated_and_per_call(built_lib):
     assert L.rdb_set_option(_lib.OPT_RESERVE_SMS, _lib.MAX_RESERVE_SMS + 1) == -6
     assert L.rdb_set_option(_lib.OPT_RESERVE_SMS, 0) == 16
     assert L.rdb_set_option(_lib.OPT_FILL_OVERLAP, 3) == -6 and L.rdb_set_option(_lib.OPT_FILL_OVERLAP, 1) == 1
+    assert L.rdb_set_option(_lib.OPT_GRADS_BESIDE, 3) == -6 and L.rdb_set_option(_lib.OPT_GRADS_BESIDE, 1) == 1
     # per-call options override the default for that call only, and are validated the same way
     stage_off = _lib.CallOptions(stage_noise=1)
     zg, S = 8192 * 1024 * 2, 16384 * 1024 * 2

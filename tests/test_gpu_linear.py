@@ -380,16 +380,49 @@ def test_noise_fill_beside_the_z_product_gives_the_same_bits(K):
     K.check_status()
 
 
+def test_input_and_coefficient_gradients_side_by_side_give_the_same_bits(K):
+    """RDB_OPT_GRADS_BESIDE: dX on the library's own stream on some of the CTA pairs while dC runs on the caller's stream on the
+    others -- the same bits as the two CTA-pair products one after the other, eagerly and replayed from a CUDA graph, with a
+    ragged shape (forced) and with a shape the automatic rule itself sends that way."""
+    from randumb_b200 import _lib
+    for (T, Kin, N, R, beside) in ((1544, 776, 520, 264, _lib.CallOptions(grads_beside=2, dense_pair=2)),
+                                   (4096, 4096, 1024, 1024, None)):
+        g = torch.Generator().manual_seed(T)
+        dy = (torch.randn(T, N, generator=g) * 0.1).bfloat16().cuda()
+        x = torch.randn(T, Kin, generator=g).bfloat16().cuda()
+        C = (torch.randn(R, Kin, generator=g) * 0.05).bfloat16().cuda()
+        dx0, dc0 = K.linear_bwd(dy, x, C, 5, 16, options=_lib.CallOptions(grads_beside=0, dense_pair=2))
+        dx1, dc1 = K.linear_bwd(dy, x, C, 5, 16, options=beside)      # also creates the stream and events, outside any capture
+        torch.cuda.synchronize()
+        assert torch.equal(dx1, dx0) and torch.equal(dc1, dc0)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            dx_g, dc_g = K.linear_bwd(dy, x, C, 5, 16, options=beside)
+        for _ in range(2):
+            dx_g.zero_()
+            dc_g.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(dx_g, dx0) and torch.equal(dc_g, dc0)
+        if T < 2048:
+            _, dx_ref, dc_ref = O.linear_reference(x.cpu(), C.cpu(), 5, N, 16, dy.cpu(), dtype=torch.float32)
+            assert O.close(dx1, dx_ref, BF16_TOL) and O.close(dc1, dc_ref, BF16_TOL)
+    K.check_status()
+
+
 def test_per_call_options_change_the_launch_not_the_result(K):
     """rdb_call_options: leaving SMs to a collective, or forcing one kernel family, for one call -- same bits as the default
     launch, and the process defaults are untouched afterwards."""
     from randumb_b200 import _lib
     g = torch.Generator().manual_seed(12)
-    A = torch.randn(2048, 1024, generator=g).bfloat16().cuda()
-    B = torch.randn(1024, 1024, generator=g).bfloat16().cuda()
-    base = K.gemm_dense(A, B)
-    for opts in (_lib.CallOptions(reserve_sms=32), _lib.CallOptions(reserve_sms=64, dense_pair=2), _lib.CallOptions(dense_pair=0)):
-        assert torch.equal(K.gemm_dense(A, B, options=opts), base)
+    A = torch.randn(4096, 1024, generator=g).bfloat16().cuda()
+    B = torch.randn(2048, 1024, generator=g).bfloat16().cuda()        # 256 single-CTA tiles / 64 pair tiles: no split-K
+    ref = A.float() @ B.float().t()
+    for family in (0, 2):
+        base = K.gemm_dense(A, B, options=_lib.CallOptions(dense_pair=family))
+        assert O.close(base, ref, BF16_TOL)
+        for rs in (20, 32, 64):      # fewer CTAs walk the same tiles
+            assert torch.equal(K.gemm_dense(A, B, options=_lib.CallOptions(reserve_sms=rs, dense_pair=family)), base)
     with pytest.raises(RuntimeError, match="options"):
         K.gemm_dense(A, B, options=_lib.CallOptions(reserve_sms=65))
     L = _lib.lib()
