@@ -104,11 +104,11 @@ const char *rdb_strerror(int code);
  *                        CTA.  Their CTAs take a whole SM each for the length of the launch, so a collective enqueued
  *                        beside them (an NCCL all-reduce of the previous product's result) only runs at the same time
  *                        if some SMs are left free.  Meant to be given per call, for the launch that should overlap.
- *   RDB_OPT_FILL_OVERLAP 1 (default): automatic -- when S has 64 Mi elements or more, rdb_linear_fwd hashes the staged S on
- *                        a stream of the library's own, forked from and joined back into the caller's stream with events,
- *                        so the integer-ALU fill runs beside the tensor-core product z = x C^T it does not depend on (a
- *                        shorter fill stays on the caller's stream: beside a short product its resident threads cost the
- *                        product's MMA-issuing thread as much as the fill takes).  The stream and its two events are
+ *   RDB_OPT_FILL_OVERLAP 1 (default): automatic -- when S has 64 Mi elements or more, or 1 Mi or fewer, rdb_linear_fwd hashes
+ *                        the staged S on a stream of the library's own, forked from and joined back into the caller's stream
+ *                        with events, so the integer-ALU fill runs beside the tensor-core product z = x C^T it does not depend
+ *                        on (a fill in between stays on the caller's stream: it is more than launch latency, and beside a
+ *                        short product its resident threads cost the product's MMA-issuing thread as much as it takes).  The stream and its two events are
  *                        created once per device by the first such call (make it before any stream capture; a call that
  *                        finds its stream capturing before they exist keeps the fill on the caller's stream).
  *                        0: always on the caller's stream.   2: always beside the z product.

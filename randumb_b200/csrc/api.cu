@@ -437,11 +437,13 @@ extern "C" int rdb_linear_fwd_ex(void *y, const void *x, const void *coef, void 
             void *z = ws + w.off[0];
             const bool staged = stage_noise(T, N, R, o);
             void *S = ws + w.off[1];
-            // the hash of S (integer ALU) does not depend on z = x C^T (tensor pipe), so a long fill runs beside that product.
-            // A short one does not: the fill's two thousand resident threads per SM slow the product's single MMA-issuing
-            // thread down by about as much as the fill takes (measured: 16.8 M elements beside a 40-50 us product lose,
-            // 67 M and more beside a 100-180 us product win 20 us)
-            const bool beside = o.fill_overlap == 2 || (o.fill_overlap == 1 && (double)N * (double)R >= 64.0 * 1024 * 1024);
+            // the hash of S (integer ALU) does not depend on z = x C^T (tensor pipe), so a long fill runs beside that product,
+            // and so does one so short that it is all launch latency (at most 1 Mi elements: the 24 layers of the
+            // GPT-2-shaped workload 0.620 -> 0.600 ms forward).  In between it does not: the fill's two thousand resident
+            // threads per SM slow the product's single MMA-issuing thread down by about as much as the fill takes (measured:
+            // 16.8 M elements beside a 40-50 us product lose, 67 M and more beside a 100-180 us product win 20 us)
+            const double s_elems = (double)N * (double)R;
+            const bool beside = o.fill_overlap == 2 || (o.fill_overlap == 1 && (s_elems >= 64.0 * 1024 * 1024 || s_elems <= 1024.0 * 1024));
             SideStream *side = (staged && beside) ? side_stream(st) : nullptr;
             std::unique_lock<std::mutex> side_lock;
             if (side) side_lock = std::unique_lock<std::mutex>(side->mu);
