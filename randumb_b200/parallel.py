@@ -313,6 +313,7 @@ class PeerExchange:
         self.g_loc = torch.empty((self.t_r, R), dtype=torch.bfloat16, device=self.dev)
         self.side = torch.cuda.Stream(device=self.dev)
         self.epoch = 0
+        self.forward_pending = False      # a forward whose y product no later barrier has been seen to follow
 
     @staticmethod
     def total_bytes(T: int, R: int) -> int:
@@ -402,6 +403,11 @@ def sharded_forward_peer(x: torch.Tensor, coef: torch.Tensor, seed: int, plan: S
     z_loc = ex.z_full[plan.tok_lo:plan.tok_hi]
     K.gemm_dense(x[plan.tok_lo:plan.tok_hi], coef, out=z_loc)                                  # [t_r, R], in place in z_full
     _mark(timer, "z product")
+    if ex.forward_pending:
+        # two forwards in a row (no backward, whose barriers would order them): a faster rank must not store its next z slice
+        # into this rank's z_full while the previous y product still reads it
+        ex.barrier()
+    ex.forward_pending = True
     ex.side.wait_stream(cur)
     with torch.cuda.stream(ex.side):
         K.noise(ex.S.shape[0], ex.R, seed, plan.row_lo, 0, out=ex.S)
@@ -444,6 +450,7 @@ def sharded_backward_peer(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.T
         K.peer_scatter(ex.ptrs, G, slot, g)
     _mark(timer, "g product")
     ex.barrier()
+    ex.forward_pending = False                                  # every rank is past its y product
     K.reduce_slots(ex.g_loc, ex.g_parts)                                                      # [t_r, R], summed in rank order
     _mark(timer, "g exchange")
     ex.side.wait_stream(cur)

@@ -58,6 +58,12 @@ def _worker(rank, world, port, tmp):
                 K.check_status()
                 out[f"y{step}"], out[f"dx{step}"], out[f"dc{step}"] = y.cpu(), dx.cpu(), dc.cpu()
                 out[f"phases{step}"] = timer.durations()
+            # two forwards in a row (inference): the second one's stores wait for every rank's first y product
+            ya = rb.parallel.sharded_forward_peer(x, C, SEED, plan, ex)
+            yb = rb.parallel.sharded_forward_peer(x, C, SEED, plan, ex)
+            torch.cuda.synchronize()
+            K.check_status()
+            out["y_twice"] = bool(torch.equal(ya, y) and torch.equal(yb, y))
             # the NCCL path on the same inputs
             y_n = rb.parallel.sharded_forward(x, C, SEED, plan)
             dx_n, dc_n = rb.parallel.sharded_backward(dy_r, x, C, SEED, plan, replicate=False)
@@ -92,5 +98,6 @@ def test_peer_exchange_matches_single_gpu_and_oracle(tmp_path):
     # same forward bits as the NCCL path (z is bit-identical whichever way it travels); gradients agree within tolerance
     # (NCCL sums the partial g in its own order, this path in rank order)
     for p in parts:
+        assert p["y_twice"]
         assert torch.equal(p["y0"], p["y_nccl"])
         assert O.close(p["dx0"], p["dx_nccl"], 2e-2) and O.close(p["dc0"], p["dc_nccl"], 2e-2)
