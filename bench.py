@@ -1148,6 +1148,38 @@ def profile_case(args):
                   f"one after the other {med(serial):.1f} us, fill on a second stream beside the product {med(beside):.1f} us", flush=True)
         print("ok")
         return
+    if case == "grads":
+        # dX = g C and dC = g^T x of rdb_linear_bwd one after the other and side by side on disjoint CTA pairs, at two shapes
+        from randumb_b200 import _lib
+
+        def med(f, reps=30):
+            for _ in range(5):
+                f()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                f()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps * 1e3
+
+        for (T, Kin, N, R, tag) in ((8192, 4096, 16384, 1024, "headline layer"), (4096, 16384, 8192, 2048, "one of eight row shards of the 65536 x 16384 layer")):
+            gen = torch.Generator().manual_seed(5)
+            x = torch.randn(T, Kin, generator=gen).bfloat16().cuda()
+            C = (torch.randn(R, Kin, generator=gen) * 0.02).bfloat16().cuda()
+            dy = torch.randn(T, N, generator=gen).bfloat16().cuda()
+            gg = torch.randn(T, R, generator=gen).bfloat16().cuda()
+            bwd = lambda o: med(lambda: K.linear_bwd(dy, x, C, 1, 0, options=o))
+            pairs = _lib.CallOptions(dense_pair=2)
+            print(f"{tag} (T {T}, K {Kin}, N {N}, d_c {R}): rdb_linear_bwd one after the other {bwd(_lib.CallOptions(grads_beside=0)):.1f} us, "
+                  f"automatic {bwd(None):.1f} us, side by side forced {bwd(_lib.CallOptions(grads_beside=2)):.1f} us; alone: "
+                  f"dX {med(lambda: K.gemm_dense(gg, C, True, False)):.1f} us (CTA pairs {med(lambda: K.gemm_dense(gg, C, True, False, options=pairs)):.1f}), "
+                  f"dC {med(lambda: K.gemm_dense(gg, x, False, False)):.1f} us (CTA pairs {med(lambda: K.gemm_dense(gg, x, False, False, options=pairs)):.1f})",
+                  flush=True)
+        K.check_status()
+        print("ok")
+        return
     tokens = args.tokens or {"noise": 2048, "staged": 4096, "products": 4096, "roles": 8192, "gemv": 1}[case]
     dev = torch.device("cuda", 0)
     if case == "gemv":
@@ -1225,6 +1257,15 @@ def profile_case(args):
                 K.set_option(_lib.OPT_NOISE_TILE, prev)
         pair = _lib.CallOptions(dense_pair=2)
         counters("pair kernel y = z S^T", lambda: K.gemm_dense(z, S, options=pair))
+        # the pair kernel's first epilogue warp of each CTA also counts, summed over its tiles: accumulator 0 seen complete ->
+        # handed back [5], -> accumulator 1 handed back [6], store phase [7]
+        ep = prof.view(148, 16).double()
+        tiles_per_pair = -(-((tokens + 511) // 512) * ((out + 255) // 256) // 74)
+        print(f"  per tile ({tiles_per_pair} tiles per pair), cycles: MMA thread waiting for TMEM {float(ep[::2, 2].mean()) / tiles_per_pair:.0f}; "
+              f"epilogue warp, even / odd CTA: accumulator 0 complete -> handed back {float(ep[::2, 5].mean()) / tiles_per_pair:.0f} / "
+              f"{float(ep[1::2, 5].mean()) / tiles_per_pair:.0f}, -> accumulator 1 handed back {float(ep[::2, 6].mean()) / tiles_per_pair:.0f} / "
+              f"{float(ep[1::2, 6].mean()) / tiles_per_pair:.0f}, store phase {float(ep[::2, 7].mean()) / tiles_per_pair:.0f} / "
+              f"{float(ep[1::2, 7].mean()) / tiles_per_pair:.0f}", flush=True)
         counters("pair kernel g = dY S", lambda: K.gemm_dense(dy, S, True, False, options=pair))
     torch.cuda.synchronize()
     K.check_status()
@@ -1251,7 +1292,7 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="row-sharded layer: exchanges by the library's kernels over peer memory (falls back to NCCL when the ranks "
                          "cannot map each other's memory) or by NCCL collectives")
-    ap.add_argument("--profile-case", default=None, choices=["noise", "staged", "roles", "products", "gemv", "hash", "overlap", "formr"],
+    ap.add_argument("--profile-case", default=None, choices=["noise", "staged", "roles", "products", "gemv", "hash", "overlap", "formr", "grads"],
                     help="run a small self-terminating case for a profiler instead of the benchmark")
     ap.add_argument("--tokens", type=int, default=None, help="profile case: token count")
     ap.add_argument("--out", type=int, default=16384, help="profile case: output rows")

@@ -153,7 +153,9 @@ typedef struct rdb_call_options {
  * for the generated operand, [2] waiting for the epilogue to drain TMEM, [3] MMA thread total, [4] TMA thread waiting
  * for a free stage, [5] generator waiting for a free stage, [6] generator hashing and storing, [7] epilogue busy,
  * [8] MMA thread in fences, [9] issuing MMAs, [10] issuing commits; the rest unused.  The CTA-pair plain-product kernel
- * writes [0] (operands), [2], [3] and [4] the same way; the benchmark divides [3] by the launch's event time to report
+ * writes [0] (operands), [2], [3] and [4] the same way, and from the first epilogue warp of each CTA, summed over its tiles,
+ * [5] accumulator 0 seen complete -> handed back, [6] -> accumulator 1 handed back, [7] the store phase (the buffer must be
+ * zeroed before such a launch: these three are added to); the benchmark divides [3] by the launch's event time to report
  * the SM clock the kernel really ran at.  Pass NULL to switch it off (the default; the counters then cost nothing).
  */
 int rdb_set_profile_buffer(void *device_buffer, size_t bytes);

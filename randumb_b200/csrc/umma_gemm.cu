@@ -1331,6 +1331,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 continue;
             }
             uint32_t packed[MT][64];                 // [sub-tile][16-byte chunk * 4 + word]: 128 bf16 columns of this lane's row
+            unsigned t_full = 0;
 #pragma unroll
             for (int s = 0; s < MT; ++s) {
                 const int a = acc_of(it, s);
@@ -1340,6 +1341,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 }
                 if (ok) {
                     tc_fence_after_sync();
+                    if (prof && s == 0) t_full = (unsigned)clock();
 #pragma unroll
                     for (int hb = 0; hb < 2; ++hb) {
                         uint32_t r0[32], r1[32];
@@ -1359,9 +1361,11 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
+                    if (prof && ew == 0 && lane == 0) atomicAdd(reinterpret_cast<unsigned long long *>(prof) + blockIdx.x * 16 + 5 + s, (unsigned long long)((unsigned)clock() - t_full));
                 }
             }
             if (!ok) break;
+            const unsigned t_store = prof ? (unsigned)clock() : 0u;
 #pragma unroll
             for (int s = 0; s < MT; ++s) {
                 const int64_t row_w = m0 + s * 2 * BM + q * 32;    // first row of this warp's 32-row slab
@@ -1390,6 +1394,11 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         bulk_commit_group();
                     }
                 }
+            }
+            if (prof && ew == 0 && lane == 0) {
+                // first epilogue warp of each CTA: cycles from seeing accumulator 0 complete to handing it back [5], to handing
+                // accumulator 1 back [6], and spent in the store phase [7], summed over this CTA's tiles
+                prof[blockIdx.x * 16 + 7] += (long long)((unsigned)clock() - t_store);
             }
         }
         if (lane == 0) bulk_wait_group0();   // all output tiles written (remote ones included) before the CTA retires
