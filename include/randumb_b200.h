@@ -215,6 +215,14 @@ int rdb_linear_stages_noise_ex(int64_t T, int64_t K, int64_t N, int64_t R, int d
 int rdb_linear_path(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl);
 
 /*
+ * Planning query: 1 when rdb_linear_bwd, asked for both gradients of this problem with these options, would run dX beside
+ * dC (RDB_OPT_GRADS_BESIDE), with the CTA pairs each of the two gets in *pairs_dx / *pairs_dc (either may be NULL); 0 when
+ * it runs them one after the other (both set to 0); a negative error for a bad dtype or option.  No reference counterpart.
+ */
+int rdb_linear_bwd_plan(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl,
+                        const rdb_call_options *options, int *pairs_dx, int *pairs_dc);
+
+/*
  * Forward  y[T,N] = x[T,K] * W^T  with W regenerated from (seed, row0) and coef[R,K].
  * This is the fused product the reference left as a placeholder: the aten.mm override
  * (src/rten_cpp/RandumbTensor.py:942-946) -> fakeMM (:771-791), and the abandoned Triton

@@ -57,6 +57,7 @@ PROTOTYPES = {
     "rdb_linear_stages_noise": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32]),
     "rdb_linear_stages_noise_ex": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32, _op]),
     "rdb_linear_path": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32]),
+    "rdb_linear_bwd_plan": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32, _op, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
     "rdb_linear_fwd_ex": (_i32, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32, _op, _vp, _vp]),
     "rdb_linear_bwd_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _u32, _i32, _i32, _i32,
                                  _op, _vp, _vp]),

@@ -370,6 +370,31 @@ extern "C" int rdb_linear_path(int64_t T, int64_t K, int64_t N, int64_t R, int d
     return p | (im << 8);
 }
 
+// whether rdb_linear_bwd would run dX beside dC for this problem, and on how many CTA pairs each
+static bool grads_beside(int64_t T, int64_t K, int64_t R, const CallOpts &o, int *pairs_dx, int *pairs_dc) {
+    return o.grads_beside && o.dense_pair && dense_split_k_slices(R, K, T) == 1 &&
+           dense_beside_plan(T, K, R, R, K, T, o.reserve_sms, o.grads_beside == 2, pairs_dx, pairs_dc);
+}
+
+extern "C" int rdb_linear_bwd_plan(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl,
+                                   const rdb_call_options *options, int *pairs_dx, int *pairs_dc) {
+    if (pairs_dx) *pairs_dx = 0;
+    if (pairs_dc) *pairs_dc = 0;
+    if (T <= 0 || K <= 0 || N <= 0 || R <= 0) return 0;
+    if (dtype != RDB_F32 && dtype != RDB_BF16) return RDB_ERR_DTYPE;
+    CallOpts o;
+    int rc = resolve_opts(options, &o);
+    if (rc) return rc;
+    const int p = choose_path(path, T, K, N, R);
+    const int im = choose_impl(impl, T, K, N, R, dtype, p, true);
+    if (im < 0) return im;
+    int a = 0, b = 0;
+    if (p != RDB_PATH_FACTORED || im != RDB_IMPL_UMMA || !grads_beside(T, K, R, o, &a, &b)) return 0;
+    if (pairs_dx) *pairs_dx = a;
+    if (pairs_dc) *pairs_dc = b;
+    return 1;
+}
+
 extern "C" int rdb_linear_weight(void *w, const void *coef, int64_t K, int64_t N, int64_t R, int64_t row0, uint32_t seed,
                                  int dtype, void *stream) {
     if (K < 0 || N < 0 || R < 0) return RDB_ERR_SHAPE;
@@ -551,8 +576,7 @@ extern "C" int rdb_linear_bwd_ex(void *dx, void *dc, const void *dy, const void 
             // dX and dC both read g and nothing of one another: when their tile lists pack better side by side than one after
             // the other, dX goes to the library's own stream on some of the CTA pairs and dC stays here on the rest
             int pairs_dx = 0, pairs_dc = 0;
-            if (dx && dc && o.grads_beside && o.dense_pair && dense_split_k_slices(R, K, T) == 1 &&
-                dense_beside_plan(T, K, R, R, K, T, o.reserve_sms, o.grads_beside == 2, &pairs_dx, &pairs_dc)) {
+            if (dx && dc && grads_beside(T, K, R, o, &pairs_dx, &pairs_dc)) {
                 if (SideStream *side = side_stream(st)) {
                     std::lock_guard<std::mutex> side_lock(side->mu);
                     cudaError_t e = cudaEventRecord(side->fork, st);

@@ -1774,7 +1774,7 @@ bool dense_beside_plan(int64_t M1, int64_t N1, int64_t Kc1, int64_t M2, int64_t 
     for (int p = 1; p < P; ++p) {
         const double c1 = pair_cost(M1, N1, Kc1, p), c2 = pair_cost(M2, N2, Kc2, P - p);
         const double c = c1 > c2 ? c1 : c2;
-        if (best_p == 0 || c < best) { best = c; best_p = p; }
+        if (best_p == 0 || c <= best) { best = c; best_p = p; }   // among equals, the split that leaves no pair without a tile
     }
     if (!always && best > 0.93 * (alone_cost(M1, N1, Kc1, P) + alone_cost(M2, N2, Kc2, P))) return false;
     *pairs1 = best_p;

@@ -116,6 +116,30 @@ def test_association_and_kernel_decision_table(built_lib):
     assert L.rdb_linear_workspace_bytes(1, 8192, k, n, r, _lib.BF16, 0, 0) == n * r * 2 + 2 * n * k * 2
 
 
+def test_backward_plan_puts_the_two_gradients_side_by_side_only_where_their_tiles_pack(built_lib):
+    """rdb_linear_bwd_plan: dX (256 tiles of 16 k-blocks) and dC (32 tiles of 128 k-blocks) of the headline layer share the
+    74 CTA pairs 42 : 32; a dX that fills the pairs by itself, or a dC with at most 128 rows, stays in sequence."""
+    L = _lib.lib()
+
+    def plan(T, K, N, R, dt=_lib.BF16, opts=None):
+        a, b = ctypes.c_int(-1), ctypes.c_int(-1)
+        rc = L.rdb_linear_bwd_plan(T, K, N, R, dt, 0, 0, ctypes.byref(opts) if opts is not None else None, ctypes.byref(a), ctypes.byref(b))
+        return rc, a.value, b.value
+
+    assert plan(8192, 4096, 16384, 1024) == (1, 42, 32)                    # headline layer
+    assert plan(4096, 16384, 65536, 2048) == (0, 0, 0)                     # row-sharded layer on one GPU
+    assert plan(8192, 768, 3072, 128) == (0, 0, 0)                         # GPT-2-small MLP: dC has 128 rows
+    assert plan(64, 784, 256, 64, _lib.F32) == (0, 0, 0)
+    assert plan(8192, 4096, 16384, 1024, opts=_lib.CallOptions(grads_beside=0)) == (0, 0, 0)
+    assert plan(8192, 4096, 16384, 1024, opts=_lib.CallOptions(dense_pair=0)) == (0, 0, 0)
+    rc, a, b = plan(4096, 16384, 65536, 2048, opts=_lib.CallOptions(grads_beside=2))
+    assert rc == 1 and a + b == 74 and a > 0 and b > 0
+    rc, a, b = plan(8192, 4096, 16384, 1024, opts=_lib.CallOptions(reserve_sms=20, grads_beside=2))   # 20 SMs left to a collective
+    assert rc == 1 and a + b == 64
+    assert plan(8192, 4096, 16384, 1024, opts=_lib.CallOptions(grads_beside=7))[0] == -6
+    assert L.rdb_linear_bwd_plan(8192, 4096, 16384, 1024, _lib.BF16, 0, 0, None, None, None) == 1
+
+
 def test_peer_exchange_arguments_are_checked_on_host(built_lib):
     L = _lib.lib()
     ok = 0x7F0000001000
