@@ -7,7 +7,7 @@
  * and   y = x W^T,   dX = dY W,   dC = S^T (dY^T X).
  * W is never formed on the factored path (every BASELINE layer but a 256 -> 10 head); the W path, chosen when it costs
  * fewer FLOPs, keeps W in the caller's workspace for the length of one call.  S is regenerated from the seed in every call: tile by tile in shared
- * memory, or (1024 tokens or more) once per call as a transient bf16 copy in the caller's workspace -- see
+ * memory, or (every backward; forwards of 1024 tokens or more) once per call as a transient bf16 copy in the caller's workspace -- see
  * RDB_OPT_STAGE_NOISE.  Nothing of it survives the call.
  *
  * Conventions for every entry point
@@ -95,10 +95,11 @@ const char *rdb_strerror(int code);
  *                           pairs evenly, else the single-CTA 128 x 256 kernel
  *                        0: always the single-CTA kernel   2: always CTA pairs
  *   RDB_OPT_STAGE_NOISE  how rdb_linear_fwd / rdb_linear_bwd (bf16, factored) obtain the noise operand:
- *                        0 (default): automatic -- for 1024 tokens or more, S (bf16, N x R, never W) is written
- *                           once per call into the workspace and consumed by the plain tensor-core product, which
- *                           hashes every noise element once instead of once per 512-token tile; below that, and
- *                           whenever S would exceed 1 GiB, the kernels regenerate S tile by tile in shared memory
+ *                        0 (default): automatic -- S (bf16, N x R, never W) is written once per call into the workspace
+ *                           and consumed by the plain tensor-core product, which hashes every noise element once instead
+ *                           of once per 512-token tile: by the backward at every token count (g = dY S has too few work
+ *                           units to hash S in otherwise), by the forward for 1024 tokens or more; a forward below that,
+ *                           and every call whose S would exceed 1 GiB, regenerates S tile by tile in shared memory
  *                        1: always regenerate tile by tile (no S in memory)   2: always stage when it fits
  *   RDB_OPT_RESERVE_SMS  0 (default) .. RDB_MAX_RESERVE_SMS: SMs the persistent plain-product kernels leave without a
  *                        CTA.  Their CTAs take a whole SM each for the length of the launch, so a collective enqueued
@@ -197,9 +198,10 @@ size_t rdb_linear_workspace_bytes_ex(int op, int64_t T, int64_t K, int64_t N, in
                                      int impl, const rdb_call_options *options);
 
 /*
- * 1 when the linear entry points would, for this problem, write S (bf16, N x R) into the workspace once per call
- * and run the plain tensor-core product on it; 0 when they regenerate S tile by tile inside the kernel (or use the
- * float32 kernels); negative: error.  See RDB_OPT_STAGE_NOISE.  No reference counterpart (a planning query).
+ * Whether the linear entry points would, for this problem, write S (bf16, N x R) into the workspace once per call and run
+ * the plain tensor-core product on it: bit 0 (value 1) for rdb_linear_fwd, bit 1 (value 2) for rdb_linear_bwd; a clear bit
+ * means that call regenerates S tile by tile inside the kernel (or uses the float32 kernels); negative: error.  See
+ * RDB_OPT_STAGE_NOISE.  No reference counterpart (a planning query).
  */
 int rdb_linear_stages_noise(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl);
 int rdb_linear_stages_noise_ex(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl,

@@ -87,11 +87,15 @@ static int choose_impl(int impl, int64_t T, int64_t K, int64_t N, int64_t R, int
 
 // Whether the bf16 factored products take S from a staged copy in the workspace (hashing every element once per
 // call) or regenerate it tile by tile inside the kernel (once per 512-token tile, nothing in memory).
-static bool stage_noise(int64_t T, int64_t N, int64_t R, const CallOpts &o) {
+static bool stage_noise(int op, int64_t T, int64_t N, int64_t R, const CallOpts &o) {
     const bool fits = (double)N * (double)R * 2.0 <= 1073741824.0;
     if (o.stage_noise == 1 || !fits) return false;
     if (o.stage_noise == 2) return true;
-    return T >= 1024;
+    // Forward (op 0): y = z S^T has N / 256 work units whatever the token count, so below 1024 tokens -- where each element
+    // is hashed at most twice -- regenerating costs the same as a fill plus a plain product and needs no scratch.
+    // Backward (op 1): g = dY S has only R / 256 work units per 512 tokens to hash all of S in, so hashing it once on every SM
+    // wins at every token count (512 tokens, 16384 x 1024: 206 against 60 us for the whole backward).
+    return op == 1 || T >= 1024;
 }
 
 struct WsLayout {
@@ -111,14 +115,14 @@ static WsLayout ws_layout(int op, int64_t T, int64_t K, int64_t N, int64_t R, in
     if (path == RDB_PATH_FACTORED) {
         if (impl == RDB_IMPL_UMMA) {
             seg[0] = (size_t)T * R * 2;
-            if (stage_noise(T, N, R, o)) seg[1] = (size_t)N * R * 2;
+            if (stage_noise(op, T, N, R, o)) seg[1] = (size_t)N * R * 2;
             // float32 partial products of the products with few output tiles and a long contraction, computed split-K:
             // forward z = x C^T (contraction K); backward g = dY S (contraction N, staged S only) and dC = g^T x (contraction T)
             if (op == 0) {
                 const int split = dense_split_k_slices(T, R, K);
                 if (split > 1) seg[2] = (size_t)split * T * R * 4;
             } else {
-                const int sg = stage_noise(T, N, R, o) ? dense_split_k_slices(T, R, N) : 1;
+                const int sg = stage_noise(1, T, N, R, o) ? dense_split_k_slices(T, R, N) : 1;
                 const int sc = dense_split_k_slices(R, K, T);
                 const size_t a = sg > 1 ? (size_t)sg * T * R * 4 : 0, b = sc > 1 ? (size_t)sc * R * K * 4 : 0;
                 seg[2] = a > b ? a : b;        // used one after the other
@@ -354,7 +358,8 @@ extern "C" int rdb_linear_stages_noise_ex(int64_t T, int64_t K, int64_t N, int64
     const int im = choose_impl(impl, T, K, N, R, dtype, p, true);
     if (im < 0) return im;
     if (im != RDB_IMPL_UMMA) return 0;
-    return (p == RDB_PATH_WPATH || stage_noise(T, N, R, o)) ? 1 : 0;
+    if (p == RDB_PATH_WPATH) return 3;
+    return (stage_noise(0, T, N, R, o) ? 1 : 0) | (stage_noise(1, T, N, R, o) ? 2 : 0);
 }
 
 extern "C" int rdb_linear_stages_noise(int64_t T, int64_t K, int64_t N, int64_t R, int dtype, int path, int impl) {
@@ -460,7 +465,7 @@ extern "C" int rdb_linear_fwd_ex(void *y, const void *x, const void *coef, void 
     if (p == RDB_PATH_FACTORED) {
         if (im == RDB_IMPL_UMMA) {
             void *z = ws + w.off[0];
-            const bool staged = stage_noise(T, N, R, o);
+            const bool staged = stage_noise(0, T, N, R, o);
             void *S = ws + w.off[1];
             // the hash of S (integer ALU) does not depend on z = x C^T (tensor pipe), so a long fill runs beside that product,
             // and so does one so short that it is all launch latency (at most 1 Mi elements: the 24 layers of the
@@ -559,7 +564,7 @@ extern "C" int rdb_linear_bwd_ex(void *dx, void *dc, const void *dy, const void 
         if (im == RDB_IMPL_UMMA) {
             void *g = ws + w.off[0];
             // g = dY S ; dX = g C (C read in place as an MN-major B operand) ; dC = g^T x (both operands MN-major)
-            if (stage_noise(T, N, R, o)) {
+            if (stage_noise(1, T, N, R, o)) {
                 void *S = ws + w.off[1];
                 rc = fill_noise(S, N, R, row0, seed, st, nullptr);
                 if (rc) return rc;

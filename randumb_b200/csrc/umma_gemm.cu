@@ -662,7 +662,7 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 // accumulator s of this CTA has been read out: tell the MMA thread of the pair
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[s]), leader_rank));
+                if (lane == 0) mbar_arrive_remote(mapa(smem_u32(&bar_tmem_empty[s]), leader_rank));
             }
             tphase ^= 1;
         }
@@ -738,7 +738,7 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         break;
                     }
                     fence_proxy_async_smem();
-                    mbar_arrive_cluster(mapa(smem_u32(&bar_full[st.idx]), leader_rank));
+                    mbar_arrive_remote(mapa(smem_u32(&bar_full[st.idx]), leader_rank));
                     st.advance<D>();
                 }
             }
@@ -757,7 +757,7 @@ noise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     }
                     const uint32_t fa = smem_u32(&bar_free_all[st.idx]);
 #pragma unroll
-                    for (int qd = 0; qd < NP; ++qd) mbar_arrive_cluster(mapa(fa, 2u * qd + half));
+                    for (int qd = 0; qd < NP; ++qd) mbar_arrive_remote(mapa(fa, 2u * qd + half));
                     st.advance<D>();
                 }
             }
@@ -1042,6 +1042,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 //   warp 1      MMA issuer (even CTA only); tcgen05.commit frees the stage in both CTAs
 //   warps 2-9   epilogue: TMEM -> bf16 -> swizzled staging -> TMA tile stores (two warps per lane quarter)
 // ================================================================================================
+// the pair kernel's epilogue reads accumulator 0 (the one the next tile's first MMAs wait for) with all four of a warp's
+// tcgen05.ld in flight before one wait; accumulator 1, read while 64 converted registers are live, two at a time
+constexpr bool DRAIN_WIDE = true;
+
 template <int MT, int D>
 struct DensePairCfg {
     static constexpr int BN = 256;
@@ -1326,7 +1330,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     }
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
+                    if (lane == 0) mbar_arrive_remote(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
                 }
                 continue;
             }
@@ -1342,6 +1346,27 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (ok) {
                     tc_fence_after_sync();
                     if (prof && s == 0) t_full = (unsigned)clock();
+                    if (DRAIN_WIDE && s == 0) {
+                        // accumulator 0 is the one the next tile's first MMAs wait for: all four loads in flight at once
+                        uint32_t r0[32], r1[32], r2[32], r3[32];
+                        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + cg * 128);
+                        tmem_ld_32x32(taddr, r0);
+                        tmem_ld_32x32(taddr + 32, r1);
+                        tmem_ld_32x32(taddr + 64, r2);
+                        tmem_ld_32x32(taddr + 96, r3);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r2[2 * j]), __uint_as_float(r2[2 * j + 1]));
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r3[2 * j]), __uint_as_float(r3[2 * j + 1]));
+                            packed[s][j] = *reinterpret_cast<uint32_t *>(&h0);
+                            packed[s][16 + j] = *reinterpret_cast<uint32_t *>(&h1);
+                            packed[s][32 + j] = *reinterpret_cast<uint32_t *>(&h2);
+                            packed[s][48 + j] = *reinterpret_cast<uint32_t *>(&h3);
+                        }
+                    } else {
 #pragma unroll
                     for (int hb = 0; hb < 2; ++hb) {
                         uint32_t r0[32], r1[32];
@@ -1357,11 +1382,13 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             packed[s][hb * 32 + 16 + j] = *reinterpret_cast<uint32_t *>(&h1);
                         }
                     }
+                    }
                     // this warp's part of the accumulator is in registers: hand it back to the MMA thread of the pair
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
-                    if (prof && ew == 0 && lane == 0) atomicAdd(reinterpret_cast<unsigned long long *>(prof) + blockIdx.x * 16 + 5 + s, (unsigned long long)((unsigned)clock() - t_full));
+                    if (lane == 0) mbar_arrive_remote(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
+                    if (prof && ew == 0 && lane == 0)
+                        atomicAdd(reinterpret_cast<unsigned long long *>(prof) + blockIdx.x * 16 + 5 + s, (unsigned long long)((unsigned)clock() - t_full));
                 }
             }
             if (!ok) break;
@@ -1575,9 +1602,10 @@ int umma_gemm_noise(void *d, const void *a, int64_t M, int64_t N, int64_t Kc, in
                     int32_t *status, cudaStream_t st, const CallOpts &o) {
     if (M == 0 || N == 0) return RDB_OK;
     int cfg = o.noise_tile;
-    // more than one 512-token tile and a short contraction (many tiles, epilogue matters): CTA pairs (cta_group::2);
-    // otherwise one CTA per 512-token tile
-    if (cfg == 0) cfg = (M > 4 * BM && Kc <= 4096) ? 7 : 1;
+    // more than one 512-token tile: two CTA pairs per cluster that share every generated stage (half the hashing per SM);
+    // a single token tile: one CTA per work unit when there are many of them (short contraction, many generated rows),
+    // four pairs splitting the hashing of each stage when there are few (long generated contraction)
+    if (cfg == 0) cfg = (M > 4 * BM) ? 8 : (Kc > 4096 ? 9 : 1);
     switch (cfg) {
         case 2: return launch_noise_gemm<1, 2, 256, 3, 3>(d, a, M, N, Kc, lda, ldd, lin, status, st);
         case 3: return launch_noise_gemm<2, 4, 128, 2, 4>(d, a, M, N, Kc, lda, ldd, lin, status, st);

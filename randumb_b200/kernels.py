@@ -248,11 +248,12 @@ def gemm_noise(a: torch.Tensor, n: int, seed: int, transposed: bool = False, row
 
 
 def linear_stages_noise(T: int, K: int, N: int, R: int, dtype: torch.dtype, path: int = PATH_AUTO, impl: int = IMPL_AUTO,
-                        options: Optional[_lib.CallOptions] = None) -> bool:
-    """Whether linear_fwd / linear_bwd would write S once into the workspace for this problem (see rdb_linear_stages_noise)."""
+                        options: Optional[_lib.CallOptions] = None, backward: bool = False) -> bool:
+    """Whether linear_fwd (or, with ``backward``, linear_bwd) would write S once into the workspace for this problem (see
+    rdb_linear_stages_noise)."""
     rc = _lib.lib().rdb_linear_stages_noise_ex(int(T), int(K), int(N), int(R), _dt(dtype), path, impl, _opts(options))
     _lib.check(min(rc, 0), "rdb_linear_stages_noise")
-    return rc == 1
+    return bool(rc & (2 if backward else 1))
 
 
 def linear_plan(T: int, K: int, N: int, R: int, dtype: torch.dtype, path: int = PATH_AUTO, impl: int = IMPL_AUTO) -> Tuple[int, int]:
@@ -265,12 +266,14 @@ def linear_plan(T: int, K: int, N: int, R: int, dtype: torch.dtype, path: int = 
 def noise_product(a: torch.Tensor, n: int, seed: int, transposed: bool = False, row0: int = 0,
                   options: Optional[_lib.CallOptions] = None) -> torch.Tensor:
     """``a @ S[row0:row0+n].T`` (``transposed=False``, a is [M, R]) or ``a @ S[row0:row0+Kc]`` (``transposed=True``, a is
-    [M, Kc], result [M, n]) with the same rule as the linear entry points: bf16 problems with 1024 rows or more hash S
-    once into a temporary and run the plain tensor-core product; everything else regenerates S inside the kernel."""
+    [M, Kc], result [M, n]) with the same rule as the linear entry points: bf16 problems hash S once into a temporary and run
+    the plain tensor-core product -- the transposed product (the backward's g = dY S) always, the other one from 1024 rows of
+    ``a`` up; everything else regenerates S inside the kernel."""
     M, Kc = a.shape
     rows, cols = (Kc, n) if transposed else (n, Kc)          # extent of the noise block S[rows, cols]
     ok8 = rows % 8 == 0 and cols % 8 == 0
-    if a.dtype == torch.bfloat16 and ok8 and linear_stages_noise(M, 8, rows, cols, a.dtype, PATH_FACTORED, options=options):
+    if a.dtype == torch.bfloat16 and ok8 and linear_stages_noise(M, 8, rows, cols, a.dtype, PATH_FACTORED, options=options,
+                                                                       backward=transposed):
         S = noise(rows, cols, seed, row0, 0, torch.bfloat16, a.device)
         return gemm_dense(a, S, True, not transposed, options=options)
     return gemm_noise(a, n, seed, transposed, row0)

@@ -88,11 +88,11 @@ def test_unaligned_operands_are_caught_on_host(built_lib):
     assert L.rdb_linear_bwd(ok, ok, odd, ok, ok, *args, _lib.IMPL_UMMA, None, None) == -4
     assert L.rdb_linear_bwd(odd, None, ok, ok, ok, *args, _lib.IMPL_UMMA, None, None) == -4
     assert "16-byte" in _lib.strerror(-4)
-    # AUTO: falls back to the CUDA-core layout (float32 z: T*R*4 bytes), so a workspace sized for the bf16 kernels is refused
+    # AUTO: falls back to the CUDA-core layout (float32 z: T*R*4 bytes), so a workspace that holds only a bf16 z is refused
     umma_ws = L.rdb_linear_workspace_bytes(0, T, K, N, R, _lib.BF16, _lib.PATH_FACTORED, _lib.IMPL_AUTO)
     simt_ws = L.rdb_linear_workspace_bytes(0, T, K, N, R, _lib.BF16, _lib.PATH_FACTORED, _lib.IMPL_SIMT)
     assert umma_ws == T * R * 2 and simt_ws == T * R * 4
-    assert L.rdb_linear_fwd(ok, odd, ok, ws, umma_ws, T, K, N, R, 0, 0, _lib.BF16, _lib.PATH_FACTORED, _lib.IMPL_AUTO, None, None) == -5
+    assert L.rdb_linear_fwd(ok, odd, ok, ws, T * R * 2, T, K, N, R, 0, 0, _lib.BF16, _lib.PATH_FACTORED, _lib.IMPL_AUTO, None, None) == -5
 
 
 def test_association_and_kernel_decision_table(built_lib):
@@ -169,7 +169,7 @@ def test_workspace_sizes(built_lib):
     L = _lib.lib()
     # bf16 factored on tensor cores: z or g, bf16 [T, R], plus S bf16 [N, R] when the noise operand is staged
     zg, S = 8192 * 1024 * 2, 16384 * 1024 * 2
-    assert L.rdb_linear_stages_noise(8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == 1
+    assert L.rdb_linear_stages_noise(8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == 3          # forward | backward
     assert L.rdb_linear_workspace_bytes(0, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == zg + S
     assert L.rdb_linear_workspace_bytes(1, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == zg + S
     assert L.rdb_set_option(_lib.OPT_STAGE_NOISE, 1) == 0          # regenerate inside the kernel: nothing of S in memory
@@ -178,8 +178,12 @@ def test_workspace_sizes(built_lib):
         assert L.rdb_linear_workspace_bytes(0, 8192, 4096, 16384, 1024, _lib.BF16, 0, 0) == zg
     finally:
         assert L.rdb_set_option(_lib.OPT_STAGE_NOISE, 0) == 1
-    # few tokens: one 512-token tile regenerates S once anyway; a noise block above 1 GiB is never staged
-    assert L.rdb_linear_stages_noise(512, 4096, 16384, 1024, _lib.BF16, 0, 0) == 0
+    # few tokens: the forward's one 512-token tile regenerates S once anyway, the backward still hashes it once on every SM
+    # (its g = dY S has four work units to do it in otherwise); a noise block above 1 GiB is never staged
+    assert L.rdb_linear_stages_noise(512, 4096, 16384, 1024, _lib.BF16, 0, 0) == 2
+    assert L.rdb_linear_workspace_bytes_ex(0, 512, 4096, 16384, 1024, _lib.BF16, 0, 0, None) == \
+        L.rdb_linear_workspace_bytes_ex(0, 512, 4096, 16384, 1024, _lib.BF16, 0, 0, ctypes.byref(_lib.CallOptions(stage_noise=1)))
+    assert L.rdb_linear_workspace_bytes(1, 512, 4096, 16384, 1024, _lib.BF16, 0, 0) >= 512 * 1024 * 2 + S
     assert L.rdb_linear_stages_noise(8192, 4096, 1 << 20, 1024, _lib.BF16, 0, 0) == 0
     assert L.rdb_linear_stages_noise(8192, 4096, 16384, 1024, _lib.F32, 0, 0) == 0
     # fp32 factored: f32 [T, R]
