@@ -141,13 +141,12 @@ __device__ __forceinline__ void bulk_copy_to_cta(uint32_t cdst, uint32_t src, ui
     asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(cdst), "r"(src), "r"(bytes), "r"(cbar) : "memory");
 }
-// Arrive on a barrier that may live in another CTA of the cluster (release at cluster scope).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t caddr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(caddr) : "memory");
-}
-// The same arrive without the cluster-scope release (default semantics: release at CTA scope).  For signals that publish no
-// memory: "this warp has read its part of the accumulator" follows tcgen05.wait::ld, after which the values are in
-// registers; the cluster-scope form measured about 1500 cycles per arrive under load, this one a few dozen.
+// Arrive on a barrier that may live in another CTA of the cluster, with the default semantics (release at CTA scope).
+// Every use signals something that needs no cluster-wide flush: "this warp has read its part of the accumulator" follows
+// tcgen05.wait::ld, after which the values are in registers; "this stage is free" publishes nothing; and the odd CTA's
+// "stage complete here" concerns shared memory of the odd SM, written before its generators arrived on the local barrier
+// and read by that same SM's tensor core.  The cluster-scope release (mbarrier.arrive.release.cluster) waits for the
+// thread's outstanding global stores as well and measured about 1500 cycles per arrive while a kernel streams its output.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t caddr) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(caddr) : "memory");
 }
