@@ -522,7 +522,7 @@ def run_ours(args, cfg):
         flops_launch = 2.0 * T * n_local * R
         fused_ms = time_pair(lambda: K.gemm_noise(z, n_local, seed, False, row0, impl=K.IMPL_UMMA),
                              lambda: K.gemm_noise(dy, R, seed, True, row0, impl=K.IMPL_UMMA))
-        fused = {"kernel": "noise_pair_kernel (y = z S^T) and noise_gemm_kernel (g = dY S): S regenerated in shared memory per 512-token tile",
+        fused = {"kernel": "noise_pair_kernel, two CTA pairs per cluster sharing every generated stage (y = z S^T and g = dY S): S regenerated in shared memory per 512-token tile",
                  "avg_launch_ms": fused_ms, "achieved": flops_launch / (fused_ms * 1e-3) / 1e12}
         if staged:
             S = K.noise(n_local, R, seed, row0, 0, dt, dev)

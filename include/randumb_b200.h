@@ -84,7 +84,7 @@ const char *rdb_strerror(int code);
  * that one call (a field < 0, or a NULL pointer, keeps the default), so concurrent callers -- autograd worker threads,
  * several streams -- never have to change process state around a launch.
  *   RDB_OPT_NOISE_TILE   kernel variant / work unit of the generated-operand product:
- *                        0: automatic (7 for more than 512 tokens with a contraction of at most 4096, else 1)
+ *                        0: automatic (8 for more than 512 tokens; for one token tile 1 with a contraction of at most 4096, else 9)
  *                        single-CTA MMAs (cta_group::1), (cluster size, token sub-tiles, generated rows):
  *                          1: (1, 4, 128)   2: (1, 2, 256)   3: (2, 4, 128)   4: (4, 4, 128)   5: (4, 2, 256)   6: (1, 4, 128) with a deeper ring
  *                          CTAs of a cluster share each generated stage through distributed shared memory

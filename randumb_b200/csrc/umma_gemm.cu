@@ -1346,6 +1346,14 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (ok) {
                     tc_fence_after_sync();
                     if (prof && s == 0) t_full = (unsigned)clock();
+                    // this warp's part of the accumulator has landed in registers: hand it back to the MMA thread of the pair
+                    auto hand_back = [&]() {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_remote(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
+                        if (prof && ew == 0 && lane == 0)
+                            atomicAdd(reinterpret_cast<unsigned long long *>(prof) + blockIdx.x * 16 + 5 + s, (unsigned long long)((unsigned)clock() - t_full));
+                    };
                     if (DRAIN_WIDE && s == 0) {
                         // accumulator 0 is the one the next tile's first MMAs wait for: all four loads in flight at once
                         uint32_t r0[32], r1[32], r2[32], r3[32];
@@ -1355,6 +1363,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         tmem_ld_32x32(taddr + 64, r2);
                         tmem_ld_32x32(taddr + 96, r3);
                         tmem_ld_wait();
+                        hand_back();          // the values are in registers: the conversion runs under the next tile's MMAs
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
@@ -1374,6 +1383,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         tmem_ld_32x32(taddr, r0);
                         tmem_ld_32x32(taddr + 32, r1);
                         tmem_ld_wait();
+                        if (hb == 1) hand_back();
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
@@ -1383,12 +1393,6 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         }
                     }
                     }
-                    // this warp's part of the accumulator is in registers: hand it back to the MMA thread of the pair
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_remote(mapa(smem_u32(&bar_tmem_empty[a]), leader_rank));
-                    if (prof && ew == 0 && lane == 0)
-                        atomicAdd(reinterpret_cast<unsigned long long *>(prof) + blockIdx.x * 16 + 5 + s, (unsigned long long)((unsigned)clock() - t_full));
                 }
             }
             if (!ok) break;
