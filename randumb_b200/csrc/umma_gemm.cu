@@ -784,7 +784,11 @@ struct DenseCfg {
     static constexpr int STAGE = A_STAGE + B_STAGE;
     static constexpr int EPI_WARPS = 8;                               // two per TMEM lane quarter, half of the columns each
     static constexpr int THREADS = (2 + EPI_WARPS) * 32;
-    static constexpr int OUT_STAGING = EPI_WARPS * 4096;              // per epilogue warp: one [32 rows x 64 columns] bf16 box
+    // per epilogue warp: [32 rows x 64 columns] bf16 boxes for the TMA tile stores.  With a ring of three stages (the
+    // variant for contractions of at most three k-blocks, whose tiles are all epilogue) there is room for two per warp, so
+    // a warp fills one while the store engine still reads the other
+    static constexpr int STG = STAGES <= 3 ? 2 : 1;
+    static constexpr int OUT_STAGING = EPI_WARPS * 4096 * STG;
     static constexpr int SMEM_DYN = STAGES * STAGE + OUT_STAGING + 1024;
     static_assert(SMEM_DYN <= 232448 - 512, "shared memory");
     static_assert(2 * BN <= TMEM_COLS, "two accumulator stages must fit TMEM");
@@ -930,7 +934,19 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         constexpr int CPW = BN / (Cfg::EPI_WARPS / 4);  // accumulator columns per warp
         const int cbase = ((warp - 2) >> 2) * CPW;
         constexpr bool TMA_OUT = (sizeof(OutT) == 2);   // bf16: swizzled staging + TMA tile stores; float32: direct stores
-        const uint32_t stag = smem_base + STAGES * Cfg::STAGE + (uint32_t)(warp - 2) * 4096u;
+        const uint32_t stag0 = smem_base + STAGES * Cfg::STAGE + (uint32_t)(warp - 2) * (4096u * Cfg::STG);
+        uint32_t stag = stag0, box = 0;
+        // before a staging box is written again the store that last read it must be done with it
+        auto next_box = [&]() {
+            if (Cfg::STG == 2) {
+                stag = stag0 + box * 4096u;
+                box ^= 1u;
+                if (lane == 0) bulk_wait_group_read1();
+            } else {
+                if (lane == 0) bulk_wait_group_read0();
+            }
+            __syncwarp();
+        };
         uint32_t acc = 0, acc_phase = 0;
         for (int64_t w = blockIdx.x; w < total_tiles; w += gridDim.x) {
             const int64_t tile = w % tiles_mn;
@@ -950,9 +966,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0);
                     tmem_ld_32x32(taddr, r0);
                     tmem_ld_32x32(taddr + 32, r1);
-                    // the previous store of this warp must have finished reading the staging box
-                    if (lane == 0) bulk_wait_group_read0();
-                    __syncwarp();
+                    next_box();
                     tmem_ld_wait();
                     const uint32_t rowaddr = stag + (uint32_t)lane * 128u;
 #pragma unroll
@@ -972,9 +986,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0 && row_w < M && n0 + c0 < N) {
-                        tma_store_2d(&tmap_d, stag, (int32_t)(n0 + c0), (int32_t)row_w);
-                        bulk_commit_group();
+                    if (lane == 0) {
+                        if (row_w < M && n0 + c0 < N) tma_store_2d(&tmap_d, stag, (int32_t)(n0 + c0), (int32_t)row_w);
+                        bulk_commit_group();      // one group per box use, empty or not: next_box() counts groups
                     }
                 }
             } else if (f32_tma) {
@@ -985,8 +999,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 for (int c0 = cbase; c0 < cbase + CPW; c0 += 32) {
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
-                    if (lane == 0) bulk_wait_group_read0();
-                    __syncwarp();
+                    next_box();
                     tmem_ld_wait();
                     const uint32_t rowaddr = stag + (uint32_t)lane * 128u;
 #pragma unroll
@@ -995,8 +1008,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                      "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0 && n0 + c0 < N) {
-                        tma_store_2d(&tmap_d, stag, (int32_t)(n0 + c0), (int32_t)row_g);
+                    if (lane == 0) {
+                        if (n0 + c0 < N) tma_store_2d(&tmap_d, stag, (int32_t)(n0 + c0), (int32_t)row_g);
                         bulk_commit_group();
                     }
                 }
@@ -1768,6 +1781,10 @@ static int dense_by_out(void *d, const void *a, const void *b, int64_t M, int64_
     // at most 128 output columns (a coefficient dimension of 128 or less): 128-column tiles, half the MMA and B traffic
     if (d_dtype == RDB_BF16 && N <= 128)
         return launch_dense<128, 6, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st, rs);
+    // a contraction of at most three k-blocks (the y and dX of a layer with a small coefficient matrix): every tile is mostly
+    // epilogue, so the ring gives a stage up for a second staging box per epilogue warp
+    if (d_dtype == RDB_BF16 && Kc <= 3 * BK)
+        return launch_dense<256, 3, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st, rs);
     if (d_dtype == RDB_BF16)
         return launch_dense<256, 4, A_MN, B_MN, __nv_bfloat16>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st, rs);
     if (d_dtype == RDB_F32) return launch_dense<256, 4, A_MN, B_MN, float>(d, a, b, M, N, Kc, lda, ldb, ldd, status, st, rs);
