@@ -277,7 +277,7 @@ class ShardedLayerBench:
                                                          else "NCCL collectives between the products")
         self.y_all = None
 
-    def step(self, gather_output=False, replicate=False, timer=None):
+    def step(self, gather_output=False, replicate=False, timer=None, keep_noise=False):
         rb, K, plan, seed = self.rb, self.K, self.plan, self.cfg["seed"]
         if self.world == 1:
             y = K.linear_fwd(self.x, self.C, seed, self.n_local, self.row0)
@@ -300,7 +300,7 @@ class ShardedLayerBench:
             # every rank receives all column blocks of y (rank-major [G, T, N/G]); runs beside the backward products
             work = self.dist.all_gather_into_tensor(self.y_all, y, async_op=True)
         if self.ex is not None and not replicate:
-            dx, dc = rb.parallel.sharded_backward_peer(self.dy, self.x, self.C, seed, plan, self.ex, timer)
+            dx, dc = rb.parallel.sharded_backward_peer(self.dy, self.x, self.C, seed, plan, self.ex, timer, keep_noise=keep_noise)
         else:
             dx, dc = rb.parallel.sharded_backward(self.dy, self.x, self.C, seed, plan, replicate=replicate)
             if timer is not None:
@@ -378,6 +378,11 @@ def sharded_record(args, dev, world, rank, rb, K):
             rec["nccl_exchange"] = {"what": "the same step with NCCL all-gather / all-reduce between the products", "ms_per_step": ms_n,
                                     "value": flops / (ms_n * 1e-3) / 1e12, "speedup_vs_single_gpu": ms1 / ms_n}
             del nccl
+            ms_k = b.timed(args.steps, args.warmup, keep_noise=True)
+            rec["keep_noise"] = {"what": "the same step with this rank's noise rows kept from the forward to the backward (hashed once "
+                                         "per step instead of twice; the single-GPU step it is compared with still hashes twice, as "
+                                         "the stateless entry points do, so this is not the like-for-like figure: `value` is)",
+                                 "ms_per_step": ms_k, "value": flops / (ms_k * 1e-3) / 1e12, "speedup_vs_single_gpu": ms1 / ms_k}
     else:
         rec["single_gpu_ms_per_step"], rec["speedup_vs_single_gpu"] = ms, 1.0
     del b

@@ -314,6 +314,7 @@ class PeerExchange:
         self.side = torch.cuda.Stream(device=self.dev)
         self.epoch = 0
         self.forward_pending = False      # a forward whose y product no later barrier has been seen to follow
+        self.noise_key = None             # (seed, row_lo, row_hi) of the noise rows self.S holds
 
     @staticmethod
     def total_bytes(T: int, R: int) -> int:
@@ -411,6 +412,7 @@ def sharded_forward_peer(x: torch.Tensor, coef: torch.Tensor, seed: int, plan: S
     ex.side.wait_stream(cur)
     with torch.cuda.stream(ex.side):
         K.noise(ex.S.shape[0], ex.R, seed, plan.row_lo, 0, out=ex.S)
+    ex.noise_key = (int(seed), plan.row_lo, plan.row_hi)         # what ex.S holds once the side stream has been waited for
     K.peer_copy(_others(ex), ex.world - 1, ex.slice_offset(ex.z_off, plan.tok_lo), z_loc)
     ex.barrier()
     cur.wait_stream(ex.side)
@@ -429,18 +431,25 @@ def _others(ex: PeerExchange):
 
 
 def sharded_backward_peer(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan,
-                          ex: PeerExchange, timer: Optional[PhaseTimer] = None, fused_scatter: bool = True
-                          ) -> Tuple[torch.Tensor, torch.Tensor]:
+                          ex: PeerExchange, timer: Optional[PhaseTimer] = None, fused_scatter: bool = True,
+                          keep_noise: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """``sharded_backward(replicate=False)`` -- (dX[tok_lo:tok_hi, :], dC[:, k_lo:k_hi]) -- with the sum of g over the ranks
     done by this library's kernels.  The partial g = dY_r S_r leaves the product kernel's epilogue tile by tile straight into
     the owner of each token slice (``rdb_gemm_dense_scatter``: the scatter half of a reduce-scatter fused into the product);
     after a barrier every rank sums the G contributions to its slice in rank order; the reduced slice is stored into every
     rank's ``g_full`` on a side stream while the tensor cores compute dX from it; dC (all tokens, this rank's input
-    features) follows the second barrier."""
+    features) follows the second barrier.
+
+    ``keep_noise`` (off by default): the exchange object's noise rows are the ones ``sharded_forward_peer`` hashed for the same
+    seed and rows, so a training step that calls forward and then backward may read them again instead of hashing them a
+    second time -- one hash per element and step instead of two, at the price of keeping S_r (``n_r x R`` bf16) alive between
+    the two calls, which the stateless C entry points never do."""
     from . import kernels as K
     R, G = ex.R, ex.world
     cur = torch.cuda.current_stream(ex.dev)
-    K.noise(ex.S.shape[0], R, seed, plan.row_lo, 0, out=ex.S)
+    if not (keep_noise and ex.noise_key == (int(seed), plan.row_lo, plan.row_hi)):
+        K.noise(ex.S.shape[0], R, seed, plan.row_lo, 0, out=ex.S)
+        ex.noise_key = (int(seed), plan.row_lo, plan.row_hi)
     _mark(timer, "noise fill")
     slot = ex.parts_off + ex.rank * ex.t_r * R * 2            # my slot in every owner's g_parts
     fused_scatter = fused_scatter and os.environ.get("RANDUMB_B200_FUSED_SCATTER", "1") != "0"

@@ -64,6 +64,11 @@ def _worker(rank, world, port, tmp):
             torch.cuda.synchronize()
             K.check_status()
             out["y_twice"] = bool(torch.equal(ya, y) and torch.equal(yb, y))
+            # a backward that reads the noise rows the forward left in the exchange object: same bits as one that hashes them again
+            dxk, dck = rb.parallel.sharded_backward_peer(dy_r, x, C, SEED, plan, ex, keep_noise=True)
+            torch.cuda.synchronize()
+            K.check_status()
+            out["keep_noise"] = bool(torch.equal(dxk, dx) and torch.equal(dck, dc))
             # the NCCL path on the same inputs
             y_n = rb.parallel.sharded_forward(x, C, SEED, plan)
             dx_n, dc_n = rb.parallel.sharded_backward(dy_r, x, C, SEED, plan, replicate=False)
@@ -98,6 +103,6 @@ def test_peer_exchange_matches_single_gpu_and_oracle(tmp_path):
     # same forward bits as the NCCL path (z is bit-identical whichever way it travels); gradients agree within tolerance
     # (NCCL sums the partial g in its own order, this path in rank order)
     for p in parts:
-        assert p["y_twice"]
+        assert p["y_twice"] and p["keep_noise"]
         assert torch.equal(p["y0"], p["y_nccl"])
         assert O.close(p["dx0"], p["dx_nccl"], 2e-2) and O.close(p["dc0"], p["dc_nccl"], 2e-2)
