@@ -7,7 +7,7 @@
  * and   y = x W^T,   dX = dY W,   dC = S^T (dY^T X).
  * W is never formed on the factored path (every BASELINE layer but a 256 -> 10 head); the W path, chosen when it costs
  * fewer FLOPs, keeps W in the caller's workspace for the length of one call.  S is regenerated from the seed in every call: tile by tile in shared
- * memory, or (every backward; forwards of 1024 tokens or more) once per call as a transient bf16 copy in the caller's workspace -- see
+ * memory, or (every backward; forwards of more than 1024 tokens) once per call as a transient bf16 copy in the caller's workspace -- see
  * RDB_OPT_STAGE_NOISE.  Nothing of it survives the call.
  *
  * Conventions for every entry point
@@ -98,7 +98,7 @@ const char *rdb_strerror(int code);
  *                        0 (default): automatic -- S (bf16, N x R, never W) is written once per call into the workspace
  *                           and consumed by the plain tensor-core product, which hashes every noise element once instead
  *                           of once per 512-token tile: by the backward at every token count (g = dY S has too few work
- *                           units to hash S in otherwise), by the forward for 1024 tokens or more; a forward below that,
+ *                           units to hash S in otherwise), by the forward for more than 1024 tokens; a forward of at most 1024,
  *                           and every call whose S would exceed 1 GiB, regenerates S tile by tile in shared memory
  *                        1: always regenerate tile by tile (no S in memory)   2: always stage when it fits
  *   RDB_OPT_RESERVE_SMS  0 (default) .. RDB_MAX_RESERVE_SMS: SMs the persistent plain-product kernels leave without a

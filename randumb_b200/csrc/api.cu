@@ -91,11 +91,13 @@ static bool stage_noise(int op, int64_t T, int64_t N, int64_t R, const CallOpts 
     const bool fits = (double)N * (double)R * 2.0 <= 1073741824.0;
     if (o.stage_noise == 1 || !fits) return false;
     if (o.stage_noise == 2) return true;
-    // Forward (op 0): y = z S^T has N / 256 work units whatever the token count, so below 1024 tokens -- where each element
-    // is hashed at most twice -- regenerating costs the same as a fill plus a plain product and needs no scratch.
+    // Forward (op 0): y = z S^T has N / 256 work units whatever the token count, and up to 1024 tokens the regenerating
+    // kernel hashes every element once too (one 512-token tile, or two that share each generated stage), under its MMAs and
+    // without the round trip of S through memory: 53 against 64 us for 1024 tokens of the headline layer, 251 against 290
+    // for a 65536 x 2048 noise block; from 1536 tokens on the fill wins.
     // Backward (op 1): g = dY S has only R / 256 work units per 512 tokens to hash all of S in, so hashing it once on every SM
     // wins at every token count (512 tokens, 16384 x 1024: 206 against 60 us for the whole backward).
-    return op == 1 || T >= 1024;
+    return op == 1 || T > 1024;
 }
 
 struct WsLayout {

@@ -267,8 +267,8 @@ def noise_product(a: torch.Tensor, n: int, seed: int, transposed: bool = False, 
                   options: Optional[_lib.CallOptions] = None) -> torch.Tensor:
     """``a @ S[row0:row0+n].T`` (``transposed=False``, a is [M, R]) or ``a @ S[row0:row0+Kc]`` (``transposed=True``, a is
     [M, Kc], result [M, n]) with the same rule as the linear entry points: bf16 problems hash S once into a temporary and run
-    the plain tensor-core product -- the transposed product (the backward's g = dY S) always, the other one from 1024 rows of
-    ``a`` up; everything else regenerates S inside the kernel."""
+    the plain tensor-core product -- the transposed product (the backward's g = dY S) always, the other one for more than 1024
+    rows of ``a``; everything else regenerates S inside the kernel."""
     M, Kc = a.shape
     rows, cols = (Kc, n) if transposed else (n, Kc)          # extent of the noise block S[rows, cols]
     ok8 = rows % 8 == 0 and cols % 8 == 0
