@@ -243,7 +243,7 @@ def workload_config(name, cfg, gpus, replicate_grads=False, gather_output=False)
                ("y all-gathered beside the backward products; " if gather_output else "y stays row-sharded; ") + "z all-gather, " +
                ("g reduce-scatter, dX all-gather, dC all-reduce (gradients replicated on every rank)" if replicate_grads else
                 "g all-reduce; dX stays token-sharded and dC input-feature-sharded (every gradient element on one rank)"))
-    par = {"gemm": f"dp{gpus} (tokens per rank fixed, dC all-reduce behind the dX product)" if gpus > 1 else "single GPU",
+    par = {"gemm": f"dp{gpus} (tokens per rank fixed, dC all-reduce after the backward)" if gpus > 1 else "single GPU",
            "sharded": sharded if gpus > 1 else "single GPU",
            "gemv": "replicas only"}[name]
     return {"workload": f"{name}: x[{cfg['T']}x{cfg['K']}] {cfg['dtype']}, virtual W[{cfg['N']}x{cfg['K']}], d_c={cfg['R']}, "
@@ -434,7 +434,7 @@ def run_ours(args, cfg):
             return sb.step(args.gather_output, args.replicate_grads)
         y = K.linear_fwd(x, C, seed, n_local, row0)
         if world > 1:
-            # data parallel: dC first, its all-reduce overlapped with the dX product
+            # data parallel: the library's backward, then the all-reduce of dC
             dx, dc = rb.parallel.data_parallel_backward(dy, x, C, seed, row0)
         else:
             dx, dc = K.linear_bwd(dy, x, C, seed, row0)

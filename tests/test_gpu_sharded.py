@@ -27,6 +27,7 @@ def _worker(rank, world, port, tmp):
     try:
         import randumb_b200 as rb
         from randumb_b200 import kernels as K
+        from oracle import oracle as O
         torch.cuda.set_device(0)
         T, Kin, N, R, seed = 1000, 264, 528, 72, 7
         g = torch.Generator().manual_seed(5)
@@ -39,11 +40,18 @@ def _worker(rank, world, port, tmp):
         # nothing replicated: token slice of dX, input-feature slice of dC
         lean_dx, lean_dc = rb.parallel.sharded_backward(dy[:, plan.row_lo:plan.row_hi].contiguous(), x, C, seed, plan,
                                                         replicate=False)
-        # data parallel: this rank's half of the tokens, dC all-reduced behind the dX product
+        # data parallel: this rank's half of the tokens, dC all-reduced after the backward ...
         lo, hi = rank * (T // world), (rank + 1) * (T // world)
         dp_dx, dp_dc = rb.parallel.data_parallel_backward(dy[lo:hi].contiguous(), x[lo:hi].contiguous(), C, seed)
+        # ... or behind the dX product: the same products, launched one by one
+        os.environ["RANDUMB_B200_DP_BACKWARD"] = "hidden"
+        try:
+            hid_dx, hid_dc = rb.parallel.data_parallel_backward(dy[lo:hi].contiguous(), x[lo:hi].contiguous(), C, seed)
+        finally:
+            del os.environ["RANDUMB_B200_DP_BACKWARD"]
         torch.cuda.synchronize()
         K.check_status()
+        assert O.close(hid_dx, dp_dx, 1e-2) and O.close(hid_dc, dp_dc, 1e-2)
         torch.save({"y": y_r.cpu(), "dx": dx.cpu(), "dc": dc.cpu(), "rows": (plan.row_lo, plan.row_hi),
                     "dp_dx": dp_dx.cpu(), "dp_dc": dp_dc.cpu(), "tok": (lo, hi),
                     "lean_dx": lean_dx.cpu(), "lean_dc": lean_dc.cpu()}, os.path.join(tmp, f"r{rank}.pt"))
