@@ -109,9 +109,10 @@ const char *rdb_strerror(int code);
  *                        the staged S on a stream of the library's own, forked from and joined back into the caller's stream
  *                        with events, so the integer-ALU fill runs beside the tensor-core product z = x C^T it does not depend
  *                        on (a fill in between stays on the caller's stream: it is more than launch latency, and beside a
- *                        short product its resident threads cost the product's MMA-issuing thread as much as it takes).  The stream and its two events are
- *                        created once per device by the first such call (make it before any stream capture; a call that
- *                        finds its stream capturing before they exist keeps the fill on the caller's stream).
+ *                        short product its resident threads cost the product's MMA-issuing thread as much as it takes).  The
+ *                        stream and its two events are created once per device by the first such call (make it before any
+ *                        stream capture; a call that finds its stream capturing before they exist keeps the fill on the
+ *                        caller's stream).
  *                        0: always on the caller's stream.   2: always beside the z product.
  *   RDB_OPT_GEMV_FUSED   0 (default): the batch-1 entry points (rdb_gemv_fwd, rdb_gemv_bwd, and rdb_linear_* for one float32 row)
  *                        launch one kernel per step (two forward, two backward), chained with programmatic dependent launch.
