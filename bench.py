@@ -243,7 +243,7 @@ def workload_config(name, cfg, gpus, replicate_grads=False, gather_output=False)
                ("y all-gathered beside the backward products; " if gather_output else "y stays row-sharded; ") + "z all-gather, " +
                ("g reduce-scatter, dX all-gather, dC all-reduce (gradients replicated on every rank)" if replicate_grads else
                 "g all-reduce; dX stays token-sharded and dC input-feature-sharded (every gradient element on one rank)"))
-    par = {"gemm": f"dp{gpus} (tokens per rank fixed, dC all-reduce after the backward)" if gpus > 1 else "single GPU",
+    par = {"gemm": f"dp{gpus} (tokens per rank fixed, dC summed over the ranks after the backward)" if gpus > 1 else "single GPU",
            "sharded": sharded if gpus > 1 else "single GPU",
            "gemv": "replicas only"}[name]
     return {"workload": f"{name}: x[{cfg['T']}x{cfg['K']}] {cfg['dtype']}, virtual W[{cfg['N']}x{cfg['K']}], d_c={cfg['R']}, "
@@ -428,6 +428,12 @@ def run_ours(args, cfg):
         dy = torch.randn(T, n_local, generator=g).to(dt).to(dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.workload == "gemv" else None
 
+    # data parallel: the coefficient gradient is summed by the library's kernels over peer memory when the ranks can map each
+    # other's buffers (RANDUMB_B200_DP_ALLREDUCE=nccl: always NCCL)
+    dc_sum = None
+    if world > 1 and sb is None and args.workload != "gemv" and os.environ.get("RANDUMB_B200_DP_ALLREDUCE", "peer") != "nccl":
+        dc_sum = rb.parallel.PeerAllReduce.create(R * Kin, dev)
+
     def step():
         if sb is not None:
             # rows split over ranks: z gathered, g summed; by default dX stays token-sharded and dC input-feature-sharded
@@ -435,7 +441,7 @@ def run_ours(args, cfg):
         y = K.linear_fwd(x, C, seed, n_local, row0)
         if world > 1:
             # data parallel: the library's backward, then the all-reduce of dC
-            dx, dc = rb.parallel.data_parallel_backward(dy, x, C, seed, row0)
+            dx, dc = rb.parallel.data_parallel_backward(dy, x, C, seed, row0, peer=dc_sum)
         else:
             dx, dc = K.linear_bwd(dy, x, C, seed, row0)
         return y, dx, dc

@@ -392,6 +392,124 @@ class PeerExchange:
         return base + row * self.R * 2
 
 
+class PeerAllReduce:
+    """Sum of a bf16 tensor over the ranks of one node through peer memory, with this library's kernels: every rank stores
+    chunk j of its tensor into rank j's slot array, after a barrier rank j adds the G contributions to its chunk in rank order
+    (float32 accumulation: the result does not depend on arrival order and is the same on every rank), stores the sum into
+    every rank's result buffer, and a second barrier publishes it.  For the 8 MB coefficient gradient of the headline layer
+    on 8 GPUs this takes about half as long as the NCCL all-reduce it replaces.  Same requirements as ``PeerExchange`` (one
+    GPU per rank, at most 8 ranks); ``create`` returns None otherwise.
+
+    Buffer (identical on every rank): [0, 4096) barrier flags | parts [G, chunk] | full [G * chunk], bf16."""
+    FLAG_BYTES = 4096
+
+    def __init__(self, numel: int, rank: int, world: int, buf: torch.Tensor, ptrs: Sequence[int], how: str, keep=None):
+        from . import kernels as K
+        self.numel, self.rank, self.world, self.buf, self.how, self._keep = numel, rank, world, buf, how, keep
+        self.dev = buf.device
+        self.chunk = self.chunk_elems(numel, world)
+        self.parts_off = self.FLAG_BYTES
+        self.full_off = self.parts_off + world * self.chunk * 2
+        self.ptrs = K._ptr_array(ptrs)
+        self.parts = buf[self.parts_off:self.full_off].view(torch.bfloat16).view(world, self.chunk)
+        self.full = buf[self.full_off:self.full_off + world * self.chunk * 2].view(torch.bfloat16)
+        self.red = torch.empty(self.chunk, dtype=torch.bfloat16, device=self.dev)
+        self.pad = torch.zeros(world * self.chunk, dtype=torch.bfloat16, device=self.dev) if world * self.chunk != numel else None
+        self.epoch = 0
+
+    @staticmethod
+    def chunk_elems(numel: int, world: int) -> int:
+        per = -(-numel // world)
+        return -(-per // 8) * 8                      # whole 16-byte units
+
+    @classmethod
+    def total_bytes(cls, numel: int, world: int) -> int:
+        return cls.FLAG_BYTES + 2 * world * cls.chunk_elems(numel, world) * 2
+
+    @classmethod
+    def create(cls, numel: int, device: torch.device, group=None) -> Optional["PeerAllReduce"]:
+        if not dist.is_initialized() or dist.get_backend(group) != "nccl":
+            return None
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if world < 2 or world > _lib.MAX_PEERS or numel <= 0:
+            return None
+        mapped = _map_peer_buffer(cls.total_bytes(numel, world), device, world, rank, group)
+        if mapped is None:
+            return None
+        buf, ptrs, how, keep = mapped
+        return cls(numel, rank, world, buf, ptrs, how, keep)
+
+    def _barrier(self) -> None:
+        from . import kernels as K
+        self.epoch += 1
+        K.peer_barrier(self.ptrs, self.rank, self.world, self.epoch, self.dev)
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """In place: ``t`` (contiguous bf16, ``numel`` elements) becomes the sum over the ranks.  Same sequence of calls on
+        every rank; everything is enqueued on the current stream."""
+        from . import kernels as K
+        assert t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() == self.numel and t.device == self.dev
+        src = t.view(-1)
+        if self.pad is not None:
+            self.pad[:self.numel].copy_(src)
+            src = self.pad
+        G, c = self.world, self.chunk
+        K.peer_scatter(self.ptrs, G, self.parts_off + self.rank * c * 2, src.view(G, c))     # my chunk j -> rank j, slot `rank`
+        self._barrier()
+        K.reduce_slots(self.red, self.parts)                                               # rank order, float32
+        K.peer_copy(self.ptrs, G, self.full_off + self.rank * c * 2, self.red)
+        self._barrier()
+        t.view(-1).copy_(self.full[:self.numel])
+        return t
+
+
+def _map_peer_buffer(nbytes: int, device: torch.device, world: int, rank: int, group=None):
+    """A zeroed buffer of ``nbytes`` on every rank, mapped into all of them: (buffer, peer pointers, how, keep-alive) or None
+    when the ranks share a GPU or neither symmetric memory nor CUDA IPC is available (the same answer on every rank)."""
+    seen = [None] * world
+    dist.all_gather_object(seen, str(torch.cuda.get_device_properties(device).uuid), group=group)
+    mapped = None
+    if len(set(seen)) == world:
+        try:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+            grp = group if group is not None else dist.group.WORLD
+            buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+            buf.zero_()
+            torch.cuda.synchronize(device)
+            hdl = symm_mem.rendezvous(buf, grp)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            if len(ptrs) != world or ptrs[rank] != buf.data_ptr():
+                raise RuntimeError("symmetric memory handle does not describe this buffer")
+            mapped = (buf, ptrs, "torch symmetric memory", hdl)
+        except Exception as e_symm:
+            try:
+                buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+                torch.cuda.synchronize(device)
+                handles = [None] * world
+                dist.all_gather_object(handles, buf.untyped_storage()._share_cuda_(), group=group)
+                ptrs, keep = [], []
+                for r, h in enumerate(handles):
+                    if r == rank:
+                        ptrs.append(buf.data_ptr())
+                        continue
+                    st = torch.UntypedStorage._new_shared_cuda(*h)
+                    keep.append(st)
+                    ptrs.append(st.data_ptr())
+                mapped = (buf, ptrs, "CUDA IPC", keep)
+            except Exception as e_ipc:
+                if os.environ.get("RANDUMB_B200_DEBUG"):
+                    print(f"peer buffer unavailable: symmetric memory: {e_symm!r}; IPC: {e_ipc!r}", flush=True)
+                mapped = None
+    ok = torch.tensor([1 if mapped is not None else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    if int(ok.item()) == 0:
+        return None
+    torch.cuda.synchronize(device)
+    dist.barrier(group=group)            # every rank's flags are zero before anybody signals
+    return mapped
+
+
 def sharded_forward_peer(x: torch.Tensor, coef: torch.Tensor, seed: int, plan: ShardedLayerPlan, ex: PeerExchange,
                          timer: Optional[PhaseTimer] = None) -> torch.Tensor:
     """``sharded_forward`` with the z all-gather done by this library's kernels: the tensor cores compute the local token
@@ -482,22 +600,26 @@ def sharded_backward_peer(dy_local: torch.Tensor, x: torch.Tensor, coef: torch.T
 # data-parallel backward: the layer's backward, then the all-reduce of dC (or the all-reduce hidden behind the dX product)
 # ------------------------------------------------------------------------------------------------
 def data_parallel_backward(dy: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, seed: int, row0: int = 0, group=None,
-                           average: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+                           average: bool = False, peer: Optional["PeerAllReduce"] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """(dX[T, K], dC[R, K] summed over the ranks) for a replicated bf16 layer and this rank's tokens.
 
     Default: the library's own backward (``rdb_linear_bwd``: dX beside dC on disjoint CTA pairs where their tiles pack),
     then the all-reduce of dC in the open.  ``RANDUMB_B200_DP_BACKWARD=hidden`` selects the older schedule -- dC first, its
     all-reduce started asynchronously behind the dX product, which is given fewer SMs so that the collective can run -- which
     hides the reduction but pays for it with the SMs taken from dX and with dX and dC no longer running side by side:
-    0.597 against 0.587 ms per step of the headline layer at 2 GPUs, 0.619 against 0.596 at 4.  The returned dC is safe to
-    use on the current stream.
+    0.597 against 0.587 ms per step of the headline layer at 2 GPUs, 0.619 against 0.596 at 4.  ``peer``: a ``PeerAllReduce``
+    for dC's size does the reduction with this library's kernels over peer memory instead of NCCL (default schedule only).
+    The returned dC is safe to use on the current stream.
     """
     from . import kernels as K
     R = coef.shape[0]
     if os.environ.get("RANDUMB_B200_DP_BACKWARD", "plain") != "hidden":
         dx, dc = K.linear_bwd(dy, x, coef, seed, row0)
         if dist.is_initialized() and dist.get_world_size(group) > 1:
-            dist.all_reduce(dc, op=dist.ReduceOp.SUM, group=group)
+            if peer is not None:
+                peer.all_reduce(dc)           # this library's kernels over peer memory, sum in rank order
+            else:
+                dist.all_reduce(dc, op=dist.ReduceOp.SUM, group=group)
             if average:
                 dc /= dist.get_world_size(group)
         return dx, dc

@@ -74,6 +74,26 @@ def _worker(rank, world, port, tmp):
             dx_n, dc_n = rb.parallel.sharded_backward(dy_r, x, C, SEED, plan, replicate=False)
             torch.cuda.synchronize()
             out["y_nccl"], out["dx_nccl"], out["dc_nccl"] = y_n.cpu(), dx_n.cpu(), dc_n.cpu()
+        # the all-reduce over peer memory: sum in rank order with float32 accumulation, the same bits on every rank, for a size
+        # that divides into whole 16-byte chunks per rank and for one that needs padding; twice in a row
+        for numel in (72 * KIN, 1001):
+            par = rb.parallel.PeerAllReduce.create(numel, dev)
+            out[f"allreduce_{numel}"] = par is not None
+            if par is not None:
+                for rep in range(2):
+                    gen = torch.Generator().manual_seed(100 * rep + rank)
+                    mine = torch.randn(numel, generator=gen).bfloat16().to(dev)
+                    parts = [torch.empty_like(mine) for _ in range(world)]
+                    dist.all_gather(parts, mine)
+                    want = torch.stack(parts).float().sum(0)          # rank order is the stacking order
+                    acc = torch.zeros(numel, dtype=torch.float32, device=dev)
+                    for p_ in parts:
+                        acc += p_.float()
+                    got = par.all_reduce(mine.clone())
+                    torch.cuda.synchronize()
+                    K.check_status()
+                    out[f"allreduce_{numel}"] = out[f"allreduce_{numel}"] and bool(torch.equal(got, acc.bfloat16())) and \
+                        bool(torch.allclose(got.float(), want, rtol=2e-2, atol=1e-2))
         torch.save(out, os.path.join(tmp, f"r{rank}.pt"))
         dist.barrier()
     finally:
@@ -103,6 +123,6 @@ def test_peer_exchange_matches_single_gpu_and_oracle(tmp_path):
     # same forward bits as the NCCL path (z is bit-identical whichever way it travels); gradients agree within tolerance
     # (NCCL sums the partial g in its own order, this path in rank order)
     for p in parts:
-        assert p["y_twice"] and p["keep_noise"]
+        assert p["y_twice"] and p["keep_noise"] and p[f"allreduce_{72 * KIN}"] and p["allreduce_1001"]
         assert torch.equal(p["y0"], p["y_nccl"])
         assert O.close(p["dx0"], p["dx_nccl"], 2e-2) and O.close(p["dc0"], p["dc_nccl"], 2e-2)
