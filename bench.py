@@ -625,7 +625,7 @@ def run_ours(args, cfg):
             "dtype": cfg["dtype"], "data": "synthetic",
             "config": dict(workload_config(args.workload, cfg, world, args.replicate_grads, args.gather_output),
                            **({"exchange": sb.exchange} if sb is not None else {})),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(args.workload, staged) * args.steps,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": (launches_per_step(args.workload, staged) + (5 if dc_sum is not None else 0)) * args.steps,   # + the peer-memory sum of dC: scatter, barrier, ordered sum, store, barrier
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
         if step_ms:
